@@ -1,0 +1,183 @@
+// Memory-bound kernels of the step: embedding gather, RMSNorm, SiLU*up, and the fused
+// rotate-and-cache kernel (RoPE on queries and keys in 32-bit, keys and values written into
+// their pages).  All take float32 or bfloat16 activations; statistics and angles are 32-bit.
+// Reference counterparts: tiny_llm/ops/cuda/embedding.cu:10-29, norm.cu:16-49, silu.cu:7-12,
+// arithmetic.cu:7-22, rope.cu:26-95, gemm.cu:380-411 (the scatter of K/V rows into pages).
+#include "common.cuh"
+
+TLLM_DEFINE_LAST_ERROR
+
+namespace tllm {
+
+// ---------------------------------------------------------------- embedding: out[t,:] = table[tokens[t],:]
+template <typename T>
+__global__ void embedding_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
+                                 float* __restrict__ out, int n_tokens, int hidden) {
+  const int t = blockIdx.x;
+  if (t >= n_tokens) return;
+  const T* row = table + (size_t)tokens[t] * hidden;
+  float* dst = out + (size_t)t * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_f32(row[i]);
+}
+
+// ---------------------------------------------------------------- RMSNorm
+// y_j = (w_j * x_j) / sqrt(sum_j(x_j^2)/H + eps); one block per row; rows may be gathered.
+template <typename T>
+__global__ void rms_norm_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                T* __restrict__ out, const int* __restrict__ rows, int n_rows,
+                                int hidden, float eps) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  if (r >= n_rows) return;
+  const float* src = x + (size_t)(rows ? rows[r] : r) * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = src[i];
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  const float denom = sqrtf(ss / (float)hidden + eps);
+  T* dst = out + (size_t)r * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = from_f32<T>((w[i] * src[i]) / denom);
+}
+
+// ---------------------------------------------------------------- SiLU(gate) * up
+// `gu` rows hold gate and up interleaved in blocks: [2 g B, 2 g B + B) gate, next B up.
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int m, int inter, int blk) {
+  const size_t total = (size_t)m * inter;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const int row = (int)(idx / inter), col = (int)(idx % inter);
+    const int g = col / blk, j = col % blk;
+    const T* src = gu + (size_t)row * 2 * inter + (size_t)g * 2 * blk;
+    const float gate = to_f32(src[j]), up = to_f32(src[blk + j]);
+    out[idx] = from_f32<T>((gate / (1.f + expf(-gate))) * up);
+  }
+}
+
+// ---------------------------------------------------------------- rotate and cache
+// qkv row: [nq*hd queries | nkv*hd keys | nkv*hd values] (keys/values absent when slot_mapping is
+// null).  Queries are rotated in place; keys are rotated and written to the key pages, values are
+// copied to the value pages, both at slot_mapping[t] = page*page_size + offset.
+// Rotation (rotate-half over the whole head; rot_dim is hd or 0): x'_i = c x_i - s x_{i+hd/2},
+// x'_{i+hd/2} = s x_i + c x_{i+hd/2}.
+template <typename T>
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+                                     const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                     int rot_dim, int n_tokens, int nq, int nkv, int hd, int row_stride,
+                                     T* __restrict__ kcache, T* __restrict__ vcache,
+                                     const int* __restrict__ slot_mapping, int page_size,
+                                     long long page_stride, long long head_stride) {
+  const int t = blockIdx.x;
+  if (t >= n_tokens) return;
+  const int half = rot_dim / 2;
+  const int pos = positions[t];
+  T* row = qkv + (size_t)t * row_stride;
+  const bool write_kv = slot_mapping != nullptr;
+  const int heads = write_kv ? nq + nkv : nq;
+  const int half_hd = hd / 2;
+  long long slot_base = 0;
+  if (write_kv) {
+    const int slot = slot_mapping[t];
+    slot_base = (long long)(slot / page_size) * page_stride + (long long)(slot % page_size) * hd;
+  }
+  // queries and keys: one thread per (head, i < hd/2) rotates the pair of dims (i, i + hd/2)
+  for (int idx = threadIdx.x; idx < heads * half_hd; idx += blockDim.x) {
+    const int h = idx / half_hd, i = idx % half_hd;
+    T* head = row + (size_t)h * hd;
+    const float va = to_f32(head[i]), vb = to_f32(head[i + half_hd]);
+    float oa = va, ob = vb;
+    if (cos_t) {
+      const float c = cos_t[(size_t)pos * half + i], s = sin_t[(size_t)pos * half + i];
+      oa = c * va - s * vb;
+      ob = s * va + c * vb;
+    }
+    T* dst = h < nq ? head : kcache + slot_base + (long long)(h - nq) * head_stride;
+    dst[i] = from_f32<T>(oa);
+    dst[i + half_hd] = from_f32<T>(ob);
+  }
+  if (write_kv) {
+    const T* vsrc = row + (size_t)(nq + nkv) * hd;
+    for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
+      const int h = idx / hd, i = idx % hd;
+      vcache[slot_base + (long long)h * head_stride + i] = vsrc[idx];
+    }
+  }
+}
+
+}  // namespace tllm
+
+using namespace tllm;
+
+extern "C" int tllm_embedding(const int* tokens, const void* table, float* out, int n_tokens, int hidden,
+                              int dtype, void* stream) {
+  TLLM_REQUIRE(n_tokens > 0 && hidden > 0, "embedding: empty input (%d tokens, width %d)", n_tokens, hidden);
+  const int threads = hidden >= 1024 ? 256 : 128;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == TLLM_F32)
+    embedding_kernel<float><<<n_tokens, threads, 0, s>>>(tokens, (const float*)table, out, n_tokens, hidden);
+  else if (dtype == TLLM_BF16)
+    embedding_kernel<__nv_bfloat16><<<n_tokens, threads, 0, s>>>(tokens, (const __nv_bfloat16*)table, out, n_tokens, hidden);
+  else
+    TLLM_FAIL(TLLM_ERR_ARG, "embedding: unknown dtype code %d", dtype);
+  TLLM_CHECK_LAUNCH("embedding");
+  return TLLM_OK;
+}
+
+extern "C" int tllm_rms_norm(const float* x, const float* w, void* out, const int* rows, int n_rows, int hidden,
+                             float eps, int out_dtype, void* stream) {
+  TLLM_REQUIRE(n_rows > 0 && hidden > 0, "rms_norm: empty input (%d rows, width %d)", n_rows, hidden);
+  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (out_dtype == TLLM_F32)
+    rms_norm_kernel<float><<<n_rows, threads, 0, s>>>(x, w, (float*)out, rows, n_rows, hidden, eps);
+  else if (out_dtype == TLLM_BF16)
+    rms_norm_kernel<__nv_bfloat16><<<n_rows, threads, 0, s>>>(x, w, (__nv_bfloat16*)out, rows, n_rows, hidden, eps);
+  else
+    TLLM_FAIL(TLLM_ERR_ARG, "rms_norm: unknown dtype code %d", out_dtype);
+  TLLM_CHECK_LAUNCH("rms_norm");
+  return TLLM_OK;
+}
+
+extern "C" int tllm_silu_mul(const void* gu, void* out, int m, int inter, int blk, int dtype, void* stream) {
+  TLLM_REQUIRE(m > 0 && inter > 0 && blk > 0 && inter % blk == 0,
+               "silu_mul: %d rows, width %d, block %d (the block must divide the width)", m, inter, blk);
+  const size_t total = (size_t)m * inter;
+  const int threads = 256;
+  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == TLLM_F32)
+    silu_mul_kernel<float><<<blocks, threads, 0, s>>>((const float*)gu, (float*)out, m, inter, blk);
+  else if (dtype == TLLM_BF16)
+    silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, s>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, m, inter, blk);
+  else
+    TLLM_FAIL(TLLM_ERR_ARG, "silu_mul: unknown dtype code %d", dtype);
+  TLLM_CHECK_LAUNCH("silu_mul");
+  return TLLM_OK;
+}
+
+extern "C" int tllm_rope_kv_write(void* qkv, const int* positions, const float* cos_t, const float* sin_t,
+                                  int rot_dim, int n_tokens, int nq, int nkv, int hd, int row_stride,
+                                  void* kcache, void* vcache, const int* slot_mapping, int page_size,
+                                  long long page_stride, long long head_stride, int dtype, void* stream) {
+  TLLM_REQUIRE(n_tokens > 0 && nq > 0 && nkv > 0, "rope_kv_write: empty input");
+  TLLM_REQUIRE(hd > 0 && hd % 2 == 0, "rope_kv_write: head size %d must be even", hd);
+  TLLM_REQUIRE(rot_dim >= 0 && rot_dim <= hd && rot_dim % 2 == 0, "rope_kv_write: rotary size %d must be even and at most the head size %d", rot_dim, hd);
+  TLLM_REQUIRE(rot_dim == 0 || (cos_t && sin_t), "rope_kv_write: rotary size %d without tables", rot_dim);
+  TLLM_REQUIRE(rot_dim == 0 || rot_dim == hd, "rope_kv_write: partial rotary (%d of %d dims) is not built", rot_dim, hd);
+  TLLM_REQUIRE(!slot_mapping || (kcache && vcache && page_size > 0), "rope_kv_write: a slot mapping needs cache pointers and a page size");
+  const int work = (nq + nkv) * hd / 2;
+  const int threads = work >= 512 ? 256 : 128;
+  cudaStream_t s = (cudaStream_t)stream;
+  const float* c = rot_dim ? cos_t : nullptr;
+  const float* sn = rot_dim ? sin_t : nullptr;
+  if (dtype == TLLM_F32)
+    rope_kv_write_kernel<float><<<n_tokens, threads, 0, s>>>((float*)qkv, positions, c, sn, rot_dim, n_tokens, nq, nkv, hd, row_stride, (float*)kcache, (float*)vcache, slot_mapping, page_size, page_stride, head_stride);
+  else if (dtype == TLLM_BF16)
+    rope_kv_write_kernel<__nv_bfloat16><<<n_tokens, threads, 0, s>>>((__nv_bfloat16*)qkv, positions, c, sn, rot_dim, n_tokens, nq, nkv, hd, row_stride, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, slot_mapping, page_size, page_stride, head_stride);
+  else
+    TLLM_FAIL(TLLM_ERR_ARG, "rope_kv_write: unknown dtype code %d", dtype);
+  TLLM_CHECK_LAUNCH("rope_kv_write");
+  return TLLM_OK;
+}

@@ -1,0 +1,298 @@
+// Next-token choice on the device, one block per row of 32-bit logits.
+//   argmax: first maximum, lowest index on ties (tiny_llm/logit_processors/argmax_processor.cpp:24-31).
+//   sample: the reference's chain temperature -> top-k -> top-p -> multinomial
+//     (tiny_llm/pipeline/pipeline.cpp:157-161), which it runs on the CPU with sorts
+//     (sort_processors.cpp:53-142, sample_processors.cpp:7-54).  Here nothing is sorted: the k-th
+//     largest value and the top-p cut are found by a bitwise search over the ordered bit patterns
+//     of the values, each probe being one counting pass over the row.
+//       top-k keeps exactly k values: those above the k-th largest, and of those equal to it the
+//         ones with the lowest token ids.
+//       top-p drops the smallest values while their summed probability stays <= 1 - p; values
+//         that tie at the cut are kept or dropped together; the maximum always stays.
+//       multinomial walks the kept tokens in ascending id and takes the first whose running
+//         probability exceeds u, u in [0,1) drawn from (seed, counter) of the row by splitmix64, so a
+//         request's draws do not depend on its batch.
+//     A row with temperature <= 0 is taken greedily.
+// `work` is scratch of n*V floats in global memory: the row's scaled logits, then its weights.
+#include <math_constants.h>
+
+#include "common.cuh"
+
+TLLM_DEFINE_LAST_ERROR
+
+namespace tllm {
+
+constexpr int ST = 1024;
+
+__device__ __forceinline__ uint32_t ordered_key(float f) {
+  const uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+struct BlockScratch {
+  float f[33];
+  int i[33];
+  unsigned long long u[33];
+};
+
+__device__ __forceinline__ float block_max_f(float v, BlockScratch& sc) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) sc.f[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < (blockDim.x >> 5) ? sc.f[lane] : -CUDART_INF_F;
+    t = warp_max(t);
+    if (lane == 0) sc.f[32] = t;
+  }
+  __syncthreads();
+  return sc.f[32];
+}
+
+__device__ __forceinline__ float block_sum_f(float v, BlockScratch& sc) { return block_sum(v, sc.f); }
+
+__device__ __forceinline__ int block_sum_i(int v, BlockScratch& sc) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if (lane == 0) sc.i[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    int t = lane < (blockDim.x >> 5) ? sc.i[lane] : 0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (lane == 0) sc.i[32] = t;
+  }
+  __syncthreads();
+  return sc.i[32];
+}
+
+// Exclusive scan of 0/1 flags over the block in thread order; *total gets the block's count.
+__device__ __forceinline__ int block_excl_scan_flag(bool flag, int* total, BlockScratch& sc) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const unsigned ballot = __ballot_sync(0xffffffffu, flag);
+  const int in_warp = __popc(ballot & ((1u << lane) - 1u));
+  __syncthreads();
+  if (lane == 0) sc.i[warp] = __popc(ballot);
+  __syncthreads();
+  if (warp == 0) {
+    const int c = lane < (blockDim.x >> 5) ? sc.i[lane] : 0;
+    int incl = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int n = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += n;
+    }
+    sc.i[lane] = incl - c;
+    if (lane == 31) sc.i[32] = incl;
+  }
+  __syncthreads();
+  *total = sc.i[32];
+  return sc.i[warp] + in_warp;
+}
+
+// Inclusive scan of floats over the block in thread order; *total gets the block's sum.
+__device__ __forceinline__ float block_incl_scan_f(float v, float* total, BlockScratch& sc) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float incl = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float n = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += n;
+  }
+  __syncthreads();
+  if (lane == 31) sc.f[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    const float c = lane < (blockDim.x >> 5) ? sc.f[lane] : 0.f;
+    float w = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float n = __shfl_up_sync(0xffffffffu, w, o);
+      if (lane >= o) w += n;
+    }
+    sc.f[lane] = w - c;
+    if (lane == 31) sc.f[32] = w;
+  }
+  __syncthreads();
+  *total = sc.f[32];
+  return sc.f[warp] + incl;
+}
+
+__device__ __forceinline__ int block_argmax(const float* __restrict__ row, int v, BlockScratch& sc) {
+  float best = -CUDART_INF_F;
+  int idx = 0x7fffffff;
+  for (int i = threadIdx.x; i < v; i += blockDim.x) {
+    const float x = row[i];
+    if (idx == 0x7fffffff || x > best) { best = x; idx = i; }
+  }
+  // pack (ordered value, inverted index) so that one max picks the value, then the lowest index
+  unsigned long long key = idx == 0x7fffffff ? 0ull
+      : ((unsigned long long)ordered_key(best) << 32) | (unsigned long long)(0xffffffffu - (unsigned)idx);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, key, o);
+    key = other > key ? other : key;
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) sc.u[warp] = key;
+  __syncthreads();
+  if (warp == 0) {
+    unsigned long long t = lane < (blockDim.x >> 5) ? sc.u[lane] : 0ull;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const unsigned long long other = __shfl_xor_sync(0xffffffffu, t, o);
+      t = other > t ? other : t;
+    }
+    if (lane == 0) sc.u[32] = t;
+  }
+  __syncthreads();
+  return (int)(0xffffffffu - (unsigned)(sc.u[32] & 0xffffffffull));
+}
+
+__global__ void __launch_bounds__(ST) argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int v) {
+  __shared__ BlockScratch sc;
+  const int b = blockIdx.x;
+  const int r = block_argmax(logits + (size_t)b * v, v, sc);
+  if (threadIdx.x == 0) out[b] = r;
+}
+
+__device__ __forceinline__ float uniform_from(unsigned long long seed, unsigned long long counter) {
+  unsigned long long z = seed + (counter + 1ull) * 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  z = z ^ (z >> 31);
+  return (float)(z >> 40) * (1.0f / 16777216.0f);
+}
+
+__global__ void __launch_bounds__(ST)
+sample_kernel(const float* __restrict__ logits, float* __restrict__ work, int v,
+              const float* __restrict__ temperature, const int* __restrict__ top_k,
+              const float* __restrict__ top_p, const unsigned long long* __restrict__ seeds,
+              const unsigned long long* __restrict__ counters, int* __restrict__ out) {
+  __shared__ BlockScratch sc;
+  __shared__ int s_choice, s_last;
+  const int b = blockIdx.x;
+  const float* row = logits + (size_t)b * v;
+  const float temp = temperature[b];
+  if (!(temp > 0.f)) {
+    const int r = block_argmax(row, v, sc);
+    if (threadIdx.x == 0) out[b] = r;
+    return;
+  }
+  float* x = work + (size_t)b * v;
+  const int k = top_k[b];
+  const float p = top_p[b];
+
+  // scaled logits and their maximum
+  float mx = -CUDART_INF_F;
+  for (int i = threadIdx.x; i < v; i += ST) {
+    const float s = row[i] / temp;
+    x[i] = s;
+    mx = fmaxf(mx, s);
+  }
+  mx = block_max_f(mx, sc);
+
+  // top-k: tau = ordered key of the k-th largest value
+  if (k > 0 && k < v) {
+    uint32_t tau = 0;
+    for (int bit = 31; bit >= 0; --bit) {
+      const uint32_t cand = tau | (1u << bit);
+      int cnt = 0;
+      for (int i = threadIdx.x; i < v; i += ST) cnt += ordered_key(x[i]) >= cand;
+      if (block_sum_i(cnt, sc) >= k) tau = cand;
+    }
+    int gt = 0;
+    for (int i = threadIdx.x; i < v; i += ST) gt += ordered_key(x[i]) > tau;
+    const int need = k - block_sum_i(gt, sc);   // how many of the values equal to tau stay
+    int base = 0;
+    for (int c0 = 0; c0 < v; c0 += ST) {
+      const int i = c0 + threadIdx.x;
+      const uint32_t key = i < v ? ordered_key(x[i]) : 0u;
+      const bool tie = i < v && key == tau;
+      int total;
+      const int rank = base + block_excl_scan_flag(tie, &total, sc);
+      if (i < v && (key < tau || (tie && rank >= need))) x[i] = -CUDART_INF_F;
+      base += total;
+    }
+  }
+
+  // weights e_i = exp(x_i - max) of the kept tokens, 0 for the dropped ones
+  float z = 0.f;
+  for (int i = threadIdx.x; i < v; i += ST) {
+    const float s = x[i];
+    const float e = s == -CUDART_INF_F ? 0.f : expf(s - mx);
+    x[i] = e;
+    z += e;
+  }
+  z = block_sum_f(z, sc);
+
+  // top-p: largest cut tau (as float bits, e >= 0) with sum(e_i < tau) <= (1 - p) z; tau <= bits(1.0f) keeps the maximum
+  if (p < 1.f) {
+    const float budget = (1.f - p) * z;
+    const uint32_t one = __float_as_uint(1.0f);
+    uint32_t tau = 0;
+    for (int bit = 30; bit >= 0; --bit) {
+      const uint32_t cand = tau | (1u << bit);
+      if (cand > one) continue;
+      float mass = 0.f;
+      for (int i = threadIdx.x; i < v; i += ST) {
+        const float e = x[i];
+        mass += __float_as_uint(e) < cand ? e : 0.f;
+      }
+      if (block_sum_f(mass, sc) <= budget) tau = cand;
+    }
+    float z2 = 0.f;
+    for (int i = threadIdx.x; i < v; i += ST) {
+      float e = x[i];
+      if (__float_as_uint(e) < tau) { e = 0.f; x[i] = 0.f; }
+      z2 += e;
+    }
+    z = block_sum_f(z2, sc);
+  }
+
+  // multinomial: first token id whose running weight exceeds u * z
+  const float target = uniform_from(seeds[b], counters[b]) * z;
+  if (threadIdx.x == 0) { s_choice = 0x7fffffff; s_last = -1; }
+  __syncthreads();
+  float base = 0.f;
+  for (int c0 = 0; c0 < v; c0 += ST) {
+    const int i = c0 + threadIdx.x;
+    const float e = i < v ? x[i] : 0.f;
+    float total;
+    const float incl = base + block_incl_scan_f(e, &total, sc);
+    if (e > 0.f) {
+      atomicMax(&s_last, i);
+      if (incl > target) atomicMin(&s_choice, i);
+    }
+    base += total;
+    __syncthreads();
+    if (s_choice != 0x7fffffff) break;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) out[b] = s_choice != 0x7fffffff ? s_choice : s_last;
+}
+
+}  // namespace tllm
+
+using namespace tllm;
+
+extern "C" int tllm_argmax(const float* logits, int* out, int n, int v, void* stream) {
+  TLLM_REQUIRE(n > 0 && v > 0, "argmax: empty input (%d rows of %d)", n, v);
+  argmax_kernel<<<n, ST, 0, (cudaStream_t)stream>>>(logits, out, v);
+  TLLM_CHECK_LAUNCH("argmax");
+  return TLLM_OK;
+}
+
+extern "C" int tllm_sample(const float* logits, float* work, int n, int v, const float* temperature, const int* top_k,
+                           const float* top_p, const unsigned long long* seeds, const unsigned long long* counters,
+                           int* out, void* stream) {
+  TLLM_REQUIRE(n > 0 && v > 0, "sample: empty input (%d rows of %d)", n, v);
+  TLLM_REQUIRE(work != nullptr, "sample: needs n*V floats of scratch");
+  sample_kernel<<<n, ST, 0, (cudaStream_t)stream>>>(logits, work, v, temperature, top_k, top_p, seeds, counters, out);
+  TLLM_CHECK_LAUNCH("sample");
+  return TLLM_OK;
+}

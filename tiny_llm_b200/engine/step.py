@@ -1,0 +1,251 @@
+"""The step function: one batch of (request, its next tokens) -- portions of prompts beside single
+decoded tokens, cut anywhere -- runs as ONE batch from the cache and returns the logits at the
+wanted places.
+
+The reference runs either whole prompts or one token per request, switched by a global flag, and
+rebuilds and uploads a block table per layer with a stream synchronisation each
+(tiny_llm/runtime/cuda/cuda_runtime.cpp:658-802).  Here every step's metadata is laid out in one
+pinned host buffer and goes to the device in one copy:
+
+  tokens[T] positions[T] token_request[T] | cu_q[R+1] q_start[R] kv_len[R] slot[R] | logit_rows[n]
+  | per cache group: slot_mapping[T], block_table[R, max_blocks]
+
+A token's position is the number of tokens its request held before it; key j is visible to it iff
+j <= position, whatever mix of portions and decoded tokens the batch has."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache import CacheManager
+from .workspace import Workspace
+
+
+class OutOfPages(RuntimeError):
+    """The cache cannot hold the step's new tokens; nothing was taken."""
+
+
+@dataclass
+class StepEntry:
+    rid: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()  # places among `tokens` whose logits are wanted
+
+
+@dataclass
+class KVView:
+    """What a mixer with a KVNeed gets: its entry's pages and the step's tables of its group."""
+    k: torch.Tensor              # [pages, kv_heads, page_size, head_dim]
+    v: torch.Tensor
+    block_table: torch.Tensor    # int32 [R, max_blocks], -1 where a page was given back
+    slot_mapping: torch.Tensor   # int32 [T]: page * page_size + offset of every token of the step
+    page_size: int
+
+
+@dataclass
+class StateView:
+    """What a mixer with a StateNeed gets: state[slot] is the request's state."""
+    state: torch.Tensor          # [max_slots, *shape]
+
+
+@dataclass
+class GroupMeta:
+    block_table: torch.Tensor
+    slot_mapping: torch.Tensor
+    max_blocks: int
+
+
+@dataclass
+class StepBatch:
+    num_tokens: int
+    num_requests: int
+    num_logits: int
+    tokens: torch.Tensor
+    positions: torch.Tensor
+    token_request: torch.Tensor
+    cu_q: torch.Tensor
+    q_start: torch.Tensor
+    kv_len: torch.Tensor
+    slots: torch.Tensor
+    logit_rows: torch.Tensor
+    groups: List[GroupMeta]
+    max_q_len: int
+    max_kv_len: int
+    # host copies for parts that plan on the host
+    host_q_lens: List[int] = field(default_factory=list)
+    host_kv_lens: List[int] = field(default_factory=list)
+
+
+class StepContext:
+    def __init__(self, runner: "ModelRunner", batch: StepBatch):
+        self.runner = runner
+        self.batch = batch
+        self.dtype = runner.dtype
+        self.device = runner.device
+        self.workspace = runner.workspace
+
+    def cache_view(self, order_pos: int):
+        ref = self.runner.cache.refs[order_pos]
+        if ref.group is not None:
+            g = self.runner.cache.groups[ref.group]
+            m = self.batch.groups[ref.group]
+            return KVView(g.kv[ref.entry, 0], g.kv[ref.entry, 1], m.block_table, m.slot_mapping, g.page_size)
+        if ref.state is not None:
+            return StateView(self.runner.cache.slots.tensors[ref.state])
+        return None
+
+
+class ModelRunner:
+    """Owns the model's device side: weights, cache storage, workspace, and the step function."""
+
+    def __init__(self, model, cache: CacheManager, dtype: torch.dtype, device,
+                 max_tokens_per_step: int = 8192, max_requests_per_step: int = 256):
+        if not model.loaded:
+            raise RuntimeError("the model has no weights yet")
+        self.model = model
+        self.cache = cache
+        self.dtype = dtype
+        self.device = torch.device(device)
+        self.max_tokens_per_step = max_tokens_per_step
+        self.max_requests_per_step = max_requests_per_step
+        self.workspace = Workspace(self.device)
+        self.max_blocks = -(-model.spec.max_positions // cache.page_size)
+        t, r, g = max_tokens_per_step, max_requests_per_step, len(cache.groups)
+        # fixed offsets (in int32 words) of every region of the metadata buffer
+        self._off = {}
+        cur = 0
+        for name, n in (("tokens", t), ("positions", t), ("token_request", t), ("cu_q", r + 1),
+                        ("q_start", r), ("kv_len", r), ("slots", r), ("logit_rows", t)):
+            self._off[name] = (cur, n)
+            cur += n
+        for gi in range(g):
+            self._off[f"slot_mapping{gi}"] = (cur, t)
+            cur += t
+        for gi in range(g):
+            self._off[f"block_table{gi}"] = (cur, r * self.max_blocks)
+            cur += r * self.max_blocks
+        self._meta_words = cur
+        pin = self.device.type == "cuda"
+        self._host_meta = torch.zeros(cur, dtype=torch.int32, pin_memory=pin)
+        self._host_np = self._host_meta.numpy()
+        self._dev_meta = torch.zeros(cur, dtype=torch.int32, device=self.device)
+        self.steps_run = 0
+
+    # ---- metadata
+    def _region(self, buf, name, n=None):
+        off, cap = self._off[name]
+        return buf[off: off + (cap if n is None else n)]
+
+    def build_batch(self, entries: Sequence[StepEntry]) -> StepBatch:
+        cache = self.cache
+        r = len(entries)
+        q_lens = [len(e.tokens) for e in entries]
+        t = sum(q_lens)
+        if r == 0 or t == 0:
+            raise ValueError("a step needs at least one request with at least one token")
+        if any(n == 0 for n in q_lens):
+            raise ValueError("every request of a step brings at least one token")
+        if t > self.max_tokens_per_step or r > self.max_requests_per_step:
+            raise ValueError(f"step of {t} tokens / {r} requests exceeds the runner's limits "
+                             f"({self.max_tokens_per_step} / {self.max_requests_per_step})")
+        if len({e.rid for e in entries}) != r:
+            raise ValueError("a request appears twice in one step")
+        starts = [cache.kv_len[e.rid] for e in entries]
+        for e, s, n in zip(entries, starts, q_lens):
+            if s + n > self.model.spec.max_positions:
+                raise ValueError(f"request {e.rid!r} would reach {s + n} tokens; the model's limit is "
+                                 f"{self.model.spec.max_positions}")
+        host = self._host_np
+        tok = self._region(host, "tokens", t)
+        pos = self._region(host, "positions", t)
+        req = self._region(host, "token_request", t)
+        cu = self._region(host, "cu_q", r + 1)
+        rows: List[int] = []
+        cur = 0
+        cu[0] = 0
+        vocab = self.model.spec.vocab_size
+        for i, (e, s, n) in enumerate(zip(entries, starts, q_lens)):
+            arr = np.asarray(e.tokens, dtype=np.int64)
+            if arr.min() < 0 or arr.max() >= vocab:
+                raise ValueError(f"request {e.rid!r}: token id outside [0, {vocab})")
+            tok[cur: cur + n] = arr
+            pos[cur: cur + n] = np.arange(s, s + n)
+            req[cur: cur + n] = i
+            for w in e.want:
+                if not 0 <= w < n:
+                    raise ValueError(f"request {e.rid!r}: wanted place {w} is outside its {n} tokens")
+                rows.append(cur + w)
+            cur += n
+            cu[i + 1] = cur
+        self._region(host, "q_start", r)[:] = starts
+        kv_after = [s + n for s, n in zip(starts, q_lens)]
+        self._region(host, "kv_len", r)[:] = kv_after
+        self._region(host, "slots", r)[:] = [cache.slot_of(e.rid) for e in entries]
+        n_out = len(rows)
+        if n_out:
+            self._region(host, "logit_rows", n_out)[:] = rows
+        max_blocks = self.max_blocks
+        used_words = self._off["logit_rows"][0] + self._off["logit_rows"][1]
+        group_hosts = []
+        for gi, g in enumerate(cache.groups):
+            sm = self._region(host, f"slot_mapping{gi}", t)
+            bt = self._region(host, f"block_table{gi}", r * max_blocks).reshape(r, max_blocks)
+            cur = 0
+            for i, (e, s, n) in enumerate(zip(entries, starts, q_lens)):
+                table = cache.block_table(gi, e.rid)
+                nb = len(table)
+                bt[i, :nb] = table
+                bt[i, nb:] = -1
+                p = np.arange(s, s + n)
+                pages = np.asarray(table, dtype=np.int64)[p // g.page_size]
+                if (pages < 0).any():
+                    raise RuntimeError(f"request {e.rid!r} writes into a page it has given back")
+                sm[cur: cur + n] = pages * g.page_size + p % g.page_size
+                cur += n
+            group_hosts.append((sm, bt))
+            used_words = self._off[f"block_table{gi}"][0] + r * max_blocks
+        # one copy, host to device
+        self._dev_meta[:used_words].copy_(self._host_meta[:used_words], non_blocking=True)
+        dev = self._dev_meta
+        groups = []
+        for gi in range(len(cache.groups)):
+            groups.append(GroupMeta(
+                block_table=self._region(dev, f"block_table{gi}", r * max_blocks).view(r, max_blocks),
+                slot_mapping=self._region(dev, f"slot_mapping{gi}", t), max_blocks=max_blocks))
+        return StepBatch(
+            num_tokens=t, num_requests=r, num_logits=n_out,
+            tokens=self._region(dev, "tokens", t), positions=self._region(dev, "positions", t),
+            token_request=self._region(dev, "token_request", t), cu_q=self._region(dev, "cu_q", r + 1),
+            q_start=self._region(dev, "q_start", r), kv_len=self._region(dev, "kv_len", r),
+            slots=self._region(dev, "slots", r), logit_rows=self._region(dev, "logit_rows", n_out),
+            groups=groups, max_q_len=max(q_lens), max_kv_len=max(kv_after),
+            host_q_lens=q_lens, host_kv_lens=kv_after)
+
+    # ---- the step
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Runs exactly the tokens it is given, as one batch, from the cache earlier steps left.
+        Returns float32 logits [number of wanted places, vocab] in the order of the entries and of
+        their `want` lists, or None if nothing is wanted.  The returned tensor is workspace memory:
+        it is valid until the next step."""
+        cache = self.cache
+        need = [0] * len(cache.groups)
+        for e in entries:
+            if not cache.has_request(e.rid):
+                raise KeyError(f"request {e.rid!r} is not live in the cache")
+            for gi, m in enumerate(cache.pages_missing(e.rid, len(e.tokens))):
+                need[gi] += m
+        if any(n > g.pool.num_free for n, g in zip(need, cache.groups)):
+            raise OutOfPages(f"the step needs {need} new pages per cache group, "
+                             f"free: {[g.pool.num_free for g in cache.groups]}")
+        for e in entries:
+            ok = cache.reserve(e.rid, len(e.tokens))
+            assert ok
+        batch = self.build_batch(entries)
+        logits = self.model.forward(StepContext(self, batch))
+        for e in entries:
+            cache.commit(e.rid, len(e.tokens))
+        self.steps_run += 1
+        return logits

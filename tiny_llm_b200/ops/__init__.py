@@ -1,0 +1,222 @@
+"""Python face of the sm_100a kernels.  Every op checks its tensors, picks the kernel for the
+dtype and sizes, and launches it on torch's current stream through the C entry points of the
+shared objects that `build.py` compiles from csrc/.  There is no other path: an op given a tensor
+that is not on a CUDA device, or called where the kernels cannot be built, raises."""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import build
+from .build import BuildError
+
+F32, BF16 = 0, 1
+OUT_SAME, OUT_F32, OUT_ACC = 0, 1, 2
+
+
+class KernelError(RuntimeError):
+    """A kernel refused its arguments (a size it is not built for) or failed to launch."""
+
+
+def _code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16, not {dtype}")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("the engine's ops run on a CUDA device only; got a tensor on " + str(t.device))
+
+
+def _check(lib, rc: int):
+    if rc != 0:
+        raise KernelError(lib.tllm_last_error().decode())
+
+
+def _i32(t: Optional[torch.Tensor], name: str):
+    if t is not None and (t.dtype != torch.int32 or not t.is_contiguous()):
+        raise KernelError(f"{name} must be a contiguous int32 tensor")
+
+
+# ----------------------------------------------------------------------------- elementwise
+
+
+def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, :] = table[tokens[t], :] as float32 (the residual stream is 32-bit)."""
+    _need_cuda(tokens, table, out)
+    _i32(tokens, "tokens")
+    t, h = out.shape
+    if out.dtype != torch.float32 or not out.is_contiguous() or not table.is_contiguous() or table.shape[1] != h \
+            or tokens.numel() != t:
+        raise KernelError("embedding: shapes or dtypes do not fit")
+    lib = build.load_library("elementwise")
+    _check(lib, lib.tllm_embedding(_ptr(tokens), _ptr(table), _ptr(out), t, h, _code(table.dtype), _stream()))
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+             rows: Optional[torch.Tensor] = None) -> None:
+    """out[r, :] = weight * x[rows[r], :] / sqrt(mean(x^2) + eps); x and weight are float32."""
+    _need_cuda(x, weight, out, rows)
+    _i32(rows, "rows")
+    h = x.shape[1]
+    n = out.shape[0]
+    if x.dtype != torch.float32 or weight.dtype != torch.float32 or not x.is_contiguous() or \
+            not out.is_contiguous() or out.shape[1] != h or weight.numel() != h or \
+            (rows is None and n != x.shape[0]) or (rows is not None and rows.numel() != n):
+        raise KernelError("rms_norm: shapes or dtypes do not fit")
+    lib = build.load_library("elementwise")
+    _check(lib, lib.tllm_rms_norm(_ptr(x), _ptr(weight), _ptr(out), _ptr(rows), n, h, ctypes.c_float(eps),
+                                  _code(out.dtype), _stream()))
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, block: int) -> None:
+    """out[m, g*block + j] = silu(gate_up[m, 2*g*block + j]) * gate_up[m, 2*g*block + block + j]."""
+    _need_cuda(gate_up, out)
+    m, inter = out.shape
+    if gate_up.shape != (m, 2 * inter) or gate_up.dtype != out.dtype or not gate_up.is_contiguous() or \
+            not out.is_contiguous():
+        raise KernelError("silu_mul: shapes or dtypes do not fit")
+    lib = build.load_library("elementwise")
+    _check(lib, lib.tllm_silu_mul(_ptr(gate_up), _ptr(out), m, inter, block, _code(out.dtype), _stream()))
+
+
+def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, cos: Optional[torch.Tensor],
+                  sin: Optional[torch.Tensor], rot_dim: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                  k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                  slot_mapping: Optional[torch.Tensor]) -> None:
+    """Rotates the queries of `qkv` in place; rotates the keys and writes keys and values into the
+    pages at slot_mapping (None: the row holds queries only and nothing is written)."""
+    _need_cuda(qkv, positions, cos, sin, k_cache, v_cache, slot_mapping)
+    _i32(positions, "positions")
+    _i32(slot_mapping, "slot_mapping")
+    t, width = qkv.shape
+    want = num_heads * head_dim + (0 if slot_mapping is None else 2 * num_kv_heads * head_dim)
+    if width != want or qkv.stride(1) != 1:
+        raise KernelError(f"rope_kv_write: rows of {width} values, expected {want}")
+    page_size = page_stride = head_stride = 0
+    if slot_mapping is not None:
+        if k_cache.dtype != qkv.dtype or v_cache.dtype != qkv.dtype or k_cache.shape != v_cache.shape or \
+                k_cache.stride() != v_cache.stride() or k_cache.stride(3) != 1 or k_cache.stride(2) != head_dim:
+            raise KernelError("rope_kv_write: cache layout does not fit")
+        page_size, page_stride, head_stride = k_cache.shape[2], k_cache.stride(0), k_cache.stride(1)
+    if cos is not None and (cos.dtype != torch.float32 or not cos.is_contiguous() or cos.shape[1] * 2 != rot_dim):
+        raise KernelError("rope_kv_write: rotary tables do not fit")
+    lib = build.load_library("elementwise")
+    _check(lib, lib.tllm_rope_kv_write(
+        _ptr(qkv), _ptr(positions), _ptr(cos), _ptr(sin), rot_dim, t, num_heads, num_kv_heads, head_dim,
+        qkv.stride(0), _ptr(k_cache if slot_mapping is not None else None),
+        _ptr(v_cache if slot_mapping is not None else None), _ptr(slot_mapping), page_size,
+        ctypes.c_longlong(page_stride), ctypes.c_longlong(head_stride), _code(qkv.dtype), _stream()))
+
+
+# ----------------------------------------------------------------------------- matrix products
+
+
+def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
+    """out = a . w^T (w is [N, K], rows contiguous).  `out` may be of a's dtype or float32;
+    accumulate=True adds the product into a float32 `out`."""
+    _need_cuda(a, w, out)
+    m, k = a.shape
+    n = w.shape[0]
+    if w.shape[1] != k or out.shape != (m, n) or a.dtype != w.dtype or a.stride(1) != 1 or \
+            out.stride(1) != 1 or not w.is_contiguous():
+        raise KernelError(f"linear: shapes or dtypes do not fit: a {tuple(a.shape)} {a.dtype}, "
+                          f"w {tuple(w.shape)} {w.dtype}, out {tuple(out.shape)} {out.dtype}")
+    if accumulate:
+        if out.dtype != torch.float32:
+            raise KernelError("linear: accumulation needs a float32 output")
+        mode = OUT_ACC
+    elif out.dtype == a.dtype:
+        mode = OUT_SAME
+    elif out.dtype == torch.float32:
+        mode = OUT_F32
+    else:
+        raise KernelError(f"linear: output dtype {out.dtype} does not fit input dtype {a.dtype}")
+    lib = build.load_library("linear_generic")
+    _check(lib, lib.tllm_linear_generic(_ptr(a), _ptr(w), _ptr(out), m, n, k, a.stride(0), out.stride(0),
+                                        _code(a.dtype), mode, _stream()))
+
+
+def linear_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, block: int, workspace) -> None:
+    """out = silu(a Wg^T) * (a Wu^T) with Wg, Wu interleaved in `w_gate_up` in row blocks of `block`."""
+    m = a.shape[0]
+    gu = workspace.get("gate_up", (m, w_gate_up.shape[0]), a.dtype)
+    linear(a, w_gate_up, gu)
+    silu_mul(gu, out, block)
+
+
+# ----------------------------------------------------------------------------- attention
+
+
+def paged_attention(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, k_cache: torch.Tensor,
+                    v_cache: torch.Tensor, block_table: torch.Tensor, batch, out: torch.Tensor, scale: float,
+                    window: Optional[int] = None) -> None:
+    """Attention of every token of the step (queries in the first num_heads*head_dim values of each
+    `qkv` row) over its request's pages.  `batch` carries token_request and positions."""
+    _need_cuda(qkv, k_cache, v_cache, block_table, out)
+    _i32(block_table, "block_table")
+    t = qkv.shape[0]
+    if out.shape != (t, num_heads * head_dim) or not out.is_contiguous() or out.dtype != qkv.dtype or \
+            k_cache.dtype != qkv.dtype or k_cache.stride() != v_cache.stride() or k_cache.stride(3) != 1 or \
+            k_cache.stride(2) != head_dim or k_cache.shape[1] != num_kv_heads or k_cache.shape[3] != head_dim:
+        raise KernelError("paged_attention: shapes or dtypes do not fit")
+    lib = build.load_library("attention_generic")
+    _check(lib, lib.tllm_paged_attention_generic(
+        _ptr(qkv), qkv.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
+        _ptr(batch.token_request), _ptr(batch.positions), _ptr(out), t, num_heads, num_kv_heads, head_dim,
+        k_cache.shape[2], ctypes.c_longlong(k_cache.stride(0)), ctypes.c_longlong(k_cache.stride(1)),
+        ctypes.c_float(scale), int(window or 0), _code(qkv.dtype), _stream()))
+
+
+# ----------------------------------------------------------------------------- sampling
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    _need_cuda(logits, out)
+    _i32(out, "out")
+    n, v = logits.shape
+    if logits.dtype != torch.float32 or not logits.is_contiguous() or out.numel() != n:
+        raise KernelError("argmax: logits must be contiguous float32 [n, V] and out int32 [n]")
+    lib = build.load_library("sampling")
+    _check(lib, lib.tllm_argmax(_ptr(logits), _ptr(out), n, v, _stream()))
+
+
+def sample(logits: torch.Tensor, work: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
+           top_p: torch.Tensor, seeds: torch.Tensor, counters: torch.Tensor, out: torch.Tensor) -> None:
+    """Temperature -> top-k -> top-p -> multinomial per row; rows with temperature <= 0 are greedy.
+    `work` is float32 scratch of at least n*V elements; seeds and counters are int64 (read as
+    unsigned 64-bit)."""
+    _need_cuda(logits, work, temperature, top_k, top_p, seeds, counters, out)
+    _i32(top_k, "top_k")
+    _i32(out, "out")
+    n, v = logits.shape
+    if logits.dtype != torch.float32 or not logits.is_contiguous() or work.dtype != torch.float32 or \
+            work.numel() < n * v or temperature.dtype != torch.float32 or top_p.dtype != torch.float32 or \
+            seeds.dtype != torch.int64 or counters.dtype != torch.int64 or \
+            any(x.numel() != n for x in (temperature, top_k, top_p, seeds, counters, out)):
+        raise KernelError("sample: shapes or dtypes do not fit")
+    lib = build.load_library("sampling")
+    _check(lib, lib.tllm_sample(_ptr(logits), _ptr(work), n, v, _ptr(temperature), _ptr(top_k), _ptr(top_p),
+                                _ptr(seeds), _ptr(counters), _ptr(out), _stream()))
+
+
+ALL_LIBRARIES = ("elementwise", "linear_generic", "attention_generic", "sampling")
+
+
+def build_all(verbose: bool = True):
+    """Compiles every library (what `__graft_entry__.build()` calls); returns their paths."""
+    return [build.compile_library(n, verbose=verbose) for n in ALL_LIBRARIES]
