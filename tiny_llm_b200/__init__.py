@@ -8,6 +8,8 @@ engine/    the step function, the scheduler and the generate loop
 sampling/  greedy, temperature, top-k, top-p
 ops/       Python face of the kernels; csrc/ holds their CUDA sources
 """
-from . import config, weights, cache, parts, engine  # noqa: F401
+from . import config, weights, cache, parts, sampling, engine  # noqa: F401
+from .engine import Pipeline
+from .sampling import SamplingParams
 
 __version__ = "0.1.0"

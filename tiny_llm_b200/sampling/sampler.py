@@ -1,0 +1,65 @@
+"""Chooses next tokens on the device from the step's 32-bit logits.  The reference copies the
+logits to the host and runs its processor chain there (tiny_llm/pipeline/pipeline.cpp:193-207)."""
+from __future__ import annotations
+
+from typing import List, Sequence
+
+import numpy as np
+import torch
+
+from .. import ops
+from .params import SamplingParams
+
+
+def uniform_from(seed: int, counter: int) -> float:
+    """The uniform number in [0, 1) the sampling kernel draws for (seed, counter): splitmix64 of
+    seed + (counter + 1) * golden ratio, top 24 bits."""
+    mask = (1 << 64) - 1
+    z = (seed + (counter + 1) * 0x9E3779B97F4A7C15) & mask
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & mask
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & mask
+    z = z ^ (z >> 31)
+    return (z >> 40) / 16777216.0
+
+
+class Sampler:
+    def __init__(self, device, vocab_size: int, max_rows: int = 256):
+        self.device = torch.device(device)
+        self.vocab_size = vocab_size
+        self.max_rows = max_rows
+        pin = self.device.type == "cuda"
+        # one host block: temperature f32 | top_p f32 | top_k i32 | seeds i64 | counters i64, as int32 words
+        self._words = max_rows * 7
+        self._host = torch.zeros(self._words, dtype=torch.int32, pin_memory=pin)
+        self._dev = torch.zeros(self._words, dtype=torch.int32, device=self.device)
+        self._out = torch.zeros(max_rows, dtype=torch.int32, device=self.device)
+        self._out_host = torch.zeros(max_rows, dtype=torch.int32, pin_memory=pin)
+        self._work = None
+
+    def _views(self, buf, n):
+        m = self.max_rows
+        return (buf[0:n].view(torch.float32), buf[m:m + n].view(torch.float32), buf[2 * m:2 * m + n],
+                buf[3 * m:3 * m + 2 * n].view(torch.int64), buf[5 * m:5 * m + 2 * n].view(torch.int64))
+
+    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], counters: Sequence[int]) -> List[int]:
+        """One token per row of `logits`; `counters[i]` is how many tokens row i's request has drawn."""
+        n = logits.shape[0]
+        if n > self.max_rows:
+            raise ValueError(f"{n} rows exceed the sampler's {self.max_rows}")
+        out = self._out[:n]
+        if all(not p.do_sample for p in params):
+            ops.argmax(logits, out)
+        else:
+            t, pp, k, s, c = self._views(self._host, n)
+            t.numpy()[:] = [p.temperature if p.do_sample else 0.0 for p in params]
+            pp.numpy()[:] = [p.top_p for p in params]
+            k.numpy()[:] = [p.top_k for p in params]
+            s.numpy()[:] = np.array([p.seed & 0x7FFFFFFFFFFFFFFF for p in params], dtype=np.int64)
+            c.numpy()[:] = np.array(list(counters), dtype=np.int64)
+            self._dev.copy_(self._host, non_blocking=True)
+            if self._work is None or self._work.numel() < n * self.vocab_size:
+                self._work = torch.empty(max(n, 8) * self.vocab_size, dtype=torch.float32, device=self.device)
+            dt, dpp, dk, ds, dc = self._views(self._dev, n)
+            ops.sample(logits, self._work, dt, dk, dpp, ds, dc, out)
+        self._out_host[:n].copy_(out, non_blocking=False)
+        return self._out_host[:n].tolist()
