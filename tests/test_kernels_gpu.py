@@ -1,0 +1,265 @@
+"""Each kernel alone against a plain 32-bit reference of the same op, at sizes other than the
+engine's (odd ones, as tiny-llm's own tests use: 107, 127, 241, 255, 353)."""
+import math
+import types
+
+import pytest
+import torch
+
+import plain_llama as pl
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def tol(dtype, scale=1.0):
+    return (2e-5 if dtype == "float32" else 2.0 ** -7) * scale
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from tiny_llm_b200 import ops
+    return ops
+
+
+@pytest.mark.parametrize("dtype", DT)
+def test_embedding(ops, dtype):
+    torch.manual_seed(0)
+    table = torch.randn(331, 241).to(DT[dtype])
+    toks = torch.randint(0, 331, (57,), dtype=torch.int32)
+    out = torch.empty(57, 241, device=DEV)
+    ops.embedding(toks.to(DEV), table.to(DEV), out)
+    assert torch.equal(out.cpu(), pl.embedding(table.float(), toks))
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("rows,width,eps", [(107, 241, 1.192e-7), (5, 4096 + 48, 1e-5), (3, 16, 1e-6)])
+def test_rms_norm(ops, dtype, rows, width, eps):
+    torch.manual_seed(1)
+    x = torch.randn(rows, width) * 3
+    w = torch.randn(width)
+    out = torch.empty(rows, width, dtype=DT[dtype], device=DEV)
+    ops.rms_norm(x.to(DEV), w.to(DEV), eps, out)
+    ref = pl.rms_norm(x, w, eps)
+    assert float((out.float().cpu() - ref).abs().max()) <= tol(dtype, float(ref.abs().max()))
+    pick = torch.tensor([rows - 1, 0, rows // 2], dtype=torch.int32)
+    out2 = torch.empty(3, width, dtype=DT[dtype], device=DEV)
+    ops.rms_norm(x.to(DEV), w.to(DEV), eps, out2, pick.to(DEV))
+    assert torch.equal(out2.cpu(), out.cpu()[pick.long()])
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("m,n,k", [(127, 353, 255), (1, 331, 80), (64, 64, 16), (200, 40, 1000), (3, 2, 1)])
+def test_linear(ops, dtype, m, n, k):
+    torch.manual_seed(2)
+    a = torch.randn(m, k).to(DT[dtype])
+    w = torch.randn(n, k).to(DT[dtype])
+    ref = pl.linear(a.float().double(), w.float().double()).float()
+    scale = float(ref.abs().max())
+    same = torch.empty(m, n, dtype=DT[dtype], device=DEV)
+    ops.linear(a.to(DEV), w.to(DEV), same)
+    assert float((same.float().cpu() - ref).abs().max()) <= tol(dtype, scale)
+    f32 = torch.empty(m, n, device=DEV)
+    ops.linear(a.to(DEV), w.to(DEV), f32)
+    assert float((f32.cpu() - ref).abs().max()) <= 2e-5 * max(scale, 1)    # 32-bit accumulation in both paths
+    acc = torch.full((m, n), 0.5, device=DEV)
+    ops.linear(a.to(DEV), w.to(DEV), acc, accumulate=True)
+    assert float((acc.cpu() - ref - 0.5).abs().max()) <= 2e-5 * max(scale, 1)
+    # a strided input (rows of a wider buffer) and a row's result that does not depend on its batch
+    wide = torch.randn(m, k + 24).to(DT[dtype]).to(DEV)
+    wide[:, :k] = a.to(DEV)
+    out2 = torch.empty(m, n, device=DEV)
+    ops.linear(wide[:, :k], w.to(DEV), out2)
+    assert torch.equal(out2, f32)
+    one = torch.empty(1, n, device=DEV)
+    ops.linear(a[m // 2: m // 2 + 1].to(DEV), w.to(DEV), one)
+    assert torch.equal(one[0], f32[m // 2])
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("m,inter,block", [(37, 176, 16), (5, 208, 16), (3, 5632, 128), (9, 7, 1)])
+def test_silu_mul(ops, dtype, m, inter, block):
+    from tiny_llm_b200.parts import interleave_gate_up
+    torch.manual_seed(3)
+    gate, up = torch.randn(m, inter).to(DT[dtype]), torch.randn(m, inter).to(DT[dtype])
+    gu = interleave_gate_up(gate.t().contiguous(), up.t().contiguous(), block).t().contiguous()   # columns interleaved
+    out = torch.empty(m, inter, dtype=DT[dtype], device=DEV)
+    ops.silu_mul(gu.to(DEV), out, block)
+    ref = pl.silu(gate.float()) * up.float()
+    assert float((out.float().cpu() - ref).abs().max()) <= tol(dtype, float(ref.abs().max()))
+
+
+def paged_setup(dtype, n_req, lens, nkv, hd, page, seed, spare_pages=3):
+    """Random keys/values for n_req sequences scattered over shuffled pages; unwritten slots are NaN."""
+    g = torch.Generator().manual_seed(seed)
+    blocks = [-(-l // page) for l in lens]
+    n_pages = sum(blocks) + spare_pages
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    max_blocks = max(blocks) + 2
+    table = torch.full((n_req, max_blocks), -1, dtype=torch.int32)
+    k_cache = torch.full((n_pages, nkv, page, hd), float("nan"), dtype=DT[dtype])
+    v_cache = torch.full((n_pages, nkv, page, hd), float("nan"), dtype=DT[dtype])
+    ks, vs = [], []
+    for r, l in enumerate(lens):
+        k = torch.randn(l, nkv, hd, generator=g).to(DT[dtype])
+        v = torch.randn(l, nkv, hd, generator=g).to(DT[dtype])
+        ks.append(k), vs.append(v)
+        for b in range(blocks[r]):
+            pg = perm.pop()
+            table[r, b] = pg
+            n = min(page, l - b * page)
+            k_cache[pg, :, :n] = k[b * page: b * page + n].permute(1, 0, 2)
+            v_cache[pg, :, :n] = v[b * page: b * page + n].permute(1, 0, 2)
+    return table, k_cache, v_cache, ks, vs
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("nq,nkv,hd,page,window", [(6, 3, 48, 8, None), (4, 1, 80, 16, None), (5, 5, 128, 32, None),
+                                                    (2, 2, 256, 4, None), (8, 2, 16, 16, 37), (3, 1, 64, 8, 8)])
+def test_paged_attention(ops, dtype, nq, nkv, hd, page, window):
+    """Queries at the end of sequences of different lengths: some portions, some single tokens."""
+    lens = [301, 64, 7, 130]
+    q_lens = [5, 1, 7, 33]
+    table, k_cache, v_cache, ks, vs = paged_setup(dtype, 4, lens, nkv, hd, page, seed=nq * hd)
+    g = torch.Generator().manual_seed(7)
+    t = sum(q_lens)
+    width = (nq + 2 * nkv) * hd
+    qkv = torch.randn(t, width, generator=g).to(DT[dtype])
+    # a far key among hundreds: request 0's first query and its key 3 are scaled so that this score stands out
+    qkv[0, :hd] *= 6.0
+    ks[0][3, 0] = (qkv[0, :hd] / qkv[0, :hd].float().norm() * 8.0).to(DT[dtype])
+    pg = int(table[0, 0])
+    k_cache[pg, 0, 3] = ks[0][3, 0]
+    tok_req = torch.cat([torch.full((n,), r, dtype=torch.int32) for r, n in enumerate(q_lens)])
+    pos = torch.cat([torch.arange(l - n, l, dtype=torch.int32) for l, n in zip(lens, q_lens)])
+    batch = types.SimpleNamespace(token_request=tok_req.to(DEV), positions=pos.to(DEV))
+    out = torch.empty(t, nq * hd, dtype=DT[dtype], device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    ops.paged_attention(qkv.to(DEV), nq, nkv, hd, k_cache.to(DEV), v_cache.to(DEV), table.to(DEV), batch, out,
+                        scale, window)
+    out = out.float().cpu()
+    assert not torch.isnan(out).any()
+    cur = 0
+    for r, (l, n) in enumerate(zip(lens, q_lens)):
+        q = qkv[cur: cur + n, : nq * hd].float().view(n, nq, hd)
+        ref = pl.attention(q, ks[r].float(), vs[r].float(), pos[cur: cur + n], window=window).reshape(n, nq * hd)
+        d = float((out[cur: cur + n] - ref).abs().max())
+        assert d <= tol(dtype, max(1.0, float(ref.abs().max()))), (r, d)
+        cur += n
+    if window is None:   # the far key carries the first query's first head
+        p = torch.softmax((qkv[0, :hd].float() * scale) @ ks[0][:lens[0] - q_lens[0] + 1, 0].float().t(), 0)
+        assert float(p[3]) > 0.9
+
+
+def test_attention_refuses_sizes_it_is_not_built_for(ops):
+    from tiny_llm_b200.ops import KernelError
+    batch = types.SimpleNamespace(token_request=torch.zeros(1, dtype=torch.int32, device=DEV),
+                                  positions=torch.zeros(1, dtype=torch.int32, device=DEV))
+    for hd in (24, 272):
+        kc = torch.zeros(2, 1, 4, hd, device=DEV)
+        with pytest.raises(KernelError, match="head size"):
+            ops.paged_attention(torch.zeros(1, 3 * hd, device=DEV), 1, 1, hd, kc, kc.clone(),
+                                torch.zeros(1, 2, dtype=torch.int32, device=DEV), batch,
+                                torch.zeros(1, hd, device=DEV), 1.0)
+    with pytest.raises(KernelError, match="CUDA"):
+        ops.rms_norm(torch.zeros(2, 4), torch.zeros(4), 1e-5, torch.zeros(2, 4))
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("nq,nkv,hd,page", [(6, 3, 48, 8), (4, 1, 128, 16), (2, 2, 16, 4)])
+def test_rope_kv_write(ops, dtype, nq, nkv, hd, page):
+    torch.manual_seed(5)
+    t, n_pages, max_pos = 23, 9, 77
+    cos, sin = pl.rope_tables(max_pos, hd, 5000.0)
+    qkv = torch.randn(t, (nq + 2 * nkv) * hd).to(DT[dtype])
+    pos = torch.randint(0, max_pos, (t,), dtype=torch.int32)
+    slots = torch.randperm(n_pages * page)[:t].to(torch.int32)
+    kc = torch.zeros(n_pages, nkv, page, hd, dtype=DT[dtype], device=DEV)
+    vc = torch.zeros_like(kc)
+    dev = qkv.to(DEV)
+    ops.rope_kv_write(dev, pos.to(DEV), cos.to(DEV), sin.to(DEV), hd, nq, nkv, hd, kc, vc, slots.to(DEV))
+    q_ref = pl.apply_rope(qkv[:, : nq * hd].float().view(t, nq, hd), cos, sin, pos)
+    k_ref = pl.apply_rope(qkv[:, nq * hd: (nq + nkv) * hd].float().view(t, nkv, hd), cos, sin, pos)
+    v_ref = qkv[:, (nq + nkv) * hd:].view(t, nkv, hd)
+    e = tol(dtype, 4.0)
+    assert float((dev[:, : nq * hd].float().cpu().view(t, nq, hd) - q_ref).abs().max()) <= e
+    assert torch.equal(dev[:, nq * hd:].cpu(), qkv[:, nq * hd:])           # keys and values of the row stay
+    kc, vc = kc.cpu(), vc.cpu()
+    for i in range(t):
+        pg, off = int(slots[i]) // page, int(slots[i]) % page
+        assert float((kc[pg, :, off].float() - k_ref[i]).abs().max()) <= e
+        assert torch.equal(vc[pg, :, off], v_ref[i])
+    written = torch.zeros(n_pages * page, dtype=torch.bool)
+    written[slots.long()] = True
+    assert float(kc.permute(0, 2, 1, 3).reshape(n_pages * page, -1)[~written].abs().sum()) == 0   # nothing else touched
+    # queries only, no tables: nothing rotates, nothing is written
+    q_only = torch.randn(t, nq * hd).to(DT[dtype])
+    dev2 = q_only.to(DEV)
+    ops.rope_kv_write(dev2, pos.to(DEV), None, None, 0, nq, nkv, hd, None, None, None)
+    assert torch.equal(dev2.cpu(), q_only)
+
+
+def test_argmax_takes_the_first_maximum(ops):
+    torch.manual_seed(6)
+    logits = torch.randn(5, 1337)
+    logits[1, 700] = logits[1, 20] = 9.0
+    logits[2, :] = 0.25
+    logits[3, 1336] = 50.0
+    out = torch.empty(5, dtype=torch.int32, device=DEV)
+    ops.argmax(logits.to(DEV), out)
+    assert out.cpu().tolist() == [pl.greedy(r) for r in logits] and out[1] == 20 and out[2] == 0
+
+
+@pytest.mark.parametrize("vocab", [331, 32000])
+def test_sample_follows_the_reference_chain(ops, vocab):
+    from tiny_llm_b200.sampling import uniform_from
+    torch.manual_seed(8)
+    cases = [(1.0, 0, 1.0), (0.7, 50, 0.95), (0.8, 0, 0.5), (1.3, 5, 1.0), (0.5, 1, 1.0), (2.0, 40, 0.1), (0.0, 50, 0.95)]
+    n = len(cases) * 6
+    logits = torch.randn(n, vocab) * 3
+    temps = torch.tensor([c[0] for c in cases] * 6)
+    ks = torch.tensor([c[1] for c in cases] * 6, dtype=torch.int32)
+    ps = torch.tensor([c[2] for c in cases] * 6)
+    seeds = torch.arange(n, dtype=torch.int64) * 7919 + 3
+    counters = torch.arange(n, dtype=torch.int64) % 5
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    work = torch.empty(n * vocab, device=DEV)
+    ops.sample(logits.to(DEV), work, temps.to(DEV), ks.to(DEV), ps.to(DEV), seeds.to(DEV), counters.to(DEV), out)
+    out = out.cpu().tolist()
+    for i in range(n):
+        if temps[i] <= 0:
+            assert out[i] == pl.greedy(logits[i])
+            continue
+        ids, p = pl.sampling_distribution(logits[i], float(temps[i]), int(ks[i]), float(ps[i]))
+        u = uniform_from(int(seeds[i]), int(counters[i]))
+        want = pl.multinomial(ids, p, u)
+        if out[i] != want:
+            # only a draw within rounding of a boundary of the running sum may land on the neighbour
+            cdf = torch.cumsum(p, 0)
+            j = ids.tolist().index(out[i]) if out[i] in ids.tolist() else -1
+            assert j >= 0, (i, "a dropped token was drawn")
+            lo = float(cdf[j - 1]) if j else 0.0
+            assert lo - 1e-5 <= u <= float(cdf[j]) + 1e-5, (i, out[i], want)
+        assert out[i] in ids.tolist()
+    # the draw depends on (seed, counter) only: the same rows in another order and batch give the same tokens
+    perm = torch.randperm(n)
+    out2 = torch.empty(n, dtype=torch.int32, device=DEV)
+    ops.sample(logits[perm].to(DEV), work, temps[perm].to(DEV), ks[perm].to(DEV), ps[perm].to(DEV),
+               seeds[perm].to(DEV), counters[perm].to(DEV), out2)
+    assert out2.cpu().tolist() == [out[int(j)] for j in perm]
+
+
+def test_sample_top_k_keeps_exactly_k_with_ties(ops):
+    logits = torch.zeros(1, 64)
+    logits[0, [5, 9, 30]] = 4.0      # three tie for two places: the lowest ids stay
+    logits[0, 50] = 6.0
+    draws = set()
+    work = torch.empty(64, device=DEV)
+    out = torch.empty(1, dtype=torch.int32, device=DEV)
+    for c in range(200):
+        ops.sample(logits.to(DEV), work, torch.tensor([1.0], device=DEV), torch.tensor([3], dtype=torch.int32, device=DEV),
+                   torch.tensor([1.0], device=DEV), torch.tensor([11], dtype=torch.int64, device=DEV),
+                   torch.tensor([c], dtype=torch.int64, device=DEV), out)
+        draws.add(int(out[0]))
+    assert draws == {5, 9, 50}

@@ -1,0 +1,115 @@
+"""Replay on the GPU against the plain implementation, in 32-bit and in bfloat16: whole; most in one
+step and the last 32 tokens one by one; portions of changing size; mixed with few pages."""
+import pytest
+import torch
+
+import replay_util as ru
+from conftest import TINY
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"A": [100, 64, 33, 47, 128, 17, 80, 51], "B": [97, 2, 40, 255, 33, 64, 13, 150], "C": [70, 192, 35, 49]}
+DTYPES = ["float32", "bfloat16"]
+
+
+@pytest.fixture(scope="module")
+def cases(model_dirs):
+    out = {}
+    for name, (cfg, page, seed) in TINY.items():
+        reqs = ru.make_requests(cfg["vocab_size"], LENGTHS[name], seed + 10)
+        out[name] = (model_dirs[name], cfg, page, reqs, {d: ru.plain_logits(model_dirs[name], reqs, d) for d in DTYPES})
+    return out
+
+
+def runner_for(model_dir, dtype, page, max_tokens, poison=True):
+    from tiny_llm_b200.engine import load_model, make_runner
+    _, model = load_model(model_dir, dtype, "cuda:0")
+    runner = make_runner(model, dtype, "cuda:0", max_tokens=max_tokens, page_size=page, max_requests=8,
+                         max_tokens_per_step=1024)
+    if poison:  # a slot that is read before it is written shows as NaN in the logits
+        for g in runner.cache.groups:
+            g.kv.fill_(float("nan"))
+    return runner
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_trace_run_program(cases, name, dtype):
+    """All four ways of cutting, through bin/trace_run as a user runs it, with the smallest pool."""
+    model_dir, cfg, page, reqs, ref = cases[name]
+    some = dict(list(reqs.items())[:5])
+    steps = (ru.trace_whole(some) + ru.trace_tail(some) + ru.trace_portions(some, 1) + ru.trace_mixed(reqs, 2))
+    got = ru.run_trace_cli(model_dir, dtype, steps, cfg["vocab_size"])
+    ref_some = {k: ref[dtype][k] for k in some}
+    ru.compare(got, ref_some, "w", dtype, "whole")
+    ru.compare(got, ref_some, "t", dtype, "last 32 one by one")
+    ru.compare(got, ref_some, "p", dtype, "portions")
+    ru.compare(got, ref[dtype], "m", dtype, "mixed")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("how", ["whole", "tail", "portions", "mixed"])
+def test_replay_in_process(cases, name, dtype, how):
+    model_dir, cfg, page, reqs, ref = cases[name]
+    steps, prefix = {"whole": (ru.trace_whole(reqs), "w"), "tail": (ru.trace_tail(reqs), "t"),
+                     "portions": (ru.trace_portions(reqs, 3), "p"), "mixed": (ru.trace_mixed(reqs, 4), "m")}[how]
+    runner = runner_for(model_dir, dtype, page, ru.tokens_needed(steps, round_to=page))
+    got = ru.run_trace_runner(runner, steps, cfg["vocab_size"])
+    ru.compare(got, ref[dtype], prefix, dtype, how)
+    assert all(g.pool.num_used == 0 for g in runner.cache.groups)
+    if how == "mixed":   # so few pages that they were used again
+        total = sum(-(-len(t) // page) for t in reqs.values())
+        assert total > runner.cache.groups[0].pool.num_pages
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_mixed_twice_with_different_pages_gives_the_same_logits(cases, name, dtype):
+    """The same trace with another page size and a larger pool: beyond rounding nothing moves."""
+    model_dir, cfg, page, reqs, ref = cases[name]
+    steps = ru.trace_mixed(reqs, 7)
+    a = ru.run_trace_runner(runner_for(model_dir, dtype, page, ru.tokens_needed(steps, page)), steps, cfg["vocab_size"])
+    b = ru.run_trace_runner(runner_for(model_dir, dtype, 4 * page, 4096), steps, cfg["vocab_size"])
+    for rid in a:
+        tol = 1e-6 if dtype == "float32" else ru.tolerance(a[rid], dtype)
+        assert float((a[rid] - b[rid]).abs().max()) <= tol, rid
+    if dtype == "float32":   # the 32-bit path orders its sums by position only: cuts do not move a bit
+        whole = ru.run_trace_runner(runner_for(model_dir, dtype, page, 4096), ru.trace_whole(reqs), cfg["vocab_size"])
+        for rid in reqs:
+            assert torch.equal(whole["w" + rid], a["m" + rid]), rid
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_long_decoding_and_first_tokens(cases, name, dtype):
+    model_dir, cfg, page, _, _ = cases[name]
+    n = cfg["max_position_embeddings"]
+    reqs = ru.make_requests(cfg["vocab_size"], [n, 1, 2, 3], 99)
+    ref = ru.plain_logits(model_dir, reqs, dtype)
+    # r0: one prompt token, then every further token one by one up to the model's last position
+    steps = ru.trace_tail({"r0": reqs["r0"]}, tail=n - 1) + ru.trace_whole({k: reqs[k] for k in ("r1", "r2", "r3")})
+    runner = runner_for(model_dir, dtype, page, ru.tokens_needed(steps, page))
+    got = ru.run_trace_runner(runner, steps, cfg["vocab_size"])
+    ru.compare(got, {"r0": ref["r0"]}, "t", dtype, "long decoding")
+    ru.compare(got, {k: ref[k] for k in ("r1", "r2", "r3")}, "w", dtype, "first tokens")
+    with pytest.raises(ValueError, match="limit"):
+        runner.cache.add_request("x")
+        from tiny_llm_b200.engine import StepEntry
+        runner.step([StepEntry("x", [1] * (n + 1), [])])
+
+
+def test_step_refuses_what_it_cannot_hold(cases):
+    from tiny_llm_b200.engine import OutOfPages, StepEntry
+    model_dir, cfg, page, _, _ = cases["A"]
+    runner = runner_for(model_dir, "float32", page, 32)
+    runner.cache.add_request("a"), runner.cache.add_request("b")
+    runner.step([StepEntry("a", [1] * 20, [])])
+    free = runner.cache.groups[0].pool.num_free
+    with pytest.raises(OutOfPages):
+        runner.step([StepEntry("a", [1], []), StepEntry("b", [1] * 17, [0])])
+    assert runner.cache.groups[0].pool.num_free == free      # nothing was taken
+    with pytest.raises(ValueError, match="token id"):
+        runner.step([StepEntry("b", [cfg["vocab_size"]], [0])])
+    with pytest.raises(KeyError):
+        runner.step([StepEntry("nobody", [1], [0])])

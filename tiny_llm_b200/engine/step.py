@@ -139,7 +139,8 @@ class ModelRunner:
         off, cap = self._off[name]
         return buf[off: off + (cap if n is None else n)]
 
-    def build_batch(self, entries: Sequence[StepEntry]) -> StepBatch:
+    def validate(self, entries: Sequence[StepEntry]) -> None:
+        """Everything that can be wrong with a step is found before a page is taken."""
         cache = self.cache
         r = len(entries)
         q_lens = [len(e.tokens) for e in entries]
@@ -153,11 +154,26 @@ class ModelRunner:
                              f"({self.max_tokens_per_step} / {self.max_requests_per_step})")
         if len({e.rid for e in entries}) != r:
             raise ValueError("a request appears twice in one step")
-        starts = [cache.kv_len[e.rid] for e in entries]
-        for e, s, n in zip(entries, starts, q_lens):
+        vocab = self.model.spec.vocab_size
+        for e, n in zip(entries, q_lens):
+            if not cache.has_request(e.rid):
+                raise KeyError(f"request {e.rid!r} is not live in the cache")
+            s = cache.kv_len[e.rid]
             if s + n > self.model.spec.max_positions:
                 raise ValueError(f"request {e.rid!r} would reach {s + n} tokens; the model's limit is "
                                  f"{self.model.spec.max_positions}")
+            if min(e.tokens) < 0 or max(e.tokens) >= vocab:
+                raise ValueError(f"request {e.rid!r}: token id outside [0, {vocab})")
+            for w in e.want:
+                if not 0 <= w < n:
+                    raise ValueError(f"request {e.rid!r}: wanted place {w} is outside its {n} tokens")
+
+    def build_batch(self, entries: Sequence[StepEntry]) -> StepBatch:
+        cache = self.cache
+        r = len(entries)
+        q_lens = [len(e.tokens) for e in entries]
+        t = sum(q_lens)
+        starts = [cache.kv_len[e.rid] for e in entries]
         host = self._host_np
         tok = self._region(host, "tokens", t)
         pos = self._region(host, "positions", t)
@@ -166,18 +182,11 @@ class ModelRunner:
         rows: List[int] = []
         cur = 0
         cu[0] = 0
-        vocab = self.model.spec.vocab_size
         for i, (e, s, n) in enumerate(zip(entries, starts, q_lens)):
-            arr = np.asarray(e.tokens, dtype=np.int64)
-            if arr.min() < 0 or arr.max() >= vocab:
-                raise ValueError(f"request {e.rid!r}: token id outside [0, {vocab})")
-            tok[cur: cur + n] = arr
+            tok[cur: cur + n] = np.asarray(e.tokens, dtype=np.int64)
             pos[cur: cur + n] = np.arange(s, s + n)
             req[cur: cur + n] = i
-            for w in e.want:
-                if not 0 <= w < n:
-                    raise ValueError(f"request {e.rid!r}: wanted place {w} is outside its {n} tokens")
-                rows.append(cur + w)
+            rows.extend(cur + w for w in e.want)
             cur += n
             cu[i + 1] = cur
         self._region(host, "q_start", r)[:] = starts
@@ -231,10 +240,9 @@ class ModelRunner:
         their `want` lists, or None if nothing is wanted.  The returned tensor is workspace memory:
         it is valid until the next step."""
         cache = self.cache
+        self.validate(entries)
         need = [0] * len(cache.groups)
         for e in entries:
-            if not cache.has_request(e.rid):
-                raise KeyError(f"request {e.rid!r} is not live in the cache")
             for gi, m in enumerate(cache.pages_missing(e.rid, len(e.tokens))):
                 need[gi] += m
         if any(n > g.pool.num_free for n, g in zip(need, cache.groups)):
