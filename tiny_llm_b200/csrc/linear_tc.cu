@@ -1,0 +1,450 @@
+// bfloat16 matrix products on the 5th-generation tensor cores: C[M,N] = A[M,K] . W[N,K]^T with
+// 32-bit accumulation in tensor memory.
+//
+//   * operands reach shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast),
+//     STAGES deep, signalled on mbarriers;
+//   * one elected thread issues tcgen05.mma (cta_group::1, kind::f16, M = 128, N = BN, K = 16 per
+//     instruction); tcgen05.commit releases each stage and, at the end, hands the accumulator over;
+//   * four warps read the accumulator back with tcgen05.ld and run the epilogue on 32-bit values:
+//     store bfloat16 / store float32 / add into a float32 output / SiLU(gate) * up / split-K
+//     atomics into a float32 output.
+//
+// Two orientations share the main loop.  NORMAL: the 128-row operand is A (tokens), the BN-row
+// operand is W: one CTA makes a 128 x BN tile of C (prefill).  SWAP: the 128-row operand is W and the
+// BN-row operand is A, BN = the token count rounded up to 16: one CTA makes C^T for 128 weight rows,
+// so that at decode the weights fill the 128-wide side of the MMA and stream through the pipeline;
+// grid.z splits K so that every SM streams a slice.
+//
+// Sizes: any M and N; K a multiple of 8 (the 16-byte rule of TMA row strides); tails of all three
+// are zero-filled by TMA and masked in the epilogue.  Every wait on an mbarrier is bounded: on
+// expiry the kernel records a code in `status`, stops issuing, frees its tensor memory and returns.
+//
+// Reference counterparts: tiny_llm/ops/cuda/gemm.cu:67-106 (SIMT tile product) and
+// gemm_q1_helper.cu:15-124 (warp-per-output GEMV for one row).
+#include <cuda.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "common.cuh"
+
+TLLM_DEFINE_LAST_ERROR
+
+namespace tllm {
+
+constexpr int BM = 128;        // rows of the 128-row operand per CTA = MMA M
+constexpr int BK = 64;         // K elements per stage = one 128-byte swizzle row of bfloat16
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;   // warp 0: TMA, warp 1: MMA + tensor-memory allocation, warps 2-5: epilogue
+
+enum Epilogue { EPI_BF16 = 0, EPI_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU = 3, EPI_ATOMIC_F32 = 4 };
+
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // a wait gives up after two seconds
+constexpr int ERR_PRODUCER = 1, ERR_MMA = 2, ERR_EPILOGUE = 3;
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: false if the phase did not complete within WAIT_LIMIT_NS, or another role gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (global_timer_ns() - t0 > WAIT_LIMIT_NS) return false;
+  }
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, stored with the
+// 128-byte swizzle: 8-row groups are 1024 bytes apart (stride byte offset), descriptor version 1.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);    // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                    // leading byte offset (unused with a swizzle, K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset
+  d |= (uint64_t)1 << 46;                    // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                    // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor: bfloat16 x bfloat16 -> float32, both operands K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t instr_desc_bf16(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
+
+template <int BN, int STAGES>
+struct SmemLayout {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 1) * 8 + 16 + 1024;   // + alignment slack
+};
+
+// rows_a / rows_b: extents of the 128-row operand and of the BN-row operand.  NORMAL: rows_a = M,
+// rows_b = N, out[M, N].  SWAP: rows_a = N (weights), rows_b = M (tokens), out[M, N] all the same.
+template <int BN, int STAGES, bool SWAP, int EPI>
+__global__ void __launch_bounds__(THREADS, 1)
+linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 void* __restrict__ out, int rows_a, int rows_b, int k_blocks, int k_blocks_per_split, int ldo,
+                 int* __restrict__ status) {
+  using L = SmemLayout<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* acc_bar = empty_bar + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile_a = blockIdx.y, tile_b = blockIdx.x;
+  const int kb_begin = blockIdx.z * k_blocks_per_split;
+  const int kb_end = min(k_blocks, kb_begin + k_blocks_per_split);
+  const int n_kb = kb_end - kb_begin;
+  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(acc_bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (n_kb > 0) {
+    if (warp == 0 && lane == 0) {
+      // ---------------- TMA producer
+      for (int i = 0; i < n_kb; ++i) {
+        const int s = i % STAGES;
+        const uint32_t parity = ((i / STAGES) & 1) ^ 1;
+        if (!mbar_wait(&empty_bar[s], parity, abort_flag)) { *abort_flag = 1; atomicExch(status, ERR_PRODUCER); break; }
+        mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
+        uint8_t* a_dst = smem + s * L::STAGE_BYTES;
+        tma_load_2d(a_dst, &map_a, (kb_begin + i) * BK, tile_a * BM, &full_bar[s]);
+        tma_load_2d(a_dst + L::A_BYTES, &map_b, (kb_begin + i) * BK, tile_b * BN, &full_bar[s]);
+      }
+    } else if (warp == 1 && lane == 0) {
+      // ---------------- MMA issuer
+      const uint32_t idesc = instr_desc_bf16(BN);
+      bool ok = true;
+      for (int i = 0; i < n_kb && ok; ++i) {
+        const int s = i % STAGES;
+        const uint32_t parity = (i / STAGES) & 1;
+        if (!mbar_wait(&full_bar[s], parity, abort_flag)) { *abort_flag = 1; atomicExch(status, ERR_MMA); ok = false; break; }
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(smem + s * L::STAGE_BYTES);
+        const uint32_t b_addr = a_addr + L::A_BYTES;
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          umma_bf16(tmem_base, smem_desc_sw128(a_addr + k * UMMA_K * 2), smem_desc_sw128(b_addr + k * UMMA_K * 2),
+                    idesc, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty_bar[s]);   // the stage is free once these MMAs have read it
+      }
+      umma_commit(acc_bar);           // arrives when every MMA issued so far has completed
+    } else if (warp >= 2) {
+      // ---------------- epilogue: warp w reads tensor-memory lanes [32 (w % 4), +32)
+      const int quad = warp & 3;
+      const int row = quad * 32 + lane;             // row of the 128-row operand within the tile
+      bool ok = mbar_wait(acc_bar, 0, abort_flag);
+      if (!ok) { *abort_flag = 1; atomicExch(status, ERR_EPILOGUE); }
+      ok = __all_sync(0xffffffffu, ok);   // tcgen05.ld below is warp-wide: all lanes or none
+      tc_fence_after();
+      if (ok) {
+        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
+        // 16-byte stores need an aligned base and row stride
+        const bool vec_ok = (reinterpret_cast<uintptr_t>(out) & 15) == 0 &&
+                            ((EPI == EPI_BF16 || EPI == EPI_SWIGLU) ? (ldo & 7) == 0 : (ldo & 3) == 0);
+        if (!SWAP) {
+          const int m = tile_a * BM + row;
+          if (EPI == EPI_SWIGLU) {
+            // columns [0, BN/2) are gate, [BN/2, BN) the matching up columns; output tile is BN/2 wide
+            const int n0 = tile_b * (BN / 2);
+            const int n_out = rows_b / 2;
+#pragma unroll 1
+            for (int c = 0; c < BN / 2; c += 32) {
+              float g[32], u[32];
+              tmem_ld32(taddr + c, g);
+              tmem_ld32(taddr + BN / 2 + c, u);
+              if (m < rows_a) {
+                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)m * ldo + n0 + c;
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (n0 + c + j < n_out) dst[j] = __float2bfloat16_rn(silu_f(g[j]) * u[j]);
+              }
+            }
+          } else {
+            const int n0 = tile_b * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+              float v[32];
+              tmem_ld32(taddr + c, v);
+              if (m < rows_a && n0 + c < rows_b) {
+                const bool full = n0 + c + 32 <= rows_b;
+                if (EPI == EPI_BF16) {
+                  __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)m * ldo + n0 + c;
+                  if (full && vec_ok) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                      uint4 pk;
+                      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+                      for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(v[j + 2 * e], v[j + 2 * e + 1]);
+                      *reinterpret_cast<uint4*>(dst + j) = pk;
+                    }
+                  } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                      if (n0 + c + j < rows_b) dst[j] = __float2bfloat16_rn(v[j]);
+                  }
+                } else {
+                  float* dst = reinterpret_cast<float*>(out) + (size_t)m * ldo + n0 + c;
+                  if (full && vec_ok) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                      float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                      if (EPI == EPI_ADD_F32) {
+                        const float4 p = *reinterpret_cast<const float4*>(dst + j);
+                        o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
+                      }
+                      *reinterpret_cast<float4*>(dst + j) = o;
+                    }
+                  } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                      if (n0 + c + j < rows_b) dst[j] = EPI == EPI_ADD_F32 ? dst[j] + v[j] : v[j];
+                  }
+                }
+              }
+            }
+          }
+        } else {
+          // SWAP: this thread's row is weight row n; tensor-memory column j is token tile_b*BN + j.
+          // For a fixed token the 32 lanes of a warp write 32 consecutive n: coalesced.
+          const int n = tile_a * BM + row;
+          const int m0 = tile_b * BN;
+#pragma unroll 1
+          for (int c = 0; c < BN; c += 16) {
+            float v[16];
+            tmem_ld16(taddr + c, v);
+            if (n < rows_a) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const int m = m0 + c + j;
+                if (m < rows_b) {
+                  const size_t o = (size_t)m * ldo + n;
+                  if (EPI == EPI_BF16) reinterpret_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(v[j]);
+                  else if (EPI == EPI_F32) reinterpret_cast<float*>(out)[o] = v[j];
+                  else if (EPI == EPI_ADD_F32) reinterpret_cast<float*>(out)[o] += v[j];
+                  else if (EPI == EPI_ATOMIC_F32) atomicAdd(reinterpret_cast<float*>(out) + o, v[j]);
+                }
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// A 2-D bfloat16 tensor [rows, k] with row stride ld (elements), tiled in boxes of box_rows x 64.
+static bool make_map(CUtensorMap* map, const void* ptr, int rows, int k, long long ld, int box_rows) {
+  using Key = std::tuple<const void*, int, int, long long, int>;
+  static std::map<Key, CUtensorMap> cache;
+  static std::mutex mu;
+  const Key key(ptr, rows, k, ld, box_rows);
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) { *map = it->second; return true; }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  if (cache.size() > 4096) cache.clear();
+  cache[key] = *map;
+  return true;
+}
+
+template <int BN, int STAGES, bool SWAP, int EPI>
+static int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int rows_a, int rows_b, int k, int splits,
+                  int ldo, int* status, cudaStream_t s) {
+  using L = SmemLayout<BN, STAGES>;
+  auto kern = linear_tc_kernel<BN, STAGES, SWAP, EPI>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (e != cudaSuccess) TLLM_FAIL(TLLM_ERR_CUDA, "linear_tc: cannot reserve %d bytes of shared memory: %s", L::TOTAL, cudaGetErrorString(e));
+    configured = true;
+  }
+  const int k_blocks = (k + BK - 1) / BK;
+  const int per_split = (k_blocks + splits - 1) / splits;
+  const int used_splits = (k_blocks + per_split - 1) / per_split;
+  dim3 grid((rows_b + BN - 1) / BN, (rows_a + BM - 1) / BM, used_splits);
+  kern<<<grid, THREADS, L::TOTAL, s>>>(ma, mb, out, rows_a, rows_b, k_blocks, per_split, ldo, status);
+  TLLM_CHECK_LAUNCH("linear_tc");
+  return TLLM_OK;
+}
+
+}  // namespace tllm
+
+using namespace tllm;
+
+// out[M, N] (row stride ldo) = / += a[M, K] (row stride lda) . w[N, K]^T, bfloat16 operands.
+//   epi: 0 store bfloat16, 1 store float32, 2 add into float32, 3 SiLU(gate)*up with gate/up rows of w
+//        interleaved in blocks of 128 (out is [M, N/2] bfloat16), 4 atomic add into float32.
+//   swap: 0 = 128 x 256 tiles of C per CTA (large M); 1 = weights on the 128-row side, M <= 128,
+//        `splits` slices of K per weight tile (epi 4 when splits > 1).
+// `status` is a device int that receives a non-zero code if a bounded wait expired.
+extern "C" int tllm_linear_tc(const void* a, const void* w, void* out, int m, int n, int k, int lda, int ldo, int epi,
+                              int swap, int splits, int* status, void* stream) {
+  TLLM_REQUIRE(m > 0 && n > 0 && k > 0, "linear_tc: empty product %d x %d x %d", m, n, k);
+  TLLM_REQUIRE(k % 8 == 0 && lda % 8 == 0, "linear_tc: K (%d) and the row stride of A (%d) must be multiples of 8 (16-byte rule of TMA)", k, lda);
+  TLLM_REQUIRE(((uintptr_t)a % 16) == 0 && ((uintptr_t)w % 16) == 0, "linear_tc: operands must be 16-byte aligned");
+  TLLM_REQUIRE(status != nullptr, "linear_tc: needs a status word");
+  cudaStream_t s = (cudaStream_t)stream;
+  CUtensorMap ma, mb;
+  if (!swap) {
+    TLLM_REQUIRE(splits == 1, "linear_tc: K is split only in the swapped orientation");
+    TLLM_REQUIRE(epi != EPI_ATOMIC_F32, "linear_tc: atomic output belongs to the swapped orientation");
+    if (epi == EPI_SWIGLU) TLLM_REQUIRE(n % 256 == 0, "linear_tc: the fused SiLU*up epilogue needs gate/up blocks of 128 rows (N = %d)", n);
+    if (!make_map(&ma, a, m, k, lda, BM) || !make_map(&mb, w, n, k, k, 256))
+      TLLM_FAIL(TLLM_ERR_CUDA, "linear_tc: cuTensorMapEncodeTiled failed");
+    switch (epi) {
+      case EPI_BF16: return launch<256, 4, false, EPI_BF16>(ma, mb, out, m, n, k, 1, ldo, status, s);
+      case EPI_F32: return launch<256, 4, false, EPI_F32>(ma, mb, out, m, n, k, 1, ldo, status, s);
+      case EPI_ADD_F32: return launch<256, 4, false, EPI_ADD_F32>(ma, mb, out, m, n, k, 1, ldo, status, s);
+      case EPI_SWIGLU: return launch<256, 4, false, EPI_SWIGLU>(ma, mb, out, m, n, k, 1, ldo, status, s);
+    }
+    TLLM_FAIL(TLLM_ERR_ARG, "linear_tc: unknown epilogue %d", epi);
+  }
+  TLLM_REQUIRE(m <= 128, "linear_tc: the swapped orientation takes at most 128 rows of A (got %d)", m);
+  TLLM_REQUIRE(epi != EPI_SWIGLU, "linear_tc: SiLU*up is fused only in the unswapped orientation");
+  TLLM_REQUIRE(splits >= 1 && (splits == 1 || epi == EPI_ATOMIC_F32), "linear_tc: split K needs the atomic epilogue");
+  const int bn = m <= 16 ? 16 : (m <= 32 ? 32 : (m <= 64 ? 64 : 128));
+  if (!make_map(&ma, w, n, k, k, BM) || !make_map(&mb, a, m, k, lda, bn))
+    TLLM_FAIL(TLLM_ERR_CUDA, "linear_tc: cuTensorMapEncodeTiled failed");
+#define TLLM_SWAP_CASE(BN_, ST_)                                                                                       \
+  switch (epi) {                                                                                                      \
+    case EPI_BF16: return launch<BN_, ST_, true, EPI_BF16>(ma, mb, out, n, m, k, splits, ldo, status, s);              \
+    case EPI_F32: return launch<BN_, ST_, true, EPI_F32>(ma, mb, out, n, m, k, splits, ldo, status, s);                \
+    case EPI_ADD_F32: return launch<BN_, ST_, true, EPI_ADD_F32>(ma, mb, out, n, m, k, splits, ldo, status, s);        \
+    case EPI_ATOMIC_F32: return launch<BN_, ST_, true, EPI_ATOMIC_F32>(ma, mb, out, n, m, k, splits, ldo, status, s);  \
+  }                                                                                                                   \
+  break;
+  switch (bn) {
+    case 16: TLLM_SWAP_CASE(16, 8)
+    case 32: TLLM_SWAP_CASE(32, 8)
+    case 64: TLLM_SWAP_CASE(64, 8)
+    case 128: TLLM_SWAP_CASE(128, 6)
+  }
+#undef TLLM_SWAP_CASE
+  TLLM_FAIL(TLLM_ERR_ARG, "linear_tc: unknown epilogue %d", epi);
+}

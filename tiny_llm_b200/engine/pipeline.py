@@ -27,7 +27,10 @@ class Pipeline:
         self.device = torch.device(f"cuda:{device}" if isinstance(device, int) else device)
         torch.cuda.set_device(self.device)
         self.dtype = parse_dtype(dtype)
-        self.config, self.model = load_model(model_path, self.dtype, self.device)
+        if isinstance(model_path, tuple):   # (config, loaded model): see from_model
+            self.config, self.model = model_path
+        else:
+            self.config, self.model = load_model(model_path, self.dtype, self.device)
         spec = self.model.spec
         if max_tokens is None:
             max_tokens = min(max_requests * spec.max_positions, 1 << 20)
@@ -39,6 +42,11 @@ class Pipeline:
         self.sampler = Sampler(self.device, spec.vocab_size, max_rows=max(2, max_requests + max_requests % 2))
         self._ids = itertools.count()
         self.requests: Dict[Hashable, Request] = {}
+
+    @classmethod
+    def from_model(cls, config, model, **kwargs) -> "Pipeline":
+        """A pipeline around a model that is already loaded on the device (kwargs as the constructor's)."""
+        return cls((config, model), **kwargs)
 
     # ---- request by request
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None, rid: Hashable = None):

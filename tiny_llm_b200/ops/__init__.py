@@ -42,9 +42,14 @@ def _need_cuda(*tensors):
             raise KernelError("the engine's ops run on a CUDA device only; got a tensor on " + str(t.device))
 
 
+launches = 0  # kernels launched through this module since import (each entry point launches one)
+
+
 def _check(lib, rc: int):
+    global launches
     if rc != 0:
         raise KernelError(lib.tllm_last_error().decode())
+    launches += 1
 
 
 def _i32(t: Optional[torch.Tensor], name: str):
@@ -126,9 +131,52 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, cos: Optional[torc
 # ----------------------------------------------------------------------------- matrix products
 
 
+EPI_BF16, EPI_F32, EPI_ADD_F32, EPI_SWIGLU, EPI_ATOMIC_F32 = 0, 1, 2, 3, 4
+SM_COUNT = 148
+force_generic = False   # tests set this to compare the tensor-core kernels with the SIMT ones
+_status = {}
+
+
+def status_word(device) -> torch.Tensor:
+    """The device int in which a kernel records that one of its bounded waits expired."""
+    key = torch.device(device).index or 0
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def check_status() -> None:
+    """Reads the status words (a device synchronisation) and raises if a kernel gave up a wait."""
+    for key, t in _status.items():
+        code = int(t.item())
+        if code:
+            t.zero_()
+            raise KernelError(f"a tensor-core kernel on device {key} gave up waiting (code {code}: "
+                              f"1 = TMA producer, 2 = MMA issuer, 3 = epilogue); its output is not valid")
+
+
+def _tc_ok(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+    k = a.shape[1]
+    return (not force_generic and a.dtype == torch.bfloat16 and k % 8 == 0 and a.stride(0) % 8 == 0 and
+            a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def _swap_splits(n: int, k: int, atomic_ok: bool) -> int:
+    """How many slices of K a weight tile of 128 rows is cut into at decode: enough CTAs to have
+    every SM stream weights, but at least four 64-wide blocks per slice."""
+    if not atomic_ok:
+        return 1
+    row_tiles = -(-n // 128)
+    k_blocks = -(-k // 64)
+    want = -(-SM_COUNT // row_tiles)
+    return max(1, min(want, k_blocks // 4))
+
+
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
     """out = a . w^T (w is [N, K], rows contiguous).  `out` may be of a's dtype or float32;
-    accumulate=True adds the product into a float32 `out`."""
+    accumulate=True adds the product into a float32 `out`.  bfloat16 products run on the tensor
+    cores (tcgen05) when K and the row stride of `a` are multiples of 8; float32 products, and
+    the sizes TMA cannot take, run on the SIMT kernel."""
     _need_cuda(a, w, out)
     m, k = a.shape
     n = w.shape[0]
@@ -146,15 +194,35 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool
         mode = OUT_F32
     else:
         raise KernelError(f"linear: output dtype {out.dtype} does not fit input dtype {a.dtype}")
+    if _tc_ok(a, w, out):
+        lib = build.load_library("linear_tc")
+        epi = {OUT_SAME: EPI_BF16, OUT_F32: EPI_F32, OUT_ACC: EPI_ADD_F32}[mode]
+        swap, splits = 0, 1
+        if m <= 128:
+            swap = 1
+            splits = _swap_splits(n, k, atomic_ok=(mode == OUT_ACC))
+            if splits > 1:
+                epi = EPI_ATOMIC_F32
+        _check(lib, lib.tllm_linear_tc(_ptr(a), _ptr(w), _ptr(out), m, n, k, a.stride(0), out.stride(0), epi, swap,
+                                       splits, _ptr(status_word(a.device)), _stream()))
+        return
     lib = build.load_library("linear_generic")
     _check(lib, lib.tllm_linear_generic(_ptr(a), _ptr(w), _ptr(out), m, n, k, a.stride(0), out.stride(0),
                                         _code(a.dtype), mode, _stream()))
 
 
 def linear_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, block: int, workspace) -> None:
-    """out = silu(a Wg^T) * (a Wu^T) with Wg, Wu interleaved in `w_gate_up` in row blocks of `block`."""
+    """out = silu(a Wg^T) * (a Wu^T) with Wg, Wu interleaved in `w_gate_up` in row blocks of `block`.
+    With blocks of 128 and more than 128 rows the product and SiLU*up are one tensor-core kernel."""
     m = a.shape[0]
-    gu = workspace.get("gate_up", (m, w_gate_up.shape[0]), a.dtype)
+    n2 = w_gate_up.shape[0]
+    if _tc_ok(a, w_gate_up, out) and block == 128 and m > 128 and n2 % 256 == 0 and out.is_contiguous():
+        _need_cuda(a, w_gate_up, out)
+        lib = build.load_library("linear_tc")
+        _check(lib, lib.tllm_linear_tc(_ptr(a), _ptr(w_gate_up), _ptr(out), m, n2, a.shape[1], a.stride(0),
+                                       out.stride(0), EPI_SWIGLU, 0, 1, _ptr(status_word(a.device)), _stream()))
+        return
+    gu = workspace.get("gate_up", (m, n2), a.dtype)
     linear(a, w_gate_up, gu)
     silu_mul(gu, out, block)
 
@@ -214,7 +282,7 @@ def sample(logits: torch.Tensor, work: torch.Tensor, temperature: torch.Tensor, 
                                 _ptr(seeds), _ptr(counters), _ptr(out), _stream()))
 
 
-ALL_LIBRARIES = ("elementwise", "linear_generic", "attention_generic", "sampling")
+ALL_LIBRARIES = ("elementwise", "linear_generic", "linear_tc", "attention_generic", "sampling")
 
 
 def build_all(verbose: bool = True):

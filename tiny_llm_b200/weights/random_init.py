@@ -23,16 +23,26 @@ def _generator(seed: int, name: str) -> torch.Generator:
     return g
 
 
-def random_state(specs: Mapping[str, WeightSpec], seed: int, std: float, dtype: torch.dtype) -> Dict[str, torch.Tensor]:
+def random_state(specs: Mapping[str, WeightSpec], seed: int, std: float, dtype: torch.dtype,
+                 device="cpu") -> Dict[str, torch.Tensor]:
+    """Tensors for every spec.  On the CPU (the default, what `write_random_model` stores) the values
+    are a function of (seed, name) alone; with a CUDA `device` they are drawn there from that
+    device's generator, which is faster for large models but a different stream."""
     out = {}
+    device = torch.device(device)
     for name, s in specs.items():
         if s.keep == INT32:
-            out[name] = torch.zeros(s.shape, dtype=torch.int32)
+            out[name] = torch.zeros(s.shape, dtype=torch.int32, device=device)
         elif s.keep == FLOAT32 and len(s.shape) == 1:
-            out[name] = torch.ones(s.shape, dtype=dtype)
+            out[name] = torch.ones(s.shape, dtype=dtype, device=device)
         else:
-            t = torch.empty(s.shape, dtype=torch.float32)
-            t.normal_(0.0, std, generator=_generator(seed, name))
+            g = _generator(seed, name)
+            if device.type != "cpu":
+                dg = torch.Generator(device=device)
+                dg.manual_seed(g.initial_seed())
+                g = dg
+            t = torch.empty(s.shape, dtype=torch.float32, device=device)
+            t.normal_(0.0, std, generator=g)
             out[name] = t.to(dtype)
     return out
 
