@@ -133,11 +133,15 @@ def test_paged_attention(ops, dtype, nq, nkv, hd, page, window):
     k_cache[pg, 0, 3] = ks[0][3, 0]
     tok_req = torch.cat([torch.full((n,), r, dtype=torch.int32) for r, n in enumerate(q_lens)])
     pos = torch.cat([torch.arange(l - n, l, dtype=torch.int32) for l, n in zip(lens, q_lens)])
-    batch = types.SimpleNamespace(token_request=tok_req.to(DEV), positions=pos.to(DEV))
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
+    starts = torch.tensor([l - n for l, n in zip(lens, q_lens)], dtype=torch.int32)
+    batch = types.SimpleNamespace(token_request=tok_req.to(DEV), positions=pos.to(DEV), cu_q=cu.to(DEV),
+                                  q_start=starts.to(DEV), num_requests=4, max_q_len=max(q_lens), max_kv_len=max(lens))
     out = torch.empty(t, nq * hd, dtype=DT[dtype], device=DEV)
     scale = 1.0 / math.sqrt(hd)
+    from tiny_llm_b200.engine import Workspace
     ops.paged_attention(qkv.to(DEV), nq, nkv, hd, k_cache.to(DEV), v_cache.to(DEV), table.to(DEV), batch, out,
-                        scale, window)
+                        scale, window, Workspace(DEV))
     out = out.float().cpu()
     assert not torch.isnan(out).any()
     cur = 0
@@ -154,8 +158,9 @@ def test_paged_attention(ops, dtype, nq, nkv, hd, page, window):
 
 def test_attention_refuses_sizes_it_is_not_built_for(ops):
     from tiny_llm_b200.ops import KernelError
-    batch = types.SimpleNamespace(token_request=torch.zeros(1, dtype=torch.int32, device=DEV),
-                                  positions=torch.zeros(1, dtype=torch.int32, device=DEV))
+    z = torch.zeros(2, dtype=torch.int32, device=DEV)
+    batch = types.SimpleNamespace(token_request=z[:1], positions=z[:1], cu_q=z, q_start=z[:1], num_requests=1,
+                                  max_q_len=1, max_kv_len=1)
     for hd in (24, 272):
         kc = torch.zeros(2, 1, 4, hd, device=DEV)
         with pytest.raises(KernelError, match="head size"):

@@ -13,10 +13,16 @@ DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 
 
 def context(dtype, positions=None, token_request=None):
+    """A step context for one request whose tokens are at `positions`."""
     from tiny_llm_b200.engine import Workspace
     batch = types.SimpleNamespace(
         positions=None if positions is None else positions.to(torch.int32).to(DEV),
         token_request=None if token_request is None else token_request.to(torch.int32).to(DEV))
+    if positions is not None:
+        n, first = len(positions), int(positions[0])
+        batch.cu_q = torch.tensor([0, n], dtype=torch.int32, device=DEV)
+        batch.q_start = torch.tensor([first], dtype=torch.int32, device=DEV)
+        batch.num_requests, batch.max_q_len, batch.max_kv_len = 1, n, first + n
     return types.SimpleNamespace(dtype=DT[dtype], device=torch.device(DEV), workspace=Workspace(DEV), batch=batch)
 
 

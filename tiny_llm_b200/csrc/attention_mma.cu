@@ -1,0 +1,346 @@
+// bfloat16 attention of the step's queries over the paged cache on the tensor cores, for prefill
+// portions and decoded tokens alike, compiled for one head size (-DTLLM_HEAD_DIM=...).
+//
+// A CTA serves one (request, key/value head, slice of keys) and a tile of 64 "rows"; a row is a
+// (new token, query head of the group) pair, so the G = heads / kv_heads query heads that share a
+// key/value head also share every K/V tile the CTA loads.  Four warps own 16 rows each.  Keys and
+// values of a 64-key tile are gathered from their pages into shared memory with cp.async, double
+// buffered; S = Q K^T and O += P V run on mma.sync.m16n8k16 (bfloat16 in, 32-bit accumulate); the
+// running softmax (max, sum, rescale) is kept in 32-bit registers with exp2 on scores scaled by
+// log2(e)/sqrt(hd)-style factors; P is rounded to bfloat16 only as the operand of the P V product.
+//
+// Visibility is one rule: key j is visible to the row of a token at position p iff j <= p and,
+// with a window w, j > p - w.  With `splits` > 1 the keys of a request are cut into slices of whole
+// tiles, each CTA writes an unnormalised partial (o, max, sum) per row to scratch, and
+// attention_combine merges them; with one split the result is written directly.
+//
+// Reference counterpart: tiny_llm/ops/cuda/flash_attention.cu:338-442 (32-bit SIMT, one lane per
+// key, 64-key tiles, chunk-local causal mask).
+#include <math_constants.h>
+
+#include "common.cuh"
+
+#ifndef TLLM_HEAD_DIM
+#error "compile with -DTLLM_HEAD_DIM=<multiple of 16 up to 256>"
+#endif
+
+TLLM_DEFINE_LAST_ERROR
+
+namespace tllm {
+
+constexpr int HD = TLLM_HEAD_DIM;
+static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multiple of 16 up to 256");
+constexpr int BM = 64;            // rows per CTA
+constexpr int BN = 64;            // keys per tile
+constexpr int WARPS = 4;
+constexpr int LDS = HD + 8;       // shared-memory row stride in elements: +16 bytes keeps ldmatrix conflict-free
+constexpr int CHUNKS = HD / 8;    // 16-byte chunks per row
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool pred) {
+  const int bytes = pred ? 16 : 0;   // 0: the destination is zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t* r, const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t* r, const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+struct AttnParams {
+  const __nv_bfloat16* q;        // rows of q_row_stride elements; queries first in each row
+  const __nv_bfloat16* kcache;   // [pages, kv_heads, page_size, HD]
+  const __nv_bfloat16* vcache;
+  const int* block_table;        // [R, max_blocks]
+  const int* cu_q;               // [R + 1]
+  const int* q_start;            // [R]: position of the request's first token in this step
+  __nv_bfloat16* out;            // [T, nq * HD]
+  float* part_o;                 // [T * nq, splits, HD]   (splits > 1)
+  float* part_ml;                // [T * nq, splits, 2]
+  long long page_stride, head_stride;
+  int q_row_stride, max_blocks, nq, nkv, page_size, window, tiles_per_req, splits;
+  float scale_log2;              // scale * log2(e)
+};
+
+// Gathers keys (or values) [j0, j0 + BN) of the request into a shared tile; rows outside
+// [j_begin, j_end] are zero and their pages are not touched (a window may have given them back).
+__device__ __forceinline__ void load_kv_tile(__nv_bfloat16* dst, const __nv_bfloat16* cache, const int* table,
+                                             int j0, int j_begin, int j_end, int kvh, const AttnParams& p) {
+  for (int idx = threadIdx.x; idx < BN * CHUNKS; idx += WARPS * 32) {
+    const int r = idx / CHUNKS, c = idx % CHUNKS;
+    const int j = j0 + r;
+    const bool ok = j >= j_begin && j <= j_end;
+    const __nv_bfloat16* src = cache;
+    if (ok) {
+      const int page = table[j / p.page_size];
+      src = cache + (long long)page * p.page_stride + (long long)kvh * p.head_stride +
+            (long long)(j % p.page_size) * HD + c * 8;
+    }
+    cp_async16(dst + r * LDS + c * 8, src, ok);
+  }
+}
+
+__global__ void __launch_bounds__(WARPS * 32)
+attention_mma_kernel(const AttnParams p) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+  __nv_bfloat16* k_s = q_s + BM * LDS;            // two stages
+  __nv_bfloat16* v_s = k_s + 2 * BN * LDS;        // two stages
+
+  const int req = blockIdx.x / p.tiles_per_req, tile = blockIdx.x % p.tiles_per_req;
+  const int kvh = blockIdx.y, split = blockIdx.z;
+  const int group = p.nq / p.nkv;
+  const int tok0 = p.cu_q[req];
+  const int q_len = p.cu_q[req + 1] - tok0;
+  const int rows_total = q_len * group;
+  const int row0 = tile * BM;
+  if (row0 >= rows_total) return;
+  const int start = p.q_start[req];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int* table = p.block_table + (size_t)req * p.max_blocks;
+
+  // keys this tile of rows can see at all, then this CTA's slice of them (whole 64-key tiles)
+  const int tok_lo = row0 / group;
+  const int tok_hi = min(q_len - 1, (row0 + BM - 1) / group);
+  const int key_hi = start + tok_hi;
+  const int key_lo = p.window > 0 ? max(0, start + tok_lo - p.window + 1) : 0;
+  const int first_tile = key_lo / BN, last_tile = key_hi / BN;
+  const int n_tiles = last_tile - first_tile + 1;
+  const int per_split = (n_tiles + p.splits - 1) / p.splits;
+  const int t_begin = first_tile + split * per_split;
+  const int t_end = min(last_tile + 1, t_begin + per_split);   // exclusive
+
+  // ---- Q tile: row r -> token r / group, head kvh * group + r % group
+  for (int idx = threadIdx.x; idx < BM * CHUNKS; idx += WARPS * 32) {
+    const int r = idx / CHUNKS, c = idx % CHUNKS;
+    const int row = row0 + r;
+    const bool ok = row < rows_total;
+    const __nv_bfloat16* src = p.q;
+    if (ok) src = p.q + (size_t)(tok0 + row / group) * p.q_row_stride + (size_t)(kvh * group + row % group) * HD + c * 8;
+    cp_async16(q_s + r * LDS + c * 8, src, ok);
+  }
+  cp_async_commit();
+  if (t_begin < t_end) {
+    load_kv_tile(k_s, p.kcache, table, t_begin * BN, key_lo, key_hi, kvh, p);
+    load_kv_tile(v_s, p.vcache, table, t_begin * BN, key_lo, key_hi, kvh, p);
+  }
+  cp_async_commit();
+
+  // per-thread rows: g and g + 8 of the warp's 16
+  const int r_a = row0 + warp * 16 + g, r_b = r_a + 8;
+  const int pos_a = start + r_a / group, pos_b = start + r_b / group;
+  const bool live_a = r_a < rows_total, live_b = r_b < rows_total;
+  const int lo_a = p.window > 0 ? pos_a - p.window + 1 : 0, lo_b = p.window > 0 ? pos_b - p.window + 1 : 0;
+
+  float m_a = -CUDART_INF_F, m_b = -CUDART_INF_F, l_a = 0.f, l_b = 0.f;
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+
+  for (int tix = t_begin; tix < t_end; ++tix) {
+    const int stage = (tix - t_begin) & 1;
+    const __nv_bfloat16* kt = k_s + stage * BN * LDS;
+    const __nv_bfloat16* vt = v_s + stage * BN * LDS;
+    if (tix + 1 < t_end) {   // prefetch the next tile into the other stage
+      load_kv_tile(k_s + (stage ^ 1) * BN * LDS, p.kcache, table, (tix + 1) * BN, key_lo, key_hi, kvh, p);
+      load_kv_tile(v_s + (stage ^ 1) * BN * LDS, p.vcache, table, (tix + 1) * BN, key_lo, key_hi, kvh, p);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+
+    // ---- S = Q K^T for this warp's 16 rows x 64 keys
+    float s[BN / 8][4];
+#pragma unroll
+    for (int i = 0; i < BN / 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+#pragma unroll
+    for (int k0 = 0; k0 < HD; k0 += 16) {
+      uint32_t a[4];
+      ldmatrix_x4(a, q_s + (warp * 16 + (lane & 15)) * LDS + k0 + (lane >> 4) * 8);
+#pragma unroll
+      for (int n0 = 0; n0 < BN; n0 += 16) {
+        uint32_t b[4];
+        ldmatrix_x4(b, kt + (n0 + (lane & 7) + (lane >> 4) * 8) * LDS + k0 + ((lane >> 3) & 1) * 8);
+        mma_bf16(s[n0 / 8], a, b[0], b[1]);
+        mma_bf16(s[n0 / 8 + 1], a, b[2], b[3]);
+      }
+    }
+
+    // ---- scale, mask, running softmax in 32-bit
+    const int j_base = tix * BN;
+    float mx_a = -CUDART_INF_F, mx_b = -CUDART_INF_F;
+#pragma unroll
+    for (int i = 0; i < BN / 8; ++i) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int j = j_base + i * 8 + t4 * 2 + e;
+        const bool va = live_a && j <= pos_a && j >= lo_a;
+        const bool vb = live_b && j <= pos_b && j >= lo_b;
+        s[i][e] = va ? s[i][e] * p.scale_log2 : -CUDART_INF_F;
+        s[i][2 + e] = vb ? s[i][2 + e] * p.scale_log2 : -CUDART_INF_F;
+        mx_a = fmaxf(mx_a, s[i][e]);
+        mx_b = fmaxf(mx_b, s[i][2 + e]);
+      }
+    }
+    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+    const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+    const float ms_a = mn_a == -CUDART_INF_F ? 0.f : mn_a, ms_b = mn_b == -CUDART_INF_F ? 0.f : mn_b;
+    const float corr_a = exp2f(m_a - ms_a), corr_b = exp2f(m_b - ms_b);   // 0 while nothing was seen
+    m_a = mn_a; m_b = mn_b;
+    float sum_a = 0.f, sum_b = 0.f;
+    uint32_t pfrag[BN / 16][4];
+#pragma unroll
+    for (int i = 0; i < BN / 8; ++i) {
+      const float p0 = exp2f(s[i][0] - ms_a), p1 = exp2f(s[i][1] - ms_a);
+      const float p2 = exp2f(s[i][2] - ms_b), p3 = exp2f(s[i][3] - ms_b);
+      sum_a += p0 + p1;
+      sum_b += p2 + p3;
+      // accumulator layout of two adjacent 8-key tiles = A-operand layout of one 16-key step
+      pfrag[i / 2][(i & 1) * 2 + 0] = pack_bf16(p0, p1);
+      pfrag[i / 2][(i & 1) * 2 + 1] = pack_bf16(p2, p3);
+    }
+    l_a = l_a * corr_a + sum_a;   // per-thread partial sums; reduced across the quad at the end
+    l_b = l_b * corr_b + sum_b;
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) { o[i][0] *= corr_a; o[i][1] *= corr_a; o[i][2] *= corr_b; o[i][3] *= corr_b; }
+
+    // ---- O += P V
+#pragma unroll
+    for (int kk = 0; kk < BN / 16; ++kk) {
+#pragma unroll
+      for (int d0 = 0; d0 < HD; d0 += 16) {
+        uint32_t b[4];
+        ldmatrix_x4_trans(b, vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDS + d0 + (lane >> 4) * 8);
+        mma_bf16(o[d0 / 8], pfrag[kk], b[0], b[1]);
+        mma_bf16(o[d0 / 8 + 1], pfrag[kk], b[2], b[3]);
+      }
+    }
+    __syncthreads();   // the stage is overwritten by the prefetch of the iteration after next
+  }
+  cp_async_wait<0>();
+
+  l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+  l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+  l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+  l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+
+  // ---- write: rows -> (token, head)
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int row = half ? r_b : r_a;
+    if (row >= rows_total) continue;
+    const float l = half ? l_b : l_a, m = half ? m_b : m_a;
+    const size_t th = (size_t)(tok0 + row / group) * p.nq + (size_t)(kvh * group + row % group);
+    if (p.splits == 1) {
+      const float inv = 1.f / l;
+      __nv_bfloat16* dst = p.out + th * HD;
+#pragma unroll
+      for (int i = 0; i < HD / 8; ++i)
+        *reinterpret_cast<uint32_t*>(dst + i * 8 + t4 * 2) = pack_bf16(o[i][half * 2] * inv, o[i][half * 2 + 1] * inv);
+    } else {
+      float* dst = p.part_o + (th * p.splits + split) * HD;
+#pragma unroll
+      for (int i = 0; i < HD / 8; ++i)
+        *reinterpret_cast<float2*>(dst + i * 8 + t4 * 2) = make_float2(o[i][half * 2], o[i][half * 2 + 1]);
+      if (t4 == 0) {
+        p.part_ml[(th * p.splits + split) * 2] = m;
+        p.part_ml[(th * p.splits + split) * 2 + 1] = l;
+      }
+    }
+  }
+}
+
+// Merges the slices of every (token, head): out = sum_s 2^(m_s - m) o_s / sum_s 2^(m_s - m) l_s.
+// A slice that saw no key of the row has m_s = -inf and l_s = 0 and drops out.
+__global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                         __nv_bfloat16* __restrict__ out, int splits) {
+  const size_t th = blockIdx.x;
+  float m = -CUDART_INF_F;
+  for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[(th * splits + s) * 2]);
+  float l = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float ms = part_ml[(th * splits + s) * 2];
+    if (ms != -CUDART_INF_F) l += exp2f(ms - m) * part_ml[(th * splits + s) * 2 + 1];
+  }
+  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float ms = part_ml[(th * splits + s) * 2];
+      if (ms != -CUDART_INF_F) acc += exp2f(ms - m) * part_o[(th * splits + s) * HD + d];
+    }
+    out[th * HD + d] = __float2bfloat16_rn(acc / l);
+  }
+}
+
+}  // namespace tllm
+
+using namespace tllm;
+
+extern "C" int tllm_attention_head_dim() { return HD; }
+
+// Bytes of scratch (float32 partials) a call with these sizes needs; 0 when splits == 1.
+extern "C" long long tllm_attention_mma_scratch_bytes(int n_tokens, int nq, int splits) {
+  return splits <= 1 ? 0 : (long long)n_tokens * nq * splits * (HD + 2) * 4;
+}
+
+extern "C" int tllm_attention_mma(const void* q, int q_row_stride, const void* kcache, const void* vcache,
+                                  const int* block_table, int max_blocks, const int* cu_q, const int* q_start,
+                                  void* out, int n_tokens, int n_requests, int max_q_len, int nq, int nkv, int hd,
+                                  int page_size, long long page_stride, long long head_stride, float scale, int window,
+                                  int splits, void* scratch, void* stream) {
+  TLLM_REQUIRE(hd == HD, "attention_mma: built for head size %d, called with %d", HD, hd);
+  TLLM_REQUIRE(n_tokens > 0 && n_requests > 0 && max_q_len > 0 && nq > 0 && nkv > 0 && nq % nkv == 0,
+               "attention_mma: %d tokens, %d requests, %d heads, %d key/value heads", n_tokens, n_requests, nq, nkv);
+  TLLM_REQUIRE(page_size > 0 && max_blocks > 0 && window >= 0 && splits >= 1, "attention_mma: page size %d, %d blocks, window %d, %d splits", page_size, max_blocks, window, splits);
+  TLLM_REQUIRE(((uintptr_t)q % 16) == 0 && (q_row_stride % 8) == 0 && ((uintptr_t)kcache % 16) == 0 && ((uintptr_t)vcache % 16) == 0 &&
+               (page_stride % 8) == 0 && (head_stride % 8) == 0, "attention_mma: rows must be 16-byte aligned");
+  TLLM_REQUIRE(splits == 1 || scratch != nullptr, "attention_mma: %d splits need scratch", splits);
+  TLLM_REQUIRE(nkv <= 65535 && splits <= 65535, "attention_mma: grid too large");
+  const int group = nq / nkv;
+  AttnParams p;
+  p.q = (const __nv_bfloat16*)q; p.kcache = (const __nv_bfloat16*)kcache; p.vcache = (const __nv_bfloat16*)vcache;
+  p.block_table = block_table; p.cu_q = cu_q; p.q_start = q_start; p.out = (__nv_bfloat16*)out;
+  p.part_o = (float*)scratch;
+  p.part_ml = splits > 1 ? (float*)scratch + (size_t)n_tokens * nq * splits * HD : nullptr;
+  p.page_stride = page_stride; p.head_stride = head_stride; p.q_row_stride = q_row_stride; p.max_blocks = max_blocks;
+  p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.window = window; p.splits = splits;
+  p.tiles_per_req = (int)(((long long)max_q_len * group + BM - 1) / BM);
+  p.scale_log2 = scale * 1.4426950408889634f;
+  const long long gx = (long long)n_requests * p.tiles_per_req;
+  TLLM_REQUIRE(gx <= 2147483647LL, "attention_mma: grid too large");
+  const int smem = (BM + 4 * BN) * LDS * 2;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) TLLM_FAIL(TLLM_ERR_CUDA, "attention_mma: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  attention_mma_kernel<<<dim3((unsigned)gx, nkv, splits), WARPS * 32, smem, s>>>(p);
+  TLLM_CHECK_LAUNCH("attention_mma");
+  if (splits > 1) {
+    attention_combine_kernel<<<(unsigned)((size_t)n_tokens * nq), HD >= 128 ? 128 : 64, 0, s>>>(p.part_o, p.part_ml, p.out, splits);
+    TLLM_CHECK_LAUNCH("attention_combine");
+  }
+  return TLLM_OK;
+}

@@ -230,11 +230,22 @@ def linear_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, b
 # ----------------------------------------------------------------------------- attention
 
 
+def _attention_splits(tiles: int, max_kv_len: int) -> int:
+    """Slices of keys per (request, key/value head) so that a small batch still fills the SMs;
+    a slice is at least four 64-key tiles."""
+    if tiles >= SM_COUNT:
+        return 1
+    return max(1, min(-(-2 * SM_COUNT // tiles), max_kv_len // 256))
+
+
 def paged_attention(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, k_cache: torch.Tensor,
                     v_cache: torch.Tensor, block_table: torch.Tensor, batch, out: torch.Tensor, scale: float,
-                    window: Optional[int] = None) -> None:
+                    window: Optional[int] = None, workspace=None) -> None:
     """Attention of every token of the step (queries in the first num_heads*head_dim values of each
-    `qkv` row) over its request's pages.  `batch` carries token_request and positions."""
+    `qkv` row) over its request's pages.  `batch` carries the step's metadata: token_request and
+    positions per token; cu_q, q_start per request; num_requests, max_q_len, max_kv_len.
+    bfloat16 runs on the tensor-core kernel compiled for this head size (it needs `workspace` for the
+    partial results when it slices the keys); float32 on the SIMT kernel."""
     _need_cuda(qkv, k_cache, v_cache, block_table, out)
     _i32(block_table, "block_table")
     t = qkv.shape[0]
@@ -242,11 +253,28 @@ def paged_attention(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_d
             k_cache.dtype != qkv.dtype or k_cache.stride() != v_cache.stride() or k_cache.stride(3) != 1 or \
             k_cache.stride(2) != head_dim or k_cache.shape[1] != num_kv_heads or k_cache.shape[3] != head_dim:
         raise KernelError("paged_attention: shapes or dtypes do not fit")
+    page_size = k_cache.shape[2]
+    if qkv.dtype == torch.bfloat16 and not force_generic and head_dim % 16 == 0 and 16 <= head_dim <= 256 and \
+            qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0:
+        lib = build.load_library("attention_mma", flags=(f"-DTLLM_HEAD_DIM={head_dim}",))
+        group = num_heads // num_kv_heads
+        tiles = batch.num_requests * (-(-batch.max_q_len * group // 64)) * num_kv_heads
+        splits = _attention_splits(tiles, batch.max_kv_len) if workspace is not None else 1
+        scratch = None
+        if splits > 1:
+            scratch = workspace.get("attention_partials", (t * num_heads * splits * (head_dim + 2),), torch.float32)
+        _check(lib, lib.tllm_attention_mma(
+            _ptr(qkv), qkv.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
+            _ptr(batch.cu_q), _ptr(batch.q_start), _ptr(out), t, batch.num_requests, batch.max_q_len, num_heads,
+            num_kv_heads, head_dim, page_size, ctypes.c_longlong(k_cache.stride(0)),
+            ctypes.c_longlong(k_cache.stride(1)), ctypes.c_float(scale), int(window or 0), splits, _ptr(scratch),
+            _stream()))
+        return
     lib = build.load_library("attention_generic")
     _check(lib, lib.tllm_paged_attention_generic(
         _ptr(qkv), qkv.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
         _ptr(batch.token_request), _ptr(batch.positions), _ptr(out), t, num_heads, num_kv_heads, head_dim,
-        k_cache.shape[2], ctypes.c_longlong(k_cache.stride(0)), ctypes.c_longlong(k_cache.stride(1)),
+        page_size, ctypes.c_longlong(k_cache.stride(0)), ctypes.c_longlong(k_cache.stride(1)),
         ctypes.c_float(scale), int(window or 0), _code(qkv.dtype), _stream()))
 
 
@@ -285,6 +313,12 @@ def sample(logits: torch.Tensor, work: torch.Tensor, temperature: torch.Tensor, 
 ALL_LIBRARIES = ("elementwise", "linear_generic", "linear_tc", "attention_generic", "sampling")
 
 
+ATTENTION_HEAD_DIMS = (16, 32, 48, 64, 128)   # head sizes `build_all` compiles ahead; others compile on first use
+
+
 def build_all(verbose: bool = True):
     """Compiles every library (what `__graft_entry__.build()` calls); returns their paths."""
-    return [build.compile_library(n, verbose=verbose) for n in ALL_LIBRARIES]
+    paths = [build.compile_library(n, verbose=verbose) for n in ALL_LIBRARIES]
+    paths += [build.compile_library("attention_mma", flags=(f"-DTLLM_HEAD_DIM={hd}",), verbose=verbose)
+              for hd in ATTENTION_HEAD_DIMS]
+    return paths

@@ -63,8 +63,18 @@ def _hash(source: str, extra_headers, flags) -> str:
     return h.hexdigest()[:16]
 
 
+def _tag(flags) -> str:
+    """A readable suffix from -DNAME=VALUE flags: attention_mma with -DTLLM_HEAD_DIM=64 -> _head_dim64."""
+    out = ""
+    for f in flags:
+        if f.startswith("-DTLLM_") and "=" in f:
+            k, v = f[len("-DTLLM_"):].split("=", 1)
+            out += f"_{k.lower()}{v}"
+    return out
+
+
 def object_path(name: str, extra_headers=(), flags=()) -> str:
-    return os.path.join(build_dir(), f"{name}-{_hash(name + '.cu', extra_headers, flags)}.so")
+    return os.path.join(build_dir(), f"{name}{_tag(flags)}-{_hash(name + '.cu', extra_headers, flags)}.so")
 
 
 def compile_library(name: str, extra_headers=(), flags=(), verbose: bool = True) -> str:
@@ -75,7 +85,8 @@ def compile_library(name: str, extra_headers=(), flags=(), verbose: bool = True)
     tmp = f"{out}.{os.getpid()}.tmp"
     cmd = [nvcc_path()] + ARCH_FLAGS + BASE_FLAGS + list(flags) + ["-I", CSRC, "-o", tmp, os.path.join(CSRC, name + ".cu")]
     if verbose:
-        print(f"[tiny_llm_b200] compiling {name}.cu for sm_100a ...", file=sys.stderr, flush=True)
+        print(f"[tiny_llm_b200] compiling {name}.cu{' ' + ' '.join(flags) if flags else ''} for sm_100a ...",
+              file=sys.stderr, flush=True)
     t0 = time.time()
     proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     last = t0
@@ -98,12 +109,13 @@ def compile_library(name: str, extra_headers=(), flags=(), verbose: bool = True)
 
 
 def load_library(name: str, extra_headers=(), flags=()) -> ctypes.CDLL:
+    key = name + _tag(flags)
     with _lock:
-        lib = _loaded.get(name)
+        lib = _loaded.get(key)
         if lib is None:
             lib = ctypes.CDLL(compile_library(name, extra_headers, flags))
             lib.tllm_last_error.restype = ctypes.c_char_p
-            _loaded[name] = lib
+            _loaded[key] = lib
         return lib
 
 

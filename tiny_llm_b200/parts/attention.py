@@ -77,7 +77,7 @@ class GQAttention:
             cache.k, cache.v, None if self.shares_cache else cache.slot_mapping)
         out = ctx.workspace.get("attn_out", (t, self.q_dim), ctx.dtype)
         ops.paged_attention(qkv, self.num_heads, self.num_kv_heads, self.head_dim, cache.k, cache.v,
-                            cache.block_table, ctx.batch, out, self.scale, self.window)
+                            cache.block_table, ctx.batch, out, self.scale, self.window, ctx.workspace)
         ops.linear(out, self.w_o, resid, accumulate=True)
 
 
