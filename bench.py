@@ -210,6 +210,9 @@ def main():
     ap.add_argument("--layers", type=int, default=TINYLLAMA["num_hidden_layers"],
                     help="fewer layers than the model has (layer sizes stay); both numbers are reported")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+                    help="measure one part only (for profiler captures of a small case)")
+    ap.add_argument("--batch", type=int, default=BATCH, help="requests of the decode step (default 8)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -231,6 +234,17 @@ def main():
     runner = make_runner(model, dtype, device, max_tokens=64 * CONTEXT, page_size=PAGE, max_requests=64,
                          max_tokens_per_step=2048)
     out = torch.zeros(64, dtype=torch.int32, device=device)
+
+    if args.only != "all":
+        # a small, single-purpose run for a profiler capture: one plain line, no record
+        if args.only == "decode":
+            ms, launched = timed_decode(runner, args.batch, start_len, steps, warmup, out)
+            print(json.dumps({"only": "decode", "batch": args.batch, "layers": args.layers, "ms_per_step": round(ms, 4),
+                              "gpu_launches": launched}))
+        else:
+            print(json.dumps({"only": "prefill", "layers": args.layers, "tokens": 2048,
+                              "ms": round(timed_prefill(runner, 2048, repeats=2), 3)}))
+        return 0
 
     sampler = ClockSampler().start()
     ms, launched = timed_decode(runner, BATCH, start_len, steps, warmup, out)

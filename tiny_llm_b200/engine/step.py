@@ -20,6 +20,7 @@ from typing import Hashable, List, Optional, Sequence
 import numpy as np
 import torch
 
+from .. import ops
 from ..cache import CacheManager
 from .workspace import Workspace
 
@@ -133,6 +134,11 @@ class ModelRunner:
         self._host_np = self._host_meta.numpy()
         self._dev_meta = torch.zeros(cur, dtype=torch.int32, device=self.device)
         self.steps_run = 0
+        # CUDA graphs of decode-only steps, keyed by what is baked into their launches
+        self.use_graphs = self.device.type == "cuda" and getattr(model, "graph_safe", False)
+        self._graphs = {}
+        self._graph_seen = set()
+        self.graph_replays = 0
 
     # ---- metadata
     def _region(self, buf, name, n=None):
@@ -252,8 +258,48 @@ class ModelRunner:
             ok = cache.reserve(e.rid, len(e.tokens))
             assert ok
         batch = self.build_batch(entries)
-        logits = self.model.forward(StepContext(self, batch))
+        logits = self._run(entries, batch)
         for e in entries:
             cache.commit(e.rid, len(e.tokens))
         self.steps_run += 1
         return logits
+
+    # ---- launch: eagerly, or as the replay of a captured graph when the step only decodes
+    def _graph_key(self, entries, batch: StepBatch):
+        """Steps in which every request brings one token and wants its logits replay a CUDA graph.
+        Baked into a graph: the number of requests and the bucket of the longest context (it fixes
+        how attention slices the keys); everything else is read from the metadata on the device."""
+        if not self.use_graphs or batch.max_q_len != 1 or batch.num_logits != batch.num_requests:
+            return None
+        if any(len(e.want) != 1 for e in entries):
+            return None
+        bucket = 256
+        while bucket < batch.max_kv_len:
+            bucket *= 2
+        return (batch.num_requests, bucket)
+
+    def _run(self, entries, batch: StepBatch):
+        key = self._graph_key(entries, batch)
+        if key is None:
+            return self.model.forward(StepContext(self, batch))
+        batch.max_kv_len = key[1]
+        held = self._graphs.get(key)
+        if held is None:
+            if key not in self._graph_seen:
+                # first time: run eagerly (this also sizes the workspace and configures the kernels)
+                self._graph_seen.add(key)
+                return self.model.forward(StepContext(self, batch))
+            graph = torch.cuda.CUDAGraph()
+            torch.cuda.synchronize(self.device)
+            before = ops.launches
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(StepContext(self, batch))
+            kernels = ops.launches - before
+            ops.launches = before
+            # the graph's launches point into these buffers: keep them alive even if the workspace grows
+            held = (graph, logits, list(self.workspace._buffers.values()), kernels)
+            self._graphs[key] = held
+        held[0].replay()
+        ops.launches += held[3]
+        self.graph_replays += 1
+        return held[1]

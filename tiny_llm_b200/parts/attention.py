@@ -22,6 +22,8 @@ from .registry import build_part, register_part
 
 
 class GQAttention:
+    graph_safe = True   # launches kernels only: a step through this part can be captured in a CUDA graph
+
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: PartSpec, window: Optional[int] = None, shares_cache: bool = False,
                  scale: Optional[float] = None):

@@ -31,6 +31,8 @@ def gate_up_block(intermediate_size: int) -> int:
 
 
 class SwiGLU:
+    graph_safe = True   # launches kernels only: a step through this part can be captured in a CUDA graph
+
     def __init__(self, hidden_size: int, intermediate_size: int):
         self.hidden_size = hidden_size
         self.intermediate_size = intermediate_size

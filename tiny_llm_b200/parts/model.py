@@ -63,6 +63,9 @@ class DecoderModel:
         self.embed = None
         self.lm_head = None
         self.loaded = False
+        # a part that synchronises or computes on the host must not be captured; parts say so themselves
+        parts = [self.final_norm] + [x for b in self.blocks for x in (b.norm1, b.mixer, b.norm2, b.ffn)]
+        self.graph_safe = all(getattr(x, "graph_safe", False) for x in parts)
 
     # ---- what the model wants from the weights and the cache
     def weight_specs(self) -> Dict[str, WeightSpec]:

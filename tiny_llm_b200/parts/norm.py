@@ -8,6 +8,8 @@ from .registry import register_part
 
 
 class RMSNorm:
+    graph_safe = True   # launches kernels only: a step through this part can be captured in a CUDA graph
+
     def __init__(self, size: int, eps: float):
         self.size = size
         self.eps = float(eps)
