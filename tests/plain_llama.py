@@ -96,14 +96,16 @@ def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
 
 
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_pos: torch.Tensor,
-              window: Optional[int] = None, causal: bool = True) -> torch.Tensor:
+              window: Optional[int] = None, causal: bool = True, quant: Quant = no_quant) -> torch.Tensor:
     """Scaled dot-product attention with grouped heads, full softmax (the reference's running
     softmax over 64-key tiles is the same function; tiny_llm/ops/cuda/flash_attention.cu:50-117,
     338-442).  q: [Tq, nq, hd]; k, v: [Tk, nkv, hd]; q head h reads kv head h // (nq/nkv); scores are
     (q / sqrt(hd)) . k; key j is visible to the query at absolute position p iff j <= p (and
     j > p - window if a window is given).  The reference compares a chunk-local query index with
     the absolute key index (flash_attention.cu:63-66, 402-405), which is the same rule when the
-    chunk starts at position 0, the only case it runs; the absolute rule is used here."""
+    chunk starts at position 0, the only case it runs; the absolute rule is used here.
+    `quant` rounds the unnormalised probabilities exp(s - max) where they enter the P.V product (the
+    bfloat16 path feeds them to the tensor cores in bfloat16); their sum stays 32-bit."""
     tq, nq, hd = q.shape
     tk, nkv, _ = k.shape
     group = nq // nkv
@@ -119,8 +121,8 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_pos: torch.Te
     for h in range(nq):
         s = (q[:, h, :] * scale) @ k[:, h // group, :].t()
         s = s.masked_fill(~visible, float("-inf"))
-        p = torch.softmax(s, dim=-1)
-        out[:, h, :] = p @ v[:, h // group, :]
+        p = torch.exp(s - s.max(dim=-1, keepdim=True).values)
+        out[:, h, :] = (quant(p) @ v[:, h // group, :]) / p.sum(dim=-1, keepdim=True)
     return out
 
 
@@ -149,7 +151,7 @@ def attention_block(h, w: Dict[str, torch.Tensor], prefix: str, cfg: dict, cos, 
     v = quant(linear(h, w[prefix + "v_proj.weight"])).view(t, nkv, hd)
     q = quant(apply_rope(q, cos, sin, positions))
     k = quant(apply_rope(k, cos, sin, positions))
-    o = quant(attention(q, k, v, positions, window=window)).reshape(t, nq * hd)
+    o = quant(attention(q, k, v, positions, window=window, quant=quant)).reshape(t, nq * hd)
     return linear(o, w[prefix + "o_proj.weight"])
 
 

@@ -50,7 +50,8 @@ def test_rms_norm(ops, dtype, rows, width, eps):
 
 
 @pytest.mark.parametrize("dtype", DT)
-@pytest.mark.parametrize("m,n,k", [(127, 353, 255), (1, 331, 80), (64, 64, 16), (200, 40, 1000), (3, 2, 1)])
+@pytest.mark.parametrize("m,n,k", [(127, 353, 255), (1, 331, 80), (64, 64, 16), (200, 40, 1000), (3, 2, 1),
+                                   (8, 640, 1024), (300, 520, 328), (129, 256, 72)])
 def test_linear(ops, dtype, m, n, k):
     torch.manual_seed(2)
     a = torch.randn(m, k).to(DT[dtype])
@@ -74,7 +75,11 @@ def test_linear(ops, dtype, m, n, k):
     assert torch.equal(out2, f32)
     one = torch.empty(1, n, device=DEV)
     ops.linear(a[m // 2: m // 2 + 1].to(DEV), w.to(DEV), one)
-    assert torch.equal(one[0], f32[m // 2])
+    if dtype == "float32":
+        assert torch.equal(one[0], f32[m // 2])                  # the 32-bit path orders its sums by k only
+    else:
+        assert float((one[0] - f32[m // 2]).abs().max()) <= 2e-5 * max(scale, 1)
+    ops.check_status()
 
 
 @pytest.mark.parametrize("dtype", DT)
@@ -88,6 +93,11 @@ def test_silu_mul(ops, dtype, m, inter, block):
     ops.silu_mul(gu.to(DEV), out, block)
     ref = pl.silu(gate.float()) * up.float()
     assert float((out.float().cpu() - ref).abs().max()) <= tol(dtype, float(ref.abs().max()))
+    if dtype == "bfloat16":   # a float32 accumulation buffer as the source: same result, buffer handed back zeroed
+        acc = gu.float().to(DEV)
+        out2 = torch.empty_like(out)
+        ops.silu_mul(acc, out2, block, consume=True)
+        assert torch.equal(out2, out) and float(acc.abs().sum()) == 0.0
 
 
 def paged_setup(dtype, n_req, lens, nkv, hd, page, seed, spare_pages=3):
@@ -198,6 +208,14 @@ def test_rope_kv_write(ops, dtype, nq, nkv, hd, page):
     written = torch.zeros(n_pages * page, dtype=torch.bool)
     written[slots.long()] = True
     assert float(kc.permute(0, 2, 1, 3).reshape(n_pages * page, -1)[~written].abs().sum()) == 0   # nothing else touched
+    # a float32 accumulation buffer as the source: same queries and pages, buffer handed back zeroed
+    acc = qkv.float().to(DEV)
+    dev3 = torch.zeros_like(dev)
+    kc3 = torch.zeros(n_pages, nkv, page, hd, dtype=DT[dtype], device=DEV)
+    vc3 = torch.zeros_like(kc3)
+    ops.rope_kv_write(dev3, pos.to(DEV), cos.to(DEV), sin.to(DEV), hd, nq, nkv, hd, kc3, vc3, slots.to(DEV), src=acc)
+    assert torch.equal(dev3[:, : nq * hd], dev[:, : nq * hd]) and torch.equal(kc3.cpu(), kc) and torch.equal(vc3.cpu(), vc)
+    assert float(acc.abs().sum()) == 0.0
     # queries only, no tables: nothing rotates, nothing is written
     q_only = torch.randn(t, nq * hd).to(DT[dtype])
     dev2 = q_only.to(DEV)

@@ -163,7 +163,7 @@ def test_run_order_names_a_layer_twice_and_shares_a_cache(dtype):
                 first_kv = (k, v)
         else:
             k, v = first_kv
-        o = quant(pl.attention(q, k, v, pos)).reshape(40, 64)
+        o = quant(pl.attention(q, k, v, pos, quant=quant)).reshape(40, 64)
         x = x + pl.linear(o, wq[p + "self_attn.o_proj.weight"])
         h = quant(pl.rms_norm(x, wq[p + "post_attention_layernorm.weight"], c["rms_norm_eps"]))
         x = x + pl.swiglu_mlp(h, wq[p + "mlp.gate_proj.weight"], wq[p + "mlp.up_proj.weight"],

@@ -47,6 +47,8 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_row_stride, const 
                                int nq, int nkv, int hd, int page_size, long long page_stride,
                                long long head_stride, float scale, int window) {
   __shared__ __align__(16) float q_s[WARPS][MAX_HD];
+  pdl_trigger();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long task = (long long)blockIdx.x * WARPS + warp;
   if (task >= (long long)n_tokens * nq) return;
@@ -68,11 +70,12 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_row_stride, const 
 
   for (int j0 = (lo / 32) * 32; j0 <= p; j0 += 32) {
     const int j = j0 + lane;
-    const bool valid = j >= lo && j <= p;
+    bool valid = j >= lo && j <= p && j / page_size < max_blocks;
+    const int page = valid ? table[j / page_size] : -1;
+    valid = valid && page >= 0;   // a table entry that names no page is never followed
     long long row_off = 0;
     float s = -CUDART_INF_F;
     if (valid) {
-      const int page = table[j / page_size];
       row_off = (long long)page * page_stride + (long long)kvh * head_stride + (long long)(j % page_size) * hd;
       const T* krow = kcache + row_off;
       float acc = 0.f;
@@ -84,9 +87,10 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_row_stride, const 
       }
       s = acc;
     }
-    const float m_new = fmaxf(m, warp_max(s));   // finite: every tile holds at least one visible key
-    const float pr = valid ? expf(s - m_new) : 0.f;
-    const float corr = expf(m - m_new);           // 0 on the first tile (m = -inf)
+    const float m_new = fmaxf(m, warp_max(s));
+    const float m_ref = m_new == -CUDART_INF_F ? 0.f : m_new;   // a tile without a visible key changes nothing
+    const float pr = valid ? expf(s - m_ref) : 0.f;
+    const float corr = expf(m - m_ref);           // 0 on the first tile (m = -inf)
     l = l * corr + warp_sum(pr);
     m = m_new;
 #pragma unroll
@@ -95,6 +99,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_row_stride, const 
     const int first = max(0, lo - j0);
     for (int kk = first; kk <= last; ++kk) {
       const float pk = __shfl_sync(0xffffffffu, pr, kk);
+      if (pk == 0.f) continue;   // uniform across the warp: nothing to add, and the row may name no page
       const long long off = __shfl_sync(0xffffffffu, row_off, kk);
       const T* vrow = vcache + off;
 #pragma unroll
@@ -135,16 +140,15 @@ extern "C" int tllm_paged_attention_generic(const void* q, int q_row_stride, con
   TLLM_REQUIRE(blocks <= 2147483647LL, "attention: %lld (token, head) pairs exceed the grid", tasks);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == TLLM_F32)
-    paged_attention_generic_kernel<float><<<(unsigned)blocks, WARPS * 32, 0, s>>>(
+    TLLM_LAUNCH("paged_attention_generic", paged_attention_generic_kernel<float>, (unsigned)blocks, WARPS * 32, 0, s,
         (const float*)q, q_row_stride, (const float*)kcache, (const float*)vcache, block_table, max_blocks,
         token_request, positions, (float*)out, n_tokens, nq, nkv, hd, page_size, page_stride, head_stride, scale, window);
   else if (dtype == TLLM_BF16)
-    paged_attention_generic_kernel<__nv_bfloat16><<<(unsigned)blocks, WARPS * 32, 0, s>>>(
+    TLLM_LAUNCH("paged_attention_generic", paged_attention_generic_kernel<__nv_bfloat16>, (unsigned)blocks, WARPS * 32, 0, s,
         (const __nv_bfloat16*)q, q_row_stride, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, block_table,
         max_blocks, token_request, positions, (__nv_bfloat16*)out, n_tokens, nq, nkv, hd, page_size, page_stride,
         head_stride, scale, window);
   else
     TLLM_FAIL(TLLM_ERR_ARG, "attention: unknown dtype code %d", dtype);
-  TLLM_CHECK_LAUNCH("paged_attention_generic");
   return TLLM_OK;
 }

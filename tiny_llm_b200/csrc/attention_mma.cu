@@ -1,11 +1,15 @@
 // bfloat16 attention of the step's queries over the paged cache on the tensor cores, for prefill
 // portions and decoded tokens alike, compiled for one head size (-DTLLM_HEAD_DIM=...).
 //
-// A CTA serves one (request, key/value head, slice of keys) and a tile of 64 "rows"; a row is a
+// A CTA serves one (request, key/value head, slice of keys) and a tile of "rows"; a row is a
 // (new token, query head of the group) pair, so the G = heads / kv_heads query heads that share a
-// key/value head also share every K/V tile the CTA loads.  Four warps own 16 rows each.  Keys and
-// values of a 64-key tile are gathered from their pages into shared memory with cp.async, double
-// buffered; S = Q K^T and O += P V run on mma.sync.m16n8k16 (bfloat16 in, 32-bit accumulate); the
+// key/value head also share every K/V tile the CTA loads.  Two kernels are built.  For portions of
+// prompts, four warps own 16 rows each of a 64-row tile and walk the keys together.  For decoded
+// tokens (at most 16 rows per request and key/value head) the four warps share the 16 rows and
+// split every 64-key tile between them, 16 keys each, with a running softmax of their own that is
+// merged through shared memory at the end: no warp computes for rows that do not exist.  Keys and
+// values of a 64-key tile are gathered from their pages into shared memory with cp.async, one page
+// lookup per row, several stages deep; S = Q K^T and O += P V run on mma.sync.m16n8k16 (bfloat16 in, 32-bit accumulate); the
 // running softmax (max, sum, rescale) is kept in 32-bit registers with exp2 on scores scaled by
 // log2(e)/sqrt(hd)-style factors; P is rounded to bfloat16 only as the operand of the P V product.
 //
@@ -30,9 +34,7 @@ namespace tllm {
 
 constexpr int HD = TLLM_HEAD_DIM;
 static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multiple of 16 up to 256");
-constexpr int BM = 64;            // rows per CTA
 constexpr int BN = 64;            // keys per tile
-constexpr int WARPS = 4;
 constexpr int LDS = HD + 8;       // shared-memory row stride in elements: +16 bytes keeps ldmatrix conflict-free
 constexpr int CHUNKS = HD / 8;    // 16-byte chunks per row
 
@@ -78,15 +80,17 @@ struct AttnParams {
 
 // Gathers keys (or values) [j0, j0 + BN) of the request into a shared tile; rows outside
 // [j_begin, j_end] are zero and their pages are not touched (a window may have given them back).
+template <int WARPS>
 __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* dst, const __nv_bfloat16* cache, const int* table,
                                              int j0, int j_begin, int j_end, int kvh, const AttnParams& p) {
   for (int idx = threadIdx.x; idx < BN * CHUNKS; idx += WARPS * 32) {
     const int r = idx / CHUNKS, c = idx % CHUNKS;
     const int j = j0 + r;
-    const bool ok = j >= j_begin && j <= j_end;
+    bool ok = j >= j_begin && j <= j_end && j / p.page_size < p.max_blocks;
     const __nv_bfloat16* src = cache;
+    const int page = ok ? table[j / p.page_size] : -1;
+    ok = ok && page >= 0;   // a table entry that names no page is never followed
     if (ok) {
-      const int page = table[j / p.page_size];
       src = cache + (long long)page * p.page_stride + (long long)kvh * p.head_stride +
             (long long)(j % p.page_size) * HD + c * 8;
     }
@@ -94,12 +98,16 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* dst, const __nv_bflo
   }
 }
 
+template <int WARPS, int STAGES>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_mma_kernel(const AttnParams p) {
+  constexpr int BM = WARPS * 16;   // rows per CTA
   extern __shared__ __align__(16) uint8_t smem_raw[];
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-  __nv_bfloat16* k_s = q_s + BM * LDS;            // two stages
-  __nv_bfloat16* v_s = k_s + 2 * BN * LDS;        // two stages
+  __nv_bfloat16* k_s = q_s + BM * LDS;                 // STAGES tiles
+  __nv_bfloat16* v_s = k_s + STAGES * BN * LDS;        // STAGES tiles
+  pdl_trigger();
+  pdl_wait();
 
   const int req = blockIdx.x / p.tiles_per_req, tile = blockIdx.x % p.tiles_per_req;
   const int kvh = blockIdx.y, split = blockIdx.z;
@@ -135,11 +143,15 @@ attention_mma_kernel(const AttnParams p) {
     cp_async16(q_s + r * LDS + c * 8, src, ok);
   }
   cp_async_commit();
-  if (t_begin < t_end) {
-    load_kv_tile(k_s, p.kcache, table, t_begin * BN, key_lo, key_hi, kvh, p);
-    load_kv_tile(v_s, p.vcache, table, t_begin * BN, key_lo, key_hi, kvh, p);
+  // prologue: the first STAGES - 1 tiles are requested; every stage is one commit group, empty or not
+#pragma unroll
+  for (int st = 0; st < STAGES - 1; ++st) {
+    if (t_begin + st < t_end) {
+      load_kv_tile<WARPS>(k_s + st * BN * LDS, p.kcache, table, (t_begin + st) * BN, key_lo, key_hi, kvh, p);
+      load_kv_tile<WARPS>(v_s + st * BN * LDS, p.vcache, table, (t_begin + st) * BN, key_lo, key_hi, kvh, p);
+    }
+    cp_async_commit();
   }
-  cp_async_commit();
 
   // per-thread rows: g and g + 8 of the warp's 16
   const int r_a = row0 + warp * 16 + g, r_b = r_a + 8;
@@ -153,18 +165,20 @@ attention_mma_kernel(const AttnParams p) {
   for (int i = 0; i < HD / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
 
   for (int tix = t_begin; tix < t_end; ++tix) {
-    const int stage = (tix - t_begin) & 1;
+    const int stage = (tix - t_begin) % STAGES;
     const __nv_bfloat16* kt = k_s + stage * BN * LDS;
     const __nv_bfloat16* vt = v_s + stage * BN * LDS;
-    if (tix + 1 < t_end) {   // prefetch the next tile into the other stage
-      load_kv_tile(k_s + (stage ^ 1) * BN * LDS, p.kcache, table, (tix + 1) * BN, key_lo, key_hi, kvh, p);
-      load_kv_tile(v_s + (stage ^ 1) * BN * LDS, p.vcache, table, (tix + 1) * BN, key_lo, key_hi, kvh, p);
+    cp_async_wait<STAGES - 2>();   // this tile (and the queries) have landed
+    __syncthreads();               // ... for every thread, and the stage read last iteration is free
+    {
+      const int nxt = tix + STAGES - 1;
+      if (nxt < t_end) {
+        const int ns = (nxt - t_begin) % STAGES;
+        load_kv_tile<WARPS>(k_s + ns * BN * LDS, p.kcache, table, nxt * BN, key_lo, key_hi, kvh, p);
+        load_kv_tile<WARPS>(v_s + ns * BN * LDS, p.vcache, table, nxt * BN, key_lo, key_hi, kvh, p);
+      }
       cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
     }
-    __syncthreads();
 
     // ---- S = Q K^T for this warp's 16 rows x 64 keys
     float s[BN / 8][4];
@@ -235,7 +249,6 @@ attention_mma_kernel(const AttnParams p) {
         mma_bf16(o[d0 / 8 + 1], pfrag[kk], b[2], b[3]);
       }
     }
-    __syncthreads();   // the stage is overwritten by the prefetch of the iteration after next
   }
   cp_async_wait<0>();
 
@@ -270,10 +283,205 @@ attention_mma_kernel(const AttnParams p) {
   }
 }
 
+// ---------------------------------------------------------------- decoded tokens
+// One thread gathers one row of the tile (keys first, then values): one page lookup, CHUNKS copies.
+__device__ __forceinline__ void load_kv_rows(__nv_bfloat16* k_dst, __nv_bfloat16* v_dst, const int* table, int j0,
+                                             int j_begin, int j_end, int kvh, const AttnParams& p) {
+  const int r = threadIdx.x & (BN - 1);
+  const bool is_v = threadIdx.x >= BN;
+  const int j = j0 + r;
+  bool ok = j >= j_begin && j <= j_end && j / p.page_size < p.max_blocks;
+  const int page = ok ? table[j / p.page_size] : -1;
+  ok = ok && page >= 0;
+  const __nv_bfloat16* src = is_v ? p.vcache : p.kcache;
+  if (ok) src += (long long)page * p.page_stride + (long long)kvh * p.head_stride + (long long)(j % p.page_size) * HD;
+  __nv_bfloat16* dst = (is_v ? v_dst : k_dst) + r * LDS;
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) cp_async16(dst + c * 8, ok ? src + c * 8 : src, ok);
+}
+
+template <int STAGES>
+__global__ void __launch_bounds__(128)
+attention_decode_kernel(const AttnParams p) {
+  static_assert(BN == 64, "one thread per key row and per value row of a tile");
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // 16 rows
+  __nv_bfloat16* k_s = q_s + 16 * LDS;                               // STAGES tiles
+  __nv_bfloat16* v_s = k_s + STAGES * BN * LDS;
+  pdl_trigger();
+  pdl_wait();
+
+  const int req = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+  const int group = p.nq / p.nkv;
+  const int tok0 = p.cu_q[req];
+  const int q_len = p.cu_q[req + 1] - tok0;
+  const int rows_total = q_len * group;        // <= 16 by the launch condition
+  const int start = p.q_start[req];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int* table = p.block_table + (size_t)req * p.max_blocks;
+
+  const int key_hi = start + q_len - 1;
+  const int key_lo = p.window > 0 ? max(0, start - p.window + 1) : 0;
+  const int first_tile = key_lo / BN, last_tile = key_hi / BN;
+  const int n_tiles = last_tile - first_tile + 1;
+  const int per_split = (n_tiles + p.splits - 1) / p.splits;
+  const int t_begin = first_tile + split * per_split;
+  const int t_end = min(last_tile + 1, t_begin + per_split);
+
+  for (int idx = threadIdx.x; idx < 16 * CHUNKS; idx += 128) {
+    const int r = idx / CHUNKS, c = idx % CHUNKS;
+    const bool ok = r < rows_total;
+    const __nv_bfloat16* src = p.q;
+    if (ok) src = p.q + (size_t)(tok0 + r / group) * p.q_row_stride + (size_t)(kvh * group + r % group) * HD + c * 8;
+    cp_async16(q_s + r * LDS + c * 8, src, ok);
+  }
+  cp_async_commit();
+#pragma unroll
+  for (int st = 0; st < STAGES - 1; ++st) {
+    if (t_begin + st < t_end)
+      load_kv_rows(k_s + st * BN * LDS, v_s + st * BN * LDS, table, (t_begin + st) * BN, key_lo, key_hi, kvh, p);
+    cp_async_commit();
+  }
+
+  const int pos_a = start + g / group, pos_b = start + (g + 8) / group;
+  const bool live_a = g < rows_total, live_b = g + 8 < rows_total;
+  const int lo_a = p.window > 0 ? pos_a - p.window + 1 : 0, lo_b = p.window > 0 ? pos_b - p.window + 1 : 0;
+  float m_a = -CUDART_INF_F, m_b = -CUDART_INF_F, l_a = 0.f, l_b = 0.f;
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  uint32_t qf[HD / 16][4];
+
+  for (int tix = t_begin; tix < t_end; ++tix) {
+    const int stage = (tix - t_begin) % STAGES;
+    const __nv_bfloat16* kt = k_s + stage * BN * LDS + warp * 16 * LDS;   // this warp's 16 keys of the tile
+    const __nv_bfloat16* vt = v_s + stage * BN * LDS + warp * 16 * LDS;
+    cp_async_wait<STAGES - 2>();
+    __syncthreads();
+    {
+      const int nxt = tix + STAGES - 1;
+      if (nxt < t_end) {
+        const int ns = (nxt - t_begin) % STAGES;
+        load_kv_rows(k_s + ns * BN * LDS, v_s + ns * BN * LDS, table, nxt * BN, key_lo, key_hi, kvh, p);
+      }
+      cp_async_commit();
+    }
+    if (tix == t_begin) {
+#pragma unroll
+      for (int k0 = 0; k0 < HD; k0 += 16) ldmatrix_x4(qf[k0 / 16], q_s + (lane & 15) * LDS + k0 + (lane >> 4) * 8);
+    }
+    float s[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+#pragma unroll
+    for (int k0 = 0; k0 < HD; k0 += 16) {
+      uint32_t b[4];
+      ldmatrix_x4(b, kt + ((lane & 7) + (lane >> 4) * 8) * LDS + k0 + ((lane >> 3) & 1) * 8);
+      mma_bf16(s[0], qf[k0 / 16], b[0], b[1]);
+      mma_bf16(s[1], qf[k0 / 16], b[2], b[3]);
+    }
+    const int j_base = tix * BN + warp * 16;
+    float mx_a = -CUDART_INF_F, mx_b = -CUDART_INF_F;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int j = j_base + i * 8 + t4 * 2 + e;
+        const bool va = live_a && j <= pos_a && j >= lo_a;
+        const bool vb = live_b && j <= pos_b && j >= lo_b;
+        s[i][e] = va ? s[i][e] * p.scale_log2 : -CUDART_INF_F;
+        s[i][2 + e] = vb ? s[i][2 + e] * p.scale_log2 : -CUDART_INF_F;
+        mx_a = fmaxf(mx_a, s[i][e]);
+        mx_b = fmaxf(mx_b, s[i][2 + e]);
+      }
+    }
+    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+    const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+    const float ms_a = mn_a == -CUDART_INF_F ? 0.f : mn_a, ms_b = mn_b == -CUDART_INF_F ? 0.f : mn_b;
+    const float corr_a = exp2f(m_a - ms_a), corr_b = exp2f(m_b - ms_b);
+    m_a = mn_a; m_b = mn_b;
+    uint32_t pf[4];
+    float sum_a = 0.f, sum_b = 0.f;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const float p0 = exp2f(s[i][0] - ms_a), p1 = exp2f(s[i][1] - ms_a);
+      const float p2 = exp2f(s[i][2] - ms_b), p3 = exp2f(s[i][3] - ms_b);
+      sum_a += p0 + p1;
+      sum_b += p2 + p3;
+      pf[i * 2] = pack_bf16(p0, p1);
+      pf[i * 2 + 1] = pack_bf16(p2, p3);
+    }
+    l_a = l_a * corr_a + sum_a;
+    l_b = l_b * corr_b + sum_b;
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) { o[i][0] *= corr_a; o[i][1] *= corr_a; o[i][2] *= corr_b; o[i][3] *= corr_b; }
+#pragma unroll
+    for (int d0 = 0; d0 < HD; d0 += 16) {
+      uint32_t b[4];
+      ldmatrix_x4_trans(b, vt + ((lane & 7) + ((lane >> 3) & 1) * 8) * LDS + d0 + (lane >> 4) * 8);
+      mma_bf16(o[d0 / 8], pf, b[0], b[1]);
+      mma_bf16(o[d0 / 8 + 1], pf, b[2], b[3]);
+    }
+  }
+  cp_async_wait<0>();
+  l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+  l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+  l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+  l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+
+  // ---- merge the four warps' running softmaxes through shared memory (the tile buffers are free now)
+  __syncthreads();
+  float* o_sh = reinterpret_cast<float*>(k_s);        // [4 warps][16 rows][HD]
+  float* ml_sh = o_sh + 4 * 16 * HD;                  // [4 warps][16 rows][2]
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i) {
+    *reinterpret_cast<float2*>(o_sh + (warp * 16 + g) * HD + i * 8 + t4 * 2) = make_float2(o[i][0], o[i][1]);
+    *reinterpret_cast<float2*>(o_sh + (warp * 16 + g + 8) * HD + i * 8 + t4 * 2) = make_float2(o[i][2], o[i][3]);
+  }
+  if (t4 == 0) {
+    ml_sh[(warp * 16 + g) * 2] = m_a; ml_sh[(warp * 16 + g) * 2 + 1] = l_a;
+    ml_sh[(warp * 16 + g + 8) * 2] = m_b; ml_sh[(warp * 16 + g + 8) * 2 + 1] = l_b;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < rows_total * (HD / 2); idx += 128) {
+    const int r = idx / (HD / 2), d = (idx % (HD / 2)) * 2;
+    float m = -CUDART_INF_F;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) m = fmaxf(m, ml_sh[(w * 16 + r) * 2]);
+    const float m_ref = m == -CUDART_INF_F ? 0.f : m;
+    float l = 0.f, acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float f = exp2f(ml_sh[(w * 16 + r) * 2] - m_ref);   // 0 for a warp that saw no key of the row
+      l += f * ml_sh[(w * 16 + r) * 2 + 1];
+      const float2 ov = *reinterpret_cast<const float2*>(o_sh + (w * 16 + r) * HD + d);
+      acc0 += f * ov.x;
+      acc1 += f * ov.y;
+    }
+    const size_t th = (size_t)(tok0 + r / group) * p.nq + (size_t)(kvh * group + r % group);
+    if (p.splits == 1) {
+      const float inv = 1.f / l;
+      *reinterpret_cast<uint32_t*>(p.out + th * HD + d) = pack_bf16(acc0 * inv, acc1 * inv);
+    } else {
+      *reinterpret_cast<float2*>(p.part_o + (th * p.splits + split) * HD + d) = make_float2(acc0, acc1);
+      if (d == 0) {
+        p.part_ml[(th * p.splits + split) * 2] = m;
+        p.part_ml[(th * p.splits + split) * 2 + 1] = l;
+      }
+    }
+  }
+}
+
 // Merges the slices of every (token, head): out = sum_s 2^(m_s - m) o_s / sum_s 2^(m_s - m) l_s.
 // A slice that saw no key of the row has m_s = -inf and l_s = 0 and drops out.
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          __nv_bfloat16* __restrict__ out, int splits) {
+  pdl_trigger();
+  pdl_wait();
   const size_t th = blockIdx.x;
   float m = -CUDART_INF_F;
   for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[(th * splits + s) * 2]);
@@ -324,23 +532,38 @@ extern "C" int tllm_attention_mma(const void* q, int q_row_stride, const void* k
   p.part_ml = splits > 1 ? (float*)scratch + (size_t)n_tokens * nq * splits * HD : nullptr;
   p.page_stride = page_stride; p.head_stride = head_stride; p.q_row_stride = q_row_stride; p.max_blocks = max_blocks;
   p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.window = window; p.splits = splits;
-  p.tiles_per_req = (int)(((long long)max_q_len * group + BM - 1) / BM);
   p.scale_log2 = scale * 1.4426950408889634f;
+  // decoded tokens (at most 16 rows per request and key/value head): one-warp CTAs, four stages
+  const bool small = (long long)max_q_len * group <= 16;
+  p.tiles_per_req = small ? 1 : (int)(((long long)max_q_len * group + 63) / 64);
   const long long gx = (long long)n_requests * p.tiles_per_req;
   TLLM_REQUIRE(gx <= 2147483647LL, "attention_mma: grid too large");
-  const int smem = (BM + 4 * BN) * LDS * 2;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) TLLM_FAIL(TLLM_ERR_CUDA, "attention_mma: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    configured = true;
-  }
   cudaStream_t s = (cudaStream_t)stream;
-  attention_mma_kernel<<<dim3((unsigned)gx, nkv, splits), WARPS * 32, smem, s>>>(p);
-  TLLM_CHECK_LAUNCH("attention_mma");
-  if (splits > 1) {
-    attention_combine_kernel<<<(unsigned)((size_t)n_tokens * nq), HD >= 128 ? 128 : 64, 0, s>>>(p.part_o, p.part_ml, p.out, splits);
-    TLLM_CHECK_LAUNCH("attention_combine");
+  if (small) {
+    constexpr int ST = 3;
+    // the merge buffers (4 x 16 x (HD + 2) floats) reuse the tile stages
+    static_assert(4 * 16 * (HD + 2) * 4 <= ST * BN * LDS * 2, "merge buffers must fit the key stages");
+    const int smem = (16 + 2 * ST * BN) * LDS * 2;
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (e != cudaSuccess) TLLM_FAIL(TLLM_ERR_CUDA, "attention_mma: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+      configured = true;
+    }
+    TLLM_LAUNCH("attention_decode", attention_decode_kernel<ST>, dim3((unsigned)n_requests, nkv, splits), 128, smem, s, p);
+  } else {
+    constexpr int ST = 2;
+    const int smem = (64 + 2 * ST * BN) * LDS * 2;
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<4, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (e != cudaSuccess) TLLM_FAIL(TLLM_ERR_CUDA, "attention_mma: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+      configured = true;
+    }
+    TLLM_LAUNCH("attention_mma", (attention_mma_kernel<4, ST>), dim3((unsigned)gx, nkv, splits), 128, smem, s, p);
   }
+  if (splits > 1)
+    TLLM_LAUNCH("attention_combine", attention_combine_kernel, (unsigned)((size_t)n_tokens * nq), HD >= 128 ? 128 : 64, 0, s,
+                p.part_o, p.part_ml, p.out, splits);
   return TLLM_OK;
 }

@@ -38,6 +38,12 @@ inline char* error_buffer() {
     if (e_ != cudaSuccess) TLLM_FAIL(TLLM_ERR_CUDA, "%s: %s", name, cudaGetErrorString(e_)); \
   } while (0)
 
+#define TLLM_LAUNCH(name, kernel, grid, block, smem, stream, ...)                                   \
+  do {                                                                                              \
+    cudaError_t e_ = ::tllm::launch_kernel(kernel, grid, block, smem, stream, __VA_ARGS__);         \
+    if (e_ != cudaSuccess) TLLM_FAIL(TLLM_ERR_CUDA, "%s: %s", name, cudaGetErrorString(e_));        \
+  } while (0)
+
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
 template <typename T> __device__ __forceinline__ T from_f32(float v);
@@ -71,8 +77,40 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return scratch[32];
 }
 
+// ---- programmatic dependent launch
+// Every kernel of the step begins with pdl_trigger() (the next kernel of the stream may be placed on
+// SMs as they free up) and calls pdl_wait() before it touches anything an earlier kernel wrote or
+// still reads.  What a kernel does before pdl_wait() must depend on nothing but constants of the
+// model (weights): that part overlaps the tail of its predecessor.  Without the launch attribute
+// both instructions do nothing, so the same kernels run in plain stream order too.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+inline int& pdl_enabled() {
+  static int on = 1;
+  return on;
+}
+
+// Launches `kernel`, as a programmatic dependent of the stream's previous kernel when enabled.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 }  // namespace tllm
 
-// Each shared object exports its own tllm_last_error().
-#define TLLM_DEFINE_LAST_ERROR \
-  extern "C" const char* tllm_last_error() { return ::tllm::error_buffer(); }
+// Each shared object exports its own tllm_last_error() and tllm_set_pdl().
+#define TLLM_DEFINE_LAST_ERROR                                                  \
+  extern "C" const char* tllm_last_error() { return ::tllm::error_buffer(); }  \
+  extern "C" void tllm_set_pdl(int on) { ::tllm::pdl_enabled() = on ? 1 : 0; }

@@ -13,6 +13,8 @@ namespace tllm {
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
                                  float* __restrict__ out, int n_tokens, int hidden) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   if (t >= n_tokens) return;
   const T* row = table + (size_t)tokens[t] * hidden;
@@ -27,6 +29,8 @@ __global__ void rms_norm_kernel(const float* __restrict__ x, const float* __rest
                                 T* __restrict__ out, const int* __restrict__ rows, int n_rows,
                                 int hidden, float eps) {
   __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   if (r >= n_rows) return;
   const float* src = x + (size_t)(rows ? rows[r] : r) * hidden;
@@ -42,17 +46,22 @@ __global__ void rms_norm_kernel(const float* __restrict__ x, const float* __rest
 }
 
 // ---------------------------------------------------------------- SiLU(gate) * up
-// `gu` rows hold gate and up interleaved in blocks: [2 g B, 2 g B + B) gate, next B up.
-template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int m, int inter, int blk) {
+// `gu` rows hold gate and up interleaved in blocks: [2 g B, 2 g B + B) gate, next B up.  With
+// ZERO the source is a float32 accumulation buffer (split-K partial sums land there) that this
+// kernel hands back cleared: every element is read once, by the thread that then zeroes it.
+template <typename TIn, typename TOut, bool ZERO>
+__global__ void silu_mul_kernel(TIn* __restrict__ gu, TOut* __restrict__ out, int m, int inter, int blk) {
+  pdl_trigger();
+  pdl_wait();
   const size_t total = (size_t)m * inter;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
     const int row = (int)(idx / inter), col = (int)(idx % inter);
     const int g = col / blk, j = col % blk;
-    const T* src = gu + (size_t)row * 2 * inter + (size_t)g * 2 * blk;
+    TIn* src = gu + (size_t)row * 2 * inter + (size_t)g * 2 * blk;
     const float gate = to_f32(src[j]), up = to_f32(src[blk + j]);
-    out[idx] = from_f32<T>((gate / (1.f + expf(-gate))) * up);
+    if (ZERO) { src[j] = from_f32<TIn>(0.f); src[blk + j] = from_f32<TIn>(0.f); }
+    out[idx] = from_f32<TOut>((gate / (1.f + expf(-gate))) * up);
   }
 }
 
@@ -63,45 +72,58 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
 // Rotation (rotate-half over the whole head; rot_dim is hd or 0): x'_i = c x_i - s x_{i+hd/2},
 // x'_{i+hd/2} = s x_i + c x_{i+hd/2}.
 template <typename T>
-__global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, float* __restrict__ src, int src_stride,
+                                     const int* __restrict__ positions,
                                      const float* __restrict__ cos_t, const float* __restrict__ sin_t,
-                                     int rot_dim, int n_tokens, int nq, int nkv, int hd, int row_stride,
+                                     int n_tokens, int nq, int nkv, int hd, int row_stride,
                                      T* __restrict__ kcache, T* __restrict__ vcache,
                                      const int* __restrict__ slot_mapping, int page_size,
                                      long long page_stride, long long head_stride) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   if (t >= n_tokens) return;
-  const int half = rot_dim / 2;
   const int pos = positions[t];
   T* row = qkv + (size_t)t * row_stride;
+  float* srow = src ? src + (size_t)t * src_stride : nullptr;   // float32 source that is handed back zeroed
   const bool write_kv = slot_mapping != nullptr;
   const int heads = write_kv ? nq + nkv : nq;
   const int half_hd = hd / 2;
   long long slot_base = 0;
   if (write_kv) {
     const int slot = slot_mapping[t];
+    if (slot < 0) return;   // a token without a slot writes nothing
     slot_base = (long long)(slot / page_size) * page_stride + (long long)(slot % page_size) * hd;
   }
   // queries and keys: one thread per (head, i < hd/2) rotates the pair of dims (i, i + hd/2)
   for (int idx = threadIdx.x; idx < heads * half_hd; idx += blockDim.x) {
     const int h = idx / half_hd, i = idx % half_hd;
-    T* head = row + (size_t)h * hd;
-    const float va = to_f32(head[i]), vb = to_f32(head[i + half_hd]);
+    const int e = h * hd + i;
+    float va, vb;
+    if (srow) {
+      va = srow[e]; vb = srow[e + half_hd];
+      srow[e] = 0.f; srow[e + half_hd] = 0.f;
+    } else {
+      va = to_f32(row[e]); vb = to_f32(row[e + half_hd]);
+    }
     float oa = va, ob = vb;
     if (cos_t) {
-      const float c = cos_t[(size_t)pos * half + i], s = sin_t[(size_t)pos * half + i];
+      const float c = cos_t[(size_t)pos * half_hd + i], s = sin_t[(size_t)pos * half_hd + i];
       oa = c * va - s * vb;
       ob = s * va + c * vb;
     }
-    T* dst = h < nq ? head : kcache + slot_base + (long long)(h - nq) * head_stride;
+    T* dst = h < nq ? row + (size_t)h * hd : kcache + slot_base + (long long)(h - nq) * head_stride;
     dst[i] = from_f32<T>(oa);
     dst[i + half_hd] = from_f32<T>(ob);
   }
   if (write_kv) {
-    const T* vsrc = row + (size_t)(nq + nkv) * hd;
+    const int v0 = (nq + nkv) * hd;
     for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
       const int h = idx / hd, i = idx % hd;
-      vcache[slot_base + (long long)h * head_stride + i] = vsrc[idx];
+      T val;
+      if (srow) { val = from_f32<T>(srow[v0 + idx]); srow[v0 + idx] = 0.f; }
+      else val = row[v0 + idx];
+      vcache[slot_base + (long long)h * head_stride + i] = val;
     }
   }
 }
@@ -116,12 +138,11 @@ extern "C" int tllm_embedding(const int* tokens, const void* table, float* out, 
   const int threads = hidden >= 1024 ? 256 : 128;
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == TLLM_F32)
-    embedding_kernel<float><<<n_tokens, threads, 0, s>>>(tokens, (const float*)table, out, n_tokens, hidden);
+    TLLM_LAUNCH("embedding", embedding_kernel<float>, n_tokens, threads, 0, s, tokens, (const float*)table, out, n_tokens, hidden);
   else if (dtype == TLLM_BF16)
-    embedding_kernel<__nv_bfloat16><<<n_tokens, threads, 0, s>>>(tokens, (const __nv_bfloat16*)table, out, n_tokens, hidden);
+    TLLM_LAUNCH("embedding", embedding_kernel<__nv_bfloat16>, n_tokens, threads, 0, s, tokens, (const __nv_bfloat16*)table, out, n_tokens, hidden);
   else
     TLLM_FAIL(TLLM_ERR_ARG, "embedding: unknown dtype code %d", dtype);
-  TLLM_CHECK_LAUNCH("embedding");
   return TLLM_OK;
 }
 
@@ -131,39 +152,43 @@ extern "C" int tllm_rms_norm(const float* x, const float* w, void* out, const in
   const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
   cudaStream_t s = (cudaStream_t)stream;
   if (out_dtype == TLLM_F32)
-    rms_norm_kernel<float><<<n_rows, threads, 0, s>>>(x, w, (float*)out, rows, n_rows, hidden, eps);
+    TLLM_LAUNCH("rms_norm", rms_norm_kernel<float>, n_rows, threads, 0, s, x, w, (float*)out, rows, n_rows, hidden, eps);
   else if (out_dtype == TLLM_BF16)
-    rms_norm_kernel<__nv_bfloat16><<<n_rows, threads, 0, s>>>(x, w, (__nv_bfloat16*)out, rows, n_rows, hidden, eps);
+    TLLM_LAUNCH("rms_norm", rms_norm_kernel<__nv_bfloat16>, n_rows, threads, 0, s, x, w, (__nv_bfloat16*)out, rows, n_rows, hidden, eps);
   else
     TLLM_FAIL(TLLM_ERR_ARG, "rms_norm: unknown dtype code %d", out_dtype);
-  TLLM_CHECK_LAUNCH("rms_norm");
   return TLLM_OK;
 }
 
-extern "C" int tllm_silu_mul(const void* gu, void* out, int m, int inter, int blk, int dtype, void* stream) {
+// in_dtype: dtype of `gu`; out_dtype: dtype of `out`.  zero_src != 0 (float32 `gu` only): `gu` is a
+// split-K accumulation buffer and is handed back cleared.
+extern "C" int tllm_silu_mul(void* gu, void* out, int m, int inter, int blk, int in_dtype, int out_dtype, int zero_src,
+                             void* stream) {
   TLLM_REQUIRE(m > 0 && inter > 0 && blk > 0 && inter % blk == 0,
                "silu_mul: %d rows, width %d, block %d (the block must divide the width)", m, inter, blk);
   const size_t total = (size_t)m * inter;
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
   cudaStream_t s = (cudaStream_t)stream;
-  if (dtype == TLLM_F32)
-    silu_mul_kernel<float><<<blocks, threads, 0, s>>>((const float*)gu, (float*)out, m, inter, blk);
-  else if (dtype == TLLM_BF16)
-    silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, s>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, m, inter, blk);
+  if (in_dtype == TLLM_F32 && out_dtype == TLLM_F32 && !zero_src)
+    TLLM_LAUNCH("silu_mul", (silu_mul_kernel<float, float, false>), blocks, threads, 0, s, (float*)gu, (float*)out, m, inter, blk);
+  else if (in_dtype == TLLM_BF16 && out_dtype == TLLM_BF16 && !zero_src)
+    TLLM_LAUNCH("silu_mul", (silu_mul_kernel<__nv_bfloat16, __nv_bfloat16, false>), blocks, threads, 0, s, (__nv_bfloat16*)gu, (__nv_bfloat16*)out, m, inter, blk);
+  else if (in_dtype == TLLM_F32 && out_dtype == TLLM_BF16 && zero_src)
+    TLLM_LAUNCH("silu_mul", (silu_mul_kernel<float, __nv_bfloat16, true>), blocks, threads, 0, s, (float*)gu, (__nv_bfloat16*)out, m, inter, blk);
   else
-    TLLM_FAIL(TLLM_ERR_ARG, "silu_mul: unknown dtype code %d", dtype);
-  TLLM_CHECK_LAUNCH("silu_mul");
+    TLLM_FAIL(TLLM_ERR_ARG, "silu_mul: dtype codes %d -> %d with zero_src %d are not built", in_dtype, out_dtype, zero_src);
   return TLLM_OK;
 }
 
-extern "C" int tllm_rope_kv_write(void* qkv, const int* positions, const float* cos_t, const float* sin_t,
-                                  int rot_dim, int n_tokens, int nq, int nkv, int hd, int row_stride,
+// `src` (optional): float32 rows of src_stride values to read instead of `qkv`; they are handed back
+// zeroed (a split-K accumulation buffer); the rotated queries are written to `qkv` all the same.
+extern "C" int tllm_rope_kv_write(void* qkv, float* src, int src_stride, const int* positions, const float* cos_t,
+                                  const float* sin_t, int rot_dim, int n_tokens, int nq, int nkv, int hd, int row_stride,
                                   void* kcache, void* vcache, const int* slot_mapping, int page_size,
                                   long long page_stride, long long head_stride, int dtype, void* stream) {
   TLLM_REQUIRE(n_tokens > 0 && nq > 0 && nkv > 0, "rope_kv_write: empty input");
   TLLM_REQUIRE(hd > 0 && hd % 2 == 0, "rope_kv_write: head size %d must be even", hd);
-  TLLM_REQUIRE(rot_dim >= 0 && rot_dim <= hd && rot_dim % 2 == 0, "rope_kv_write: rotary size %d must be even and at most the head size %d", rot_dim, hd);
   TLLM_REQUIRE(rot_dim == 0 || (cos_t && sin_t), "rope_kv_write: rotary size %d without tables", rot_dim);
   TLLM_REQUIRE(rot_dim == 0 || rot_dim == hd, "rope_kv_write: partial rotary (%d of %d dims) is not built", rot_dim, hd);
   TLLM_REQUIRE(!slot_mapping || (kcache && vcache && page_size > 0), "rope_kv_write: a slot mapping needs cache pointers and a page size");
@@ -173,11 +198,10 @@ extern "C" int tllm_rope_kv_write(void* qkv, const int* positions, const float* 
   const float* c = rot_dim ? cos_t : nullptr;
   const float* sn = rot_dim ? sin_t : nullptr;
   if (dtype == TLLM_F32)
-    rope_kv_write_kernel<float><<<n_tokens, threads, 0, s>>>((float*)qkv, positions, c, sn, rot_dim, n_tokens, nq, nkv, hd, row_stride, (float*)kcache, (float*)vcache, slot_mapping, page_size, page_stride, head_stride);
+    TLLM_LAUNCH("rope_kv_write", rope_kv_write_kernel<float>, n_tokens, threads, 0, s, (float*)qkv, src, src_stride, positions, c, sn, n_tokens, nq, nkv, hd, row_stride, (float*)kcache, (float*)vcache, slot_mapping, page_size, page_stride, head_stride);
   else if (dtype == TLLM_BF16)
-    rope_kv_write_kernel<__nv_bfloat16><<<n_tokens, threads, 0, s>>>((__nv_bfloat16*)qkv, positions, c, sn, rot_dim, n_tokens, nq, nkv, hd, row_stride, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, slot_mapping, page_size, page_stride, head_stride);
+    TLLM_LAUNCH("rope_kv_write", rope_kv_write_kernel<__nv_bfloat16>, n_tokens, threads, 0, s, (__nv_bfloat16*)qkv, src, src_stride, positions, c, sn, n_tokens, nq, nkv, hd, row_stride, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, slot_mapping, page_size, page_stride, head_stride);
   else
     TLLM_FAIL(TLLM_ERR_ARG, "rope_kv_write: unknown dtype code %d", dtype);
-  TLLM_CHECK_LAUNCH("rope_kv_write");
   return TLLM_OK;
 }

@@ -22,6 +22,8 @@ linear_generic_kernel(const T* __restrict__ a, const T* __restrict__ w, void* __
                       int m, int n, int k, int lda, int ldo) {
   __shared__ float as[BK][BM + 4];
   __shared__ float ws[BK][BN + 4];
+  pdl_trigger();
+  pdl_wait();
   const int tid = threadIdx.x;
   const int tx = tid % 16, ty = tid / 16;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -75,14 +77,13 @@ template <typename T>
 int launch(const void* a, const void* w, void* out, int m, int n, int k, int lda, int ldo, int mode, cudaStream_t s) {
   dim3 grid((n + BN - 1) / BN, (m + BM - 1) / BM);
   if (mode == OUT_SAME)
-    linear_generic_kernel<T, OUT_SAME><<<grid, THREADS, 0, s>>>((const T*)a, (const T*)w, out, m, n, k, lda, ldo);
+    TLLM_LAUNCH("linear_generic", (linear_generic_kernel<T, OUT_SAME>), grid, THREADS, 0, s, (const T*)a, (const T*)w, out, m, n, k, lda, ldo);
   else if (mode == OUT_F32)
-    linear_generic_kernel<T, OUT_F32><<<grid, THREADS, 0, s>>>((const T*)a, (const T*)w, out, m, n, k, lda, ldo);
+    TLLM_LAUNCH("linear_generic", (linear_generic_kernel<T, OUT_F32>), grid, THREADS, 0, s, (const T*)a, (const T*)w, out, m, n, k, lda, ldo);
   else if (mode == OUT_ACC)
-    linear_generic_kernel<T, OUT_ACC><<<grid, THREADS, 0, s>>>((const T*)a, (const T*)w, out, m, n, k, lda, ldo);
+    TLLM_LAUNCH("linear_generic", (linear_generic_kernel<T, OUT_ACC>), grid, THREADS, 0, s, (const T*)a, (const T*)w, out, m, n, k, lda, ldo);
   else
     TLLM_FAIL(TLLM_ERR_ARG, "linear: unknown output mode %d", mode);
-  TLLM_CHECK_LAUNCH("linear_generic");
   return TLLM_OK;
 }
 

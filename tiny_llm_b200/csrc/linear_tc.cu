@@ -13,7 +13,7 @@
 // operand is W: one CTA makes a 128 x BN tile of C (prefill).  SWAP: the 128-row operand is W and the
 // BN-row operand is A, BN = the token count rounded up to 16: one CTA makes C^T for 128 weight rows,
 // so that at decode the weights fill the 128-wide side of the MMA and stream through the pipeline;
-// grid.z splits K so that every SM streams a slice.
+// grid.z splits K so that every SM streams a slice, and two such CTAs fit an SM.
 //
 // Sizes: any M and N; K a multiple of 8 (the 16-byte rule of TMA row strides); tails of all three
 // are zero-filled by TMA and masked in the epilogue.  Every wait on an mbarrier is bounded: on
@@ -160,7 +160,7 @@ struct SmemLayout {
 // rows_a / rows_b: extents of the 128-row operand and of the BN-row operand.  NORMAL: rows_a = M,
 // rows_b = N, out[M, N].  SWAP: rows_a = N (weights), rows_b = M (tokens), out[M, N] all the same.
 template <int BN, int STAGES, bool SWAP, int EPI>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, SWAP ? 2 : 1)
 linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  void* __restrict__ out, int rows_a, int rows_b, int k_blocks, int k_blocks_per_split, int ldo,
                  int* __restrict__ status) {
@@ -192,17 +192,34 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // The weight operand (A when SWAP, else B) depends on no earlier kernel: its first STAGES tiles are
+  // requested before this grid waits for its predecessors, so they stream in under their tail.
+  pdl_trigger();
+  const int n_pre = min(n_kb, STAGES);
+  if (warp == 0 && lane == 0) {
+    for (int i = 0; i < n_pre; ++i) {
+      mbar_expect_tx(&full_bar[i], L::STAGE_BYTES);
+      uint8_t* a_dst = smem + i * L::STAGE_BYTES;
+      if (SWAP) tma_load_2d(a_dst, &map_a, (kb_begin + i) * BK, tile_a * BM, &full_bar[i]);
+      else tma_load_2d(a_dst + L::A_BYTES, &map_b, (kb_begin + i) * BK, tile_b * BN, &full_bar[i]);
+    }
+  }
+  pdl_wait();
+
   if (n_kb > 0) {
     if (warp == 0 && lane == 0) {
       // ---------------- TMA producer
       for (int i = 0; i < n_kb; ++i) {
         const int s = i % STAGES;
-        const uint32_t parity = ((i / STAGES) & 1) ^ 1;
-        if (!mbar_wait(&empty_bar[s], parity, abort_flag)) { *abort_flag = 1; atomicExch(status, ERR_PRODUCER); break; }
-        mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
         uint8_t* a_dst = smem + s * L::STAGE_BYTES;
-        tma_load_2d(a_dst, &map_a, (kb_begin + i) * BK, tile_a * BM, &full_bar[s]);
-        tma_load_2d(a_dst + L::A_BYTES, &map_b, (kb_begin + i) * BK, tile_b * BN, &full_bar[s]);
+        const bool pre = i < n_pre;   // the weight tile of this stage is already on its way
+        if (!pre) {
+          const uint32_t parity = ((i / STAGES) & 1) ^ 1;
+          if (!mbar_wait(&empty_bar[s], parity, abort_flag)) { *abort_flag = 1; atomicExch(status, ERR_PRODUCER); break; }
+          mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
+        }
+        if (!pre || !SWAP) tma_load_2d(a_dst, &map_a, (kb_begin + i) * BK, tile_a * BM, &full_bar[s]);
+        if (!pre || SWAP) tma_load_2d(a_dst + L::A_BYTES, &map_b, (kb_begin + i) * BK, tile_b * BN, &full_bar[s]);
       }
     } else if (warp == 1 && lane == 0) {
       // ---------------- MMA issuer
@@ -388,8 +405,7 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int r
   const int per_split = (k_blocks + splits - 1) / splits;
   const int used_splits = (k_blocks + per_split - 1) / per_split;
   dim3 grid((rows_b + BN - 1) / BN, (rows_a + BM - 1) / BM, used_splits);
-  kern<<<grid, THREADS, L::TOTAL, s>>>(ma, mb, out, rows_a, rows_b, k_blocks, per_split, ldo, status);
-  TLLM_CHECK_LAUNCH("linear_tc");
+  TLLM_LAUNCH("linear_tc", kern, grid, THREADS, L::TOTAL, s, ma, mb, out, rows_a, rows_b, k_blocks, per_split, ldo, status);
   return TLLM_OK;
 }
 
@@ -439,11 +455,13 @@ extern "C" int tllm_linear_tc(const void* a, const void* w, void* out, int m, in
     case EPI_ATOMIC_F32: return launch<BN_, ST_, true, EPI_ATOMIC_F32>(ma, mb, out, n, m, k, splits, ldo, status, s);  \
   }                                                                                                                   \
   break;
+  // stage counts keep a CTA under half of an SM's shared memory: two CTAs stream side by side, so
+  // that a grid of up to 296 CTAs is resident at once and no second wave trails behind
   switch (bn) {
-    case 16: TLLM_SWAP_CASE(16, 8)
-    case 32: TLLM_SWAP_CASE(32, 8)
-    case 64: TLLM_SWAP_CASE(64, 8)
-    case 128: TLLM_SWAP_CASE(128, 6)
+    case 16: TLLM_SWAP_CASE(16, 6)
+    case 32: TLLM_SWAP_CASE(32, 5)
+    case 64: TLLM_SWAP_CASE(64, 4)
+    case 128: TLLM_SWAP_CASE(128, 3)
   }
 #undef TLLM_SWAP_CASE
   TLLM_FAIL(TLLM_ERR_ARG, "linear_tc: unknown epilogue %d", epi);

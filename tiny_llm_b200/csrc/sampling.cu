@@ -155,6 +155,8 @@ __device__ __forceinline__ int block_argmax(const float* __restrict__ row, int v
 
 __global__ void __launch_bounds__(ST) argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int v) {
   __shared__ BlockScratch sc;
+  pdl_trigger();
+  pdl_wait();
   const int b = blockIdx.x;
   const int r = block_argmax(logits + (size_t)b * v, v, sc);
   if (threadIdx.x == 0) out[b] = r;
@@ -175,6 +177,8 @@ sample_kernel(const float* __restrict__ logits, float* __restrict__ work, int v,
               const unsigned long long* __restrict__ counters, int* __restrict__ out) {
   __shared__ BlockScratch sc;
   __shared__ int s_choice, s_last;
+  pdl_trigger();
+  pdl_wait();
   const int b = blockIdx.x;
   const float* row = logits + (size_t)b * v;
   const float temp = temperature[b];
@@ -282,8 +286,7 @@ using namespace tllm;
 
 extern "C" int tllm_argmax(const float* logits, int* out, int n, int v, void* stream) {
   TLLM_REQUIRE(n > 0 && v > 0, "argmax: empty input (%d rows of %d)", n, v);
-  argmax_kernel<<<n, ST, 0, (cudaStream_t)stream>>>(logits, out, v);
-  TLLM_CHECK_LAUNCH("argmax");
+  TLLM_LAUNCH("argmax", argmax_kernel, n, ST, 0, (cudaStream_t)stream, logits, out, v);
   return TLLM_OK;
 }
 
@@ -292,7 +295,6 @@ extern "C" int tllm_sample(const float* logits, float* work, int n, int v, const
                            int* out, void* stream) {
   TLLM_REQUIRE(n > 0 && v > 0, "sample: empty input (%d rows of %d)", n, v);
   TLLM_REQUIRE(work != nullptr, "sample: needs n*V floats of scratch");
-  sample_kernel<<<n, ST, 0, (cudaStream_t)stream>>>(logits, work, v, temperature, top_k, top_p, seeds, counters, out);
-  TLLM_CHECK_LAUNCH("sample");
+  TLLM_LAUNCH("sample", sample_kernel, n, ST, 0, (cudaStream_t)stream, logits, work, v, temperature, top_k, top_p, seeds, counters, out);
   return TLLM_OK;
 }

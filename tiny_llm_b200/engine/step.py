@@ -129,9 +129,13 @@ class ModelRunner:
             self._off[f"block_table{gi}"] = (cur, r * self.max_blocks)
             cur += r * self.max_blocks
         self._meta_words = cur
+        # The host side of the metadata is a ring of pinned buffers: the copy to the device is
+        # asynchronous, and a caller that enqueues steps without waiting for them must not overwrite a
+        # buffer whose copy has not run yet.  An event per buffer says when its copy is done.
         pin = self.device.type == "cuda"
-        self._host_meta = torch.zeros(cur, dtype=torch.int32, pin_memory=pin)
-        self._host_np = self._host_meta.numpy()
+        self._staging = [torch.zeros(cur, dtype=torch.int32, pin_memory=pin) for _ in range(4 if pin else 1)]
+        self._staging_done = [None] * len(self._staging)
+        self._staging_next = 0
         self._dev_meta = torch.zeros(cur, dtype=torch.int32, device=self.device)
         self.steps_run = 0
         # CUDA graphs of decode-only steps, keyed by what is baked into their launches
@@ -180,7 +184,12 @@ class ModelRunner:
         q_lens = [len(e.tokens) for e in entries]
         t = sum(q_lens)
         starts = [cache.kv_len[e.rid] for e in entries]
-        host = self._host_np
+        slot = self._staging_next
+        self._staging_next = (slot + 1) % len(self._staging)
+        if self._staging_done[slot] is not None:
+            self._staging_done[slot].synchronize()   # the copy that last read this buffer has finished
+        host_meta = self._staging[slot]
+        host = host_meta.numpy()
         tok = self._region(host, "tokens", t)
         pos = self._region(host, "positions", t)
         req = self._region(host, "token_request", t)
@@ -223,7 +232,11 @@ class ModelRunner:
             group_hosts.append((sm, bt))
             used_words = self._off[f"block_table{gi}"][0] + r * max_blocks
         # one copy, host to device
-        self._dev_meta[:used_words].copy_(self._host_meta[:used_words], non_blocking=True)
+        self._dev_meta[:used_words].copy_(host_meta[:used_words], non_blocking=True)
+        if self.device.type == "cuda":
+            if self._staging_done[slot] is None:
+                self._staging_done[slot] = torch.cuda.Event()
+            self._staging_done[slot].record()
         dev = self._dev_meta
         groups = []
         for gi in range(len(cache.groups)):

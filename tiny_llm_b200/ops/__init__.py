@@ -5,6 +5,7 @@ that is not on a CUDA device, or called where the kernels cannot be built, raise
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -43,6 +44,16 @@ def _need_cuda(*tensors):
 
 
 launches = 0  # kernels launched through this module since import (each entry point launches one)
+_pdl = True
+
+
+def set_pdl(on: bool) -> None:
+    """Programmatic dependent launch: each kernel is launched so that its prologue (and, for the
+    matrix products, its first weight tiles) may overlap the tail of the kernel before it."""
+    global _pdl
+    _pdl = bool(on)
+    for lib in build._loaded.values():
+        lib.tllm_set_pdl(1 if _pdl else 0)
 
 
 def _check(lib, rc: int):
@@ -88,24 +99,30 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tenso
                                   _code(out.dtype), _stream()))
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, block: int) -> None:
-    """out[m, g*block + j] = silu(gate_up[m, 2*g*block + j]) * gate_up[m, 2*g*block + block + j]."""
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, block: int, consume: bool = False) -> None:
+    """out[m, g*block + j] = silu(gate_up[m, 2*g*block + j]) * gate_up[m, 2*g*block + block + j].
+    consume=True: `gate_up` is a float32 accumulation buffer (split-K sums) and is handed back zeroed."""
     _need_cuda(gate_up, out)
     m, inter = out.shape
-    if gate_up.shape != (m, 2 * inter) or gate_up.dtype != out.dtype or not gate_up.is_contiguous() or \
-            not out.is_contiguous():
+    if gate_up.shape != (m, 2 * inter) or not gate_up.is_contiguous() or not out.is_contiguous() or \
+            (consume and gate_up.dtype != torch.float32) or (not consume and gate_up.dtype != out.dtype):
         raise KernelError("silu_mul: shapes or dtypes do not fit")
     lib = build.load_library("elementwise")
-    _check(lib, lib.tllm_silu_mul(_ptr(gate_up), _ptr(out), m, inter, block, _code(out.dtype), _stream()))
+    _check(lib, lib.tllm_silu_mul(_ptr(gate_up), _ptr(out), m, inter, block, _code(gate_up.dtype), _code(out.dtype),
+                                  1 if consume else 0, _stream()))
 
 
 def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, cos: Optional[torch.Tensor],
                   sin: Optional[torch.Tensor], rot_dim: int, num_heads: int, num_kv_heads: int, head_dim: int,
                   k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
-                  slot_mapping: Optional[torch.Tensor]) -> None:
+                  slot_mapping: Optional[torch.Tensor], src: Optional[torch.Tensor] = None) -> None:
     """Rotates the queries of `qkv` in place; rotates the keys and writes keys and values into the
-    pages at slot_mapping (None: the row holds queries only and nothing is written)."""
-    _need_cuda(qkv, positions, cos, sin, k_cache, v_cache, slot_mapping)
+    pages at slot_mapping (None: the row holds queries only and nothing is written).
+    `src`: float32 rows to read instead of `qkv` (a split-K accumulation buffer, handed back zeroed);
+    the rotated queries still go to `qkv`."""
+    _need_cuda(qkv, positions, cos, sin, k_cache, v_cache, slot_mapping, src)
+    if src is not None and (src.dtype != torch.float32 or src.shape != qkv.shape or src.stride(1) != 1):
+        raise KernelError("rope_kv_write: the float32 source must have the shape of qkv")
     _i32(positions, "positions")
     _i32(slot_mapping, "slot_mapping")
     t, width = qkv.shape
@@ -122,7 +139,8 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, cos: Optional[torc
         raise KernelError("rope_kv_write: rotary tables do not fit")
     lib = build.load_library("elementwise")
     _check(lib, lib.tllm_rope_kv_write(
-        _ptr(qkv), _ptr(positions), _ptr(cos), _ptr(sin), rot_dim, t, num_heads, num_kv_heads, head_dim,
+        _ptr(qkv), _ptr(src), 0 if src is None else src.stride(0), _ptr(positions), _ptr(cos), _ptr(sin), rot_dim, t,
+        num_heads, num_kv_heads, head_dim,
         qkv.stride(0), _ptr(k_cache if slot_mapping is not None else None),
         _ptr(v_cache if slot_mapping is not None else None), _ptr(slot_mapping), page_size,
         ctypes.c_longlong(page_stride), ctypes.c_longlong(head_stride), _code(qkv.dtype), _stream()))
@@ -134,6 +152,7 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, cos: Optional[torc
 EPI_BF16, EPI_F32, EPI_ADD_F32, EPI_SWIGLU, EPI_ATOMIC_F32 = 0, 1, 2, 3, 4
 SM_COUNT = 148
 force_generic = False   # tests set this to compare the tensor-core kernels with the SIMT ones
+split_k = os.environ.get("TLLM_SPLIT_K", "1") != "0"   # slices of K at decode (a switch for measurements)
 _status = {}
 
 
@@ -164,12 +183,20 @@ def _tc_ok(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
 def _swap_splits(n: int, k: int, atomic_ok: bool) -> int:
     """How many slices of K a weight tile of 128 rows is cut into at decode: enough CTAs to have
     every SM stream weights, but at least four 64-wide blocks per slice."""
-    if not atomic_ok:
+    if not atomic_ok or not split_k:
         return 1
     row_tiles = -(-n // 128)
     k_blocks = -(-k // 64)
     want = -(-SM_COUNT // row_tiles)
     return max(1, min(want, k_blocks // 4))
+
+
+def prefers_split(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """True when `linear` would cut K into slices for this product if it may add into a float32
+    output: few rows (decode), so few weight tiles that the SMs only fill when K is split too.
+    A caller that wants a bfloat16 result then accumulates into a zeroed float32 buffer and lets the
+    next kernel convert (silu_mul / rope_kv_write with consume/src)."""
+    return _tc_ok(a, w, None) and a.shape[0] <= 128 and _swap_splits(w.shape[0], a.shape[1], True) > 1
 
 
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
@@ -222,6 +249,11 @@ def linear_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, b
         _check(lib, lib.tllm_linear_tc(_ptr(a), _ptr(w_gate_up), _ptr(out), m, n2, a.shape[1], a.stride(0),
                                        out.stride(0), EPI_SWIGLU, 0, 1, _ptr(status_word(a.device)), _stream()))
         return
+    if prefers_split(a, w_gate_up):
+        acc = workspace.get_zeroed("gate_up_f32", (m, n2))
+        linear(a, w_gate_up, acc, accumulate=True)
+        silu_mul(acc, out, block, consume=True)
+        return
     gu = workspace.get("gate_up", (m, n2), a.dtype)
     linear(a, w_gate_up, gu)
     silu_mul(gu, out, block)
@@ -230,12 +262,17 @@ def linear_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, b
 # ----------------------------------------------------------------------------- attention
 
 
-def _attention_splits(tiles: int, max_kv_len: int) -> int:
-    """Slices of keys per (request, key/value head) so that a small batch still fills the SMs;
-    a slice is at least four 64-key tiles."""
-    if tiles >= SM_COUNT:
+def _attention_splits(num_requests: int, max_q_len: int, group: int, num_kv_heads: int, max_kv_len: int) -> int:
+    """Slices of keys per (request, key/value head).  Decoded tokens (at most 16 rows) run as small
+    CTAs of which three share an SM: about that many are wanted, each with at least two 64-key
+    tiles.  Portions of prompts are sliced only when there are fewer CTAs than SMs."""
+    if max_q_len * group <= 16:
+        ctas = num_requests * num_kv_heads
+        return max(1, min(-(-3 * SM_COUNT // ctas), max_kv_len // 128))
+    ctas = num_requests * (-(-max_q_len * group // 64)) * num_kv_heads
+    if ctas >= SM_COUNT:
         return 1
-    return max(1, min(-(-2 * SM_COUNT // tiles), max_kv_len // 256))
+    return max(1, min(-(-2 * SM_COUNT // ctas), max_kv_len // 256))
 
 
 def paged_attention(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, k_cache: torch.Tensor,
@@ -258,8 +295,9 @@ def paged_attention(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_d
             qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0:
         lib = build.load_library("attention_mma", flags=(f"-DTLLM_HEAD_DIM={head_dim}",))
         group = num_heads // num_kv_heads
-        tiles = batch.num_requests * (-(-batch.max_q_len * group // 64)) * num_kv_heads
-        splits = _attention_splits(tiles, batch.max_kv_len) if workspace is not None else 1
+        splits = 1
+        if workspace is not None:
+            splits = _attention_splits(batch.num_requests, batch.max_q_len, group, num_kv_heads, batch.max_kv_len)
         scratch = None
         if splits > 1:
             scratch = workspace.get("attention_partials", (t * num_heads * splits * (head_dim + 2),), torch.float32)

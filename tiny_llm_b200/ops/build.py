@@ -115,8 +115,14 @@ def load_library(name: str, extra_headers=(), flags=()) -> ctypes.CDLL:
         if lib is None:
             lib = ctypes.CDLL(compile_library(name, extra_headers, flags))
             lib.tllm_last_error.restype = ctypes.c_char_p
+            lib.tllm_set_pdl(1 if _pdl_default() else 0)
             _loaded[key] = lib
         return lib
+
+
+def _pdl_default() -> bool:
+    from .. import ops
+    return ops._pdl and os.environ.get("TLLM_PDL", "1") != "0"
 
 
 def loaded_libraries():

@@ -64,9 +64,15 @@ class GQAttention:
     def forward(self, ctx, h, resid, cache) -> None:
         t = h.shape[0]
         qkv = ctx.workspace.get("qkv", (t, self.qkv_dim), ctx.dtype)
-        ops.linear(h, self.w_qkv, qkv)
         pos = self.position
         fused = getattr(pos, "fused", False)
+        acc = None
+        if fused and ops.prefers_split(h, self.w_qkv):
+            # few rows: K is split over the SMs into a zeroed float32 buffer that the rotate-and-cache kernel consumes
+            acc = ctx.workspace.get_zeroed("qkv_f32", (t, self.qkv_dim))
+            ops.linear(h, self.w_qkv, acc, accumulate=True)
+        else:
+            ops.linear(h, self.w_qkv, qkv)
         if not fused:
             q = qkv[:, : self.q_dim].view(t, self.num_heads, self.head_dim)
             k = None if self.shares_cache else \
@@ -76,7 +82,7 @@ class GQAttention:
             qkv, ctx.batch.positions,
             pos.cos if fused else None, pos.sin if fused else None, pos.rot_dim if fused else 0,
             self.num_heads, self.num_kv_heads, self.head_dim,
-            cache.k, cache.v, None if self.shares_cache else cache.slot_mapping)
+            cache.k, cache.v, None if self.shares_cache else cache.slot_mapping, src=acc)
         out = ctx.workspace.get("attn_out", (t, self.q_dim), ctx.dtype)
         ops.paged_attention(qkv, self.num_heads, self.num_kv_heads, self.head_dim, cache.k, cache.v,
                             cache.block_table, ctx.batch, out, self.scale, self.window, ctx.workspace)
