@@ -298,3 +298,40 @@ extern "C" int tllm_sample(const float* logits, float* work, int n, int v, const
   TLLM_LAUNCH("sample", sample_kernel, n, ST, 0, (cudaStream_t)stream, logits, work, v, temperature, top_k, top_p, seeds, counters, out);
   return TLLM_OK;
 }
+
+// ---------------------------------------------------------------- sampling without a caller's scratch
+// See sampling_noalloc.h.  The scratch of the sampling kernel lives in this file-scope device array.
+// In host code `g_noalloc_scratch` is only a handle for the symbol, not an address the GPU can use:
+// its device address is looked up once per device with cudaGetSymbolAddress and kept here.
+#include "sampling_noalloc.h"
+
+static __device__ __align__(256) float g_noalloc_scratch[TLLM_SAMPLE_NOALLOC_MAX_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {};   // device address of the array, per device ordinal
+}  // namespace
+
+extern "C" int tllm_sample_noalloc(const float* logits, int n, int v, const float* temperature, const int* top_k,
+                                   const float* top_p, const unsigned long long* seeds,
+                                   const unsigned long long* counters, int* out, void* stream) {
+  TLLM_REQUIRE(n > 0 && v > 0, "sample_noalloc: empty input (%d rows of %d)", n, v);
+  TLLM_REQUIRE((long long)n * v <= (long long)TLLM_SAMPLE_NOALLOC_MAX_FLOATS,
+               "sample_noalloc: %d rows of %d logits need %lld floats of scratch, the built-in array holds %d; "
+               "use tllm_sample with scratch of your own", n, v, (long long)n * v, TLLM_SAMPLE_NOALLOC_MAX_FLOATS);
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) TLLM_FAIL(TLLM_ERR_CUDA, "sample_noalloc: cudaGetDevice: %s", cudaGetErrorString(e));
+  TLLM_REQUIRE(dev >= 0 && dev < kMaxDevices, "sample_noalloc: device ordinal %d is out of range", dev);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    // set-up, once per device, with that device current: must happen outside of stream capture
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      TLLM_FAIL(TLLM_ERR_CUDA, "sample_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    g_noalloc_ptr[dev] = p;
+  }
+  TLLM_LAUNCH("sample_noalloc", sample_kernel, n, ST, 0, (cudaStream_t)stream, logits, g_noalloc_ptr[dev], v,
+              temperature, top_k, top_p, seeds, counters, out);
+  return TLLM_OK;
+}

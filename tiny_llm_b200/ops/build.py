@@ -22,6 +22,7 @@ CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-shared", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 HEADERS = ["common.cuh"]
+EXTRA_HEADERS = {"sampling": ["sampling_noalloc.h"]}   # per-source headers that enter the hash
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
@@ -56,7 +57,7 @@ def build_dir() -> str:
 
 def _hash(source: str, extra_headers, flags) -> str:
     h = hashlib.sha256()
-    for f in [source] + list(HEADERS) + list(extra_headers):
+    for f in [source] + list(HEADERS) + list(EXTRA_HEADERS.get(source[:-3], [])) + list(extra_headers):
         with open(os.path.join(CSRC, f), "rb") as fh:
             h.update(f.encode() + b"\0" + fh.read())
     h.update(" ".join(ARCH_FLAGS + BASE_FLAGS + list(flags)).encode())
