@@ -58,6 +58,12 @@ __device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x in one instruction; 2^(-inf) = 0
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
@@ -109,7 +115,8 @@ attention_mma_kernel(const AttnParams p) {
   pdl_trigger();
   pdl_wait();
 
-  const int req = blockIdx.x / p.tiles_per_req, tile = blockIdx.x % p.tiles_per_req;
+  // the tiles of the latest tokens see the most keys: they are scheduled first
+  const int req = blockIdx.x / p.tiles_per_req, tile = p.tiles_per_req - 1 - blockIdx.x % p.tiles_per_req;
   const int kvh = blockIdx.y, split = blockIdx.z;
   const int group = p.nq / p.nkv;
   const int tok0 = p.cu_q[req];
@@ -158,6 +165,11 @@ attention_mma_kernel(const AttnParams p) {
   const int pos_a = start + r_a / group, pos_b = start + r_b / group;
   const bool live_a = r_a < rows_total, live_b = r_b < rows_total;
   const int lo_a = p.window > 0 ? pos_a - p.window + 1 : 0, lo_b = p.window > 0 ? pos_b - p.window + 1 : 0;
+  // what all 16 rows of this warp can see (the same for every lane); rows beyond the request's last
+  // hold zero queries and are never stored, so they need no mask of their own
+  const int wrow = row0 + warp * 16;
+  const int warp_pos_min = start + wrow / group;
+  const int warp_lo_max = p.window > 0 ? start + (wrow + 15) / group - p.window + 1 : 0;
 
   float m_a = -CUDART_INF_F, m_b = -CUDART_INF_F, l_a = 0.f, l_b = 0.f;
   float o[HD / 8][4];
@@ -197,36 +209,41 @@ attention_mma_kernel(const AttnParams p) {
       }
     }
 
-    // ---- scale, mask, running softmax in 32-bit
+    // ---- mask, running softmax in 32-bit.  Scores stay raw; the scale (times log2 e) is folded into
+    // the exponent: p = 2^(s * c - m * c).  A tile that every row of the warp sees whole skips the mask.
     const int j_base = tix * BN;
+    const float c = p.scale_log2;
+    if (!(j_base + BN - 1 <= warp_pos_min && j_base >= warp_lo_max)) {
+#pragma unroll
+      for (int i = 0; i < BN / 8; ++i) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int j = j_base + i * 8 + t4 * 2 + e;
+          if (!(live_a && j <= pos_a && j >= lo_a)) s[i][e] = -CUDART_INF_F;
+          if (!(live_b && j <= pos_b && j >= lo_b)) s[i][2 + e] = -CUDART_INF_F;
+        }
+      }
+    }
     float mx_a = -CUDART_INF_F, mx_b = -CUDART_INF_F;
 #pragma unroll
     for (int i = 0; i < BN / 8; ++i) {
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int j = j_base + i * 8 + t4 * 2 + e;
-        const bool va = live_a && j <= pos_a && j >= lo_a;
-        const bool vb = live_b && j <= pos_b && j >= lo_b;
-        s[i][e] = va ? s[i][e] * p.scale_log2 : -CUDART_INF_F;
-        s[i][2 + e] = vb ? s[i][2 + e] * p.scale_log2 : -CUDART_INF_F;
-        mx_a = fmaxf(mx_a, s[i][e]);
-        mx_b = fmaxf(mx_b, s[i][2 + e]);
-      }
+      mx_a = fmaxf(mx_a, fmaxf(s[i][0], s[i][1]));
+      mx_b = fmaxf(mx_b, fmaxf(s[i][2], s[i][3]));
     }
     mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
     mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
     mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
     mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
-    const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+    const float mn_a = fmaxf(m_a, mx_a * c), mn_b = fmaxf(m_b, mx_b * c);   // running maxima in scaled units
     const float ms_a = mn_a == -CUDART_INF_F ? 0.f : mn_a, ms_b = mn_b == -CUDART_INF_F ? 0.f : mn_b;
-    const float corr_a = exp2f(m_a - ms_a), corr_b = exp2f(m_b - ms_b);   // 0 while nothing was seen
+    const float corr_a = ex2(m_a - ms_a), corr_b = ex2(m_b - ms_b);   // 0 while nothing was seen
     m_a = mn_a; m_b = mn_b;
     float sum_a = 0.f, sum_b = 0.f;
     uint32_t pfrag[BN / 16][4];
 #pragma unroll
     for (int i = 0; i < BN / 8; ++i) {
-      const float p0 = exp2f(s[i][0] - ms_a), p1 = exp2f(s[i][1] - ms_a);
-      const float p2 = exp2f(s[i][2] - ms_b), p3 = exp2f(s[i][3] - ms_b);
+      const float p0 = ex2(fmaf(s[i][0], c, -ms_a)), p1 = ex2(fmaf(s[i][1], c, -ms_a));
+      const float p2 = ex2(fmaf(s[i][2], c, -ms_b)), p3 = ex2(fmaf(s[i][3], c, -ms_b));
       sum_a += p0 + p1;
       sum_b += p2 + p3;
       // accumulator layout of two adjacent 8-key tiles = A-operand layout of one 16-key step
@@ -347,6 +364,9 @@ attention_decode_kernel(const AttnParams p) {
   const int pos_a = start + g / group, pos_b = start + (g + 8) / group;
   const bool live_a = g < rows_total, live_b = g + 8 < rows_total;
   const int lo_a = p.window > 0 ? pos_a - p.window + 1 : 0, lo_b = p.window > 0 ? pos_b - p.window + 1 : 0;
+  // what all rows can see: keys up to the first new token's position, from the last one's window on
+  // (rows beyond the request's last hold zero queries and are never stored)
+  const int lo_max = p.window > 0 ? start + q_len - 1 - p.window + 1 : 0;
   float m_a = -CUDART_INF_F, m_b = -CUDART_INF_F, l_a = 0.f, l_b = 0.f;
   float o[HD / 8][4];
 #pragma unroll
@@ -382,34 +402,34 @@ attention_decode_kernel(const AttnParams p) {
       mma_bf16(s[1], qf[k0 / 16], b[2], b[3]);
     }
     const int j_base = tix * BN + warp * 16;
-    float mx_a = -CUDART_INF_F, mx_b = -CUDART_INF_F;
+    const float c = p.scale_log2;
+    if (!(j_base + 15 <= start && j_base >= lo_max)) {   // else every row sees these 16 keys
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
+      for (int i = 0; i < 2; ++i) {
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int j = j_base + i * 8 + t4 * 2 + e;
-        const bool va = live_a && j <= pos_a && j >= lo_a;
-        const bool vb = live_b && j <= pos_b && j >= lo_b;
-        s[i][e] = va ? s[i][e] * p.scale_log2 : -CUDART_INF_F;
-        s[i][2 + e] = vb ? s[i][2 + e] * p.scale_log2 : -CUDART_INF_F;
-        mx_a = fmaxf(mx_a, s[i][e]);
-        mx_b = fmaxf(mx_b, s[i][2 + e]);
+        for (int e = 0; e < 2; ++e) {
+          const int j = j_base + i * 8 + t4 * 2 + e;
+          if (!(live_a && j <= pos_a && j >= lo_a)) s[i][e] = -CUDART_INF_F;
+          if (!(live_b && j <= pos_b && j >= lo_b)) s[i][2 + e] = -CUDART_INF_F;
+        }
       }
     }
+    float mx_a = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+    float mx_b = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
     mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
     mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
     mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
     mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
-    const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+    const float mn_a = fmaxf(m_a, mx_a * c), mn_b = fmaxf(m_b, mx_b * c);
     const float ms_a = mn_a == -CUDART_INF_F ? 0.f : mn_a, ms_b = mn_b == -CUDART_INF_F ? 0.f : mn_b;
-    const float corr_a = exp2f(m_a - ms_a), corr_b = exp2f(m_b - ms_b);
+    const float corr_a = ex2(m_a - ms_a), corr_b = ex2(m_b - ms_b);
     m_a = mn_a; m_b = mn_b;
     uint32_t pf[4];
     float sum_a = 0.f, sum_b = 0.f;
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-      const float p0 = exp2f(s[i][0] - ms_a), p1 = exp2f(s[i][1] - ms_a);
-      const float p2 = exp2f(s[i][2] - ms_b), p3 = exp2f(s[i][3] - ms_b);
+      const float p0 = ex2(fmaf(s[i][0], c, -ms_a)), p1 = ex2(fmaf(s[i][1], c, -ms_a));
+      const float p2 = ex2(fmaf(s[i][2], c, -ms_b)), p3 = ex2(fmaf(s[i][3], c, -ms_b));
       sum_a += p0 + p1;
       sum_b += p2 + p3;
       pf[i * 2] = pack_bf16(p0, p1);
@@ -519,6 +539,7 @@ extern "C" int tllm_attention_mma(const void* q, int q_row_stride, const void* k
   TLLM_REQUIRE(hd == HD, "attention_mma: built for head size %d, called with %d", HD, hd);
   TLLM_REQUIRE(n_tokens > 0 && n_requests > 0 && max_q_len > 0 && nq > 0 && nkv > 0 && nq % nkv == 0,
                "attention_mma: %d tokens, %d requests, %d heads, %d key/value heads", n_tokens, n_requests, nq, nkv);
+  TLLM_REQUIRE(scale > 0.f, "attention_mma: the score scale must be positive (got %g)", (double)scale);
   TLLM_REQUIRE(page_size > 0 && max_blocks > 0 && window >= 0 && splits >= 1, "attention_mma: page size %d, %d blocks, window %d, %d splits", page_size, max_blocks, window, splits);
   TLLM_REQUIRE(((uintptr_t)q % 16) == 0 && (q_row_stride % 8) == 0 && ((uintptr_t)kcache % 16) == 0 && ((uintptr_t)vcache % 16) == 0 &&
                (page_stride % 8) == 0 && (head_stride % 8) == 0, "attention_mma: rows must be 16-byte aligned");

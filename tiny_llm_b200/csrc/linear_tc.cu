@@ -264,11 +264,23 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
               float g[32], u[32];
               tmem_ld32(taddr + c, g);
               tmem_ld32(taddr + BN / 2 + c, u);
-              if (m < rows_a) {
+              if (m < rows_a && n0 + c < n_out) {
                 __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)m * ldo + n0 + c;
+                if (n0 + c + 32 <= n_out && vec_ok) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j)
-                  if (n0 + c + j < n_out) dst[j] = __float2bfloat16_rn(silu_f(g[j]) * u[j]);
+                  for (int j = 0; j < 32; j += 8) {
+                    uint4 pk;
+                    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                      h[e] = __floats2bfloat162_rn(silu_f(g[j + 2 * e]) * u[j + 2 * e], silu_f(g[j + 2 * e + 1]) * u[j + 2 * e + 1]);
+                    *reinterpret_cast<uint4*>(dst + j) = pk;
+                  }
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 32; ++j)
+                    if (n0 + c + j < n_out) dst[j] = __float2bfloat16_rn(silu_f(g[j]) * u[j]);
+                }
               }
             }
           } else {
