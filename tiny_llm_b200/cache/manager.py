@@ -160,6 +160,8 @@ class CacheManager:
                 raise TypeError(f"unknown cache need {need!r}")
         self.kv_len: Dict[Hashable, int] = {}
         self._reserved: Dict[Hashable, int] = {}
+        self.birth: Dict[Hashable, int] = {}   # a number that differs between two lives of the same request id
+        self._births = 0
 
     # ---- storage
     def allocate_storage(self, dtype: torch.dtype, device) -> None:
@@ -177,6 +179,8 @@ class CacheManager:
             return None
         self.kv_len[rid] = 0
         self._reserved[rid] = 0
+        self._births += 1
+        self.birth[rid] = self._births
         for g in self.groups:
             g.tables[rid] = []
         return slot
@@ -196,13 +200,17 @@ class CacheManager:
         """Takes the pages for the next n_new tokens in every group, or none at all."""
         if n_new <= 0:
             raise ValueError("reserve needs a positive token count")
-        if not self.can_reserve(rid, n_new):
-            return False
-        for m, g in zip(self.pages_missing(rid, n_new), self.groups):
-            got = g.pool.allocate(m, rid)
-            assert got is not None
-            g.tables[rid].extend(got)
-        self._reserved[rid] = max(self._reserved[rid], n_new)
+        missing = self.pages_missing(rid, n_new)
+        if any(missing):
+            if any(m > g.pool.num_free for m, g in zip(missing, self.groups)):
+                return False
+            for m, g in zip(missing, self.groups):
+                if m:
+                    got = g.pool.allocate(m, rid)
+                    assert got is not None
+                    g.tables[rid].extend(got)
+        if n_new > self._reserved[rid]:
+            self._reserved[rid] = n_new
         return True
 
     def commit(self, rid: Hashable, n_new: int) -> None:
@@ -232,6 +240,7 @@ class CacheManager:
         self.slots.release(rid)
         del self.kv_len[rid]
         del self._reserved[rid]
+        del self.birth[rid]
 
     # ---- views for the step
     def block_table(self, group: int, rid: Hashable) -> List[int]:

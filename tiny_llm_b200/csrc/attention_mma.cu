@@ -301,20 +301,29 @@ attention_mma_kernel(const AttnParams p) {
 }
 
 // ---------------------------------------------------------------- decoded tokens
-// One thread gathers one row of the tile (keys first, then values): one page lookup, CHUNKS copies.
+// A tile is 128 rows, 64 keys then 64 values; warp w gathers rows [32 w, 32 w + 32).  Each lane looks
+// up the page of one row; the copies are then issued so that consecutive lanes fetch consecutive
+// 16-byte pieces of a row (whole 128-byte lines per instruction), the row's address coming from
+// its lane by shuffle.
 __device__ __forceinline__ void load_kv_rows(__nv_bfloat16* k_dst, __nv_bfloat16* v_dst, const int* table, int j0,
                                              int j_begin, int j_end, int kvh, const AttnParams& p) {
-  const int r = threadIdx.x & (BN - 1);
-  const bool is_v = threadIdx.x >= BN;
-  const int j = j0 + r;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = warp * 32 + lane;            // 0..63 keys, 64..127 values
+  const bool is_v = row >= BN;
+  const int j = j0 + (row & (BN - 1));
   bool ok = j >= j_begin && j <= j_end && j / p.page_size < p.max_blocks;
   const int page = ok ? table[j / p.page_size] : -1;
   ok = ok && page >= 0;
   const __nv_bfloat16* src = is_v ? p.vcache : p.kcache;
   if (ok) src += (long long)page * p.page_stride + (long long)kvh * p.head_stride + (long long)(j % p.page_size) * HD;
-  __nv_bfloat16* dst = (is_v ? v_dst : k_dst) + r * LDS;
+  __nv_bfloat16* dst = (warp < 2 ? k_dst : v_dst) + (warp & 1) * 32 * LDS;   // this warp's 32 rows
 #pragma unroll
-  for (int c = 0; c < CHUNKS; ++c) cp_async16(dst + c * 8, ok ? src + c * 8 : src, ok);
+  for (int idx = lane; idx < 32 * CHUNKS; idx += 32) {
+    const int r = idx / CHUNKS, c = idx % CHUNKS;
+    const unsigned long long a = __shfl_sync(0xffffffffu, (unsigned long long)src, r);
+    const int okr = __shfl_sync(0xffffffffu, (int)ok, r);
+    cp_async16(dst + r * LDS + c * 8, reinterpret_cast<const __nv_bfloat16*>(a) + (okr ? c * 8 : 0), okr != 0);
+  }
 }
 
 template <int STAGES>

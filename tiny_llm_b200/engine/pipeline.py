@@ -64,7 +64,7 @@ class Pipeline:
         entries = []
         sampling: List[Scheduled] = []
         for s in plan:
-            toks = s.request.tokens[s.start: s.start + s.count]
+            toks = s.request.token_slice(s.start, s.count)
             entries.append(StepEntry(s.request.rid, toks, [s.count - 1] if s.samples else []))
             if s.samples:
                 sampling.append(s)

@@ -50,6 +50,15 @@ class Request:
     def remaining(self) -> int:
         return self.num_tokens - self.num_computed
 
+    def token_slice(self, start: int, count: int) -> List[int]:
+        """Tokens [start, start + count) of prompt + generated, without joining the two lists."""
+        n = len(self.prompt)
+        if start >= n:
+            return self.generated[start - n: start - n + count]
+        if start + count <= n:
+            return self.prompt[start: start + count]
+        return self.prompt[start:] + self.generated[: start + count - n]
+
 
 @dataclass
 class Scheduled:

@@ -142,6 +142,7 @@ class ModelRunner:
         self.use_graphs = self.device.type == "cuda" and getattr(model, "graph_safe", False)
         self._graphs = {}
         self._graph_seen = set()
+        self._table_rows = {}
         self.graph_replays = 0
 
     # ---- metadata
@@ -190,6 +191,8 @@ class ModelRunner:
             self._staging_done[slot].synchronize()   # the copy that last read this buffer has finished
         host_meta = self._staging[slot]
         host = host_meta.numpy()
+        if t == r:
+            return self._build_decode_batch(entries, starts, host_meta, host, slot)
         tok = self._region(host, "tokens", t)
         pos = self._region(host, "positions", t)
         req = self._region(host, "token_request", t)
@@ -251,6 +254,82 @@ class ModelRunner:
             slots=self._region(dev, "slots", r), logit_rows=self._region(dev, "logit_rows", n_out),
             groups=groups, max_q_len=max(q_lens), max_kv_len=max(kv_after),
             host_q_lens=q_lens, host_kv_lens=kv_after)
+
+    def _table_row(self, gi: int, rid, table: List[int]) -> np.ndarray:
+        """The request's block table as a cached int32 row of max_blocks entries (-1 beyond its pages)."""
+        key = (gi, rid)
+        held = self._table_rows.get(key)
+        if held is None:
+            if len(self._table_rows) > 8 * self.max_requests_per_step:   # rows of requests that have ended
+                live = {(g, rid2) for g in range(len(self.cache.groups)) for rid2 in self.cache.kv_len}
+                self._table_rows = {k: v for k, v in self._table_rows.items() if k in live}
+            held = [np.full(self.max_blocks, -1, dtype=np.int32), 0, -1]
+            self._table_rows[key] = held
+        row, n, birth = held
+        if birth != self.cache.birth[rid]:   # another life of this request id: its pages are others
+            row[:] = -1
+            n = 0
+            held[2] = self.cache.birth[rid]
+        if n != len(table):
+            row[n: len(table)] = table[n:]
+            held[1] = len(table)
+        return row
+
+    def _build_decode_batch(self, entries, starts, host_meta, host, slot) -> StepBatch:
+        """The common step: every request brings one token.  Same layout as the general path, filled
+        with whole-array writes; block tables come from rows cached per request."""
+        cache = self.cache
+        r = len(entries)
+        starts_np = np.asarray(starts, dtype=np.int64)
+        self._region(host, "tokens", r)[:] = [e.tokens[0] for e in entries]
+        self._region(host, "positions", r)[:] = starts_np
+        self._region(host, "token_request", r)[:] = np.arange(r)
+        self._region(host, "cu_q", r + 1)[:] = np.arange(r + 1)
+        self._region(host, "q_start", r)[:] = starts_np
+        self._region(host, "kv_len", r)[:] = starts_np + 1
+        self._region(host, "slots", r)[:] = [cache.slot_of(e.rid) for e in entries]
+        rows = [i for i, e in enumerate(entries) if len(e.want)]
+        n_out = len(rows)
+        if n_out:
+            self._region(host, "logit_rows", n_out)[:] = rows
+        max_blocks = self.max_blocks
+        used_words = 0
+        for gi, g in enumerate(cache.groups):
+            sm = self._region(host, f"slot_mapping{gi}", r)
+            bt = self._region(host, f"block_table{gi}", r * max_blocks).reshape(r, max_blocks)
+            windowed = g.need.window is not None
+            for i, e in enumerate(entries):
+                table = cache.block_table(gi, e.rid)
+                if windowed:     # entries of a windowed group turn to -1 as the window moves: no cached row
+                    bt[i, :len(table)] = table
+                    bt[i, len(table):] = -1
+                else:
+                    bt[i] = self._table_row(gi, e.rid, table)
+            blocks = starts_np // g.page_size
+            pages = bt[np.arange(r), blocks].astype(np.int64)
+            if (pages < 0).any():
+                raise RuntimeError("a request writes into a page it has given back")
+            sm[:] = pages * g.page_size + starts_np % g.page_size
+            used_words = self._off[f"block_table{gi}"][0] + r * max_blocks
+        if not cache.groups:
+            used_words = self._off["logit_rows"][0] + self._off["logit_rows"][1]
+        self._dev_meta[:used_words].copy_(host_meta[:used_words], non_blocking=True)
+        if self.device.type == "cuda":
+            if self._staging_done[slot] is None:
+                self._staging_done[slot] = torch.cuda.Event()
+            self._staging_done[slot].record()
+        dev = self._dev_meta
+        groups = [GroupMeta(block_table=self._region(dev, f"block_table{gi}", r * max_blocks).view(r, max_blocks),
+                            slot_mapping=self._region(dev, f"slot_mapping{gi}", r), max_blocks=max_blocks)
+                  for gi in range(len(cache.groups))]
+        kv_after = [s + 1 for s in starts]
+        return StepBatch(
+            num_tokens=r, num_requests=r, num_logits=n_out,
+            tokens=self._region(dev, "tokens", r), positions=self._region(dev, "positions", r),
+            token_request=self._region(dev, "token_request", r), cu_q=self._region(dev, "cu_q", r + 1),
+            q_start=self._region(dev, "q_start", r), kv_len=self._region(dev, "kv_len", r),
+            slots=self._region(dev, "slots", r), logit_rows=self._region(dev, "logit_rows", n_out),
+            groups=groups, max_q_len=1, max_kv_len=max(kv_after), host_q_lens=[1] * r, host_kv_lens=kv_after)
 
     # ---- the step
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
