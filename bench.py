@@ -168,25 +168,32 @@ def timed_prefill(runner, tokens, repeats=5):
     return statistics.median(times)
 
 
-def timed_e2e(pipe, batch, start_len, steps, warmup):
-    """The same decode through the Python entry point: host tokens in and out every step."""
+def timed_e2e(pipe, batch, context, steps, warmup):
+    """The same decode through the Python entry point: host tokens in and out every step.  The
+    requests are admitted over several steps (the prompt budget), so they get a margin of tokens
+    that keeps all of them decoding side by side through warm-up and the timed steps; the last timed
+    step still runs within `margin` tokens of `context`."""
     import torch
     from tiny_llm_b200.sampling import SamplingParams
     g = torch.Generator().manual_seed(3)
     vocab = pipe.model.spec.vocab_size
-    params = SamplingParams(max_new_tokens=steps + warmup, do_sample=False, ignore_eos=True)
+    margin = 2 * batch + 4
+    new_tokens = steps + warmup + margin
+    params = SamplingParams(max_new_tokens=new_tokens, do_sample=False, ignore_eos=True)
     for _ in range(batch):
-        pipe.add_request(torch.randint(0, vocab, (start_len,), generator=g).tolist(), params)
+        pipe.add_request(torch.randint(0, vocab, (context - new_tokens,), generator=g).tolist(), params)
     while any(r.remaining > 1 for r in pipe.scheduler.running) or pipe.scheduler.waiting:
         pipe.step()                                  # prompts in (untimed)
-    for _ in range(warmup - 1):
+    for _ in range(warmup):
         pipe.step()
     torch.cuda.synchronize()
+    assert len(pipe.scheduler.running) == batch
     t0 = time.perf_counter()
     for _ in range(steps):
         pipe.step()
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
+    assert len(pipe.scheduler.running) == batch      # nobody ended inside the timed steps
     while pipe.has_work():
         pipe.step()
     return dt * 1e3 / steps
@@ -259,7 +266,7 @@ def main():
 
     pipe = Pipeline.from_model(cfg, model, dtype=dtype, device=0, page_size=PAGE, max_tokens=BATCH * CONTEXT,
                                max_requests=BATCH, max_tokens_per_step=2048, chunk=1024)
-    e2e_ms = timed_e2e(pipe, BATCH, start_len, steps, warmup)
+    e2e_ms = timed_e2e(pipe, BATCH, CONTEXT, steps, warmup)
     h2d = 4 * (3 * BATCH + (BATCH + 1) + 3 * BATCH + BATCH + BATCH + BATCH * pipe.runner.max_blocks)
 
     # roofline of the decode step: every weight once + the cache of the live requests

@@ -12,8 +12,16 @@ import torch
 
 from ..sampling import Sampler, SamplingParams
 from .loading import load_model, make_runner, parse_dtype
-from .scheduler import Request, Scheduled, Scheduler
+from .scheduler import PENDING, RUNNING, Request, Scheduled, Scheduler
 from .step import StepEntry
+
+
+class _Pending:
+    """The ids a step sampled that the host has not read yet: where they go in each request."""
+
+    def __init__(self, ticket, requests: List[Request], index: List[int]):
+        self.ticket, self.requests, self.index = ticket, requests, index
+        self.rids = [r.rid for r in requests]
 
 
 class Pipeline:
@@ -42,6 +50,8 @@ class Pipeline:
         self.sampler = Sampler(self.device, spec.vocab_size, max_rows=max(2, max_requests + max_requests % 2))
         self._ids = itertools.count()
         self.requests: Dict[Hashable, Request] = {}
+        self._pending: Optional[_Pending] = None
+        self.counters = {"steps": 0, "chained": 0}
 
     @classmethod
     def from_model(cls, config, model, **kwargs) -> "Pipeline":
@@ -57,27 +67,92 @@ class Pipeline:
         return rid
 
     def step(self) -> List[Request]:
-        """Plans one step, runs it, samples, and returns the requests that ended in it."""
+        """Plans one step, runs it, samples, and returns the requests that ended.
+
+        While requests only decode, steps are chained: the ids a step samples stay on the device and
+        feed the next step directly, and the host reads them one step late, while the next step already
+        runs.  A request that turns out to have sampled an end-of-sequence token has then run one step
+        too many; that step's result is dropped.  Everything else (arrivals, portions of prompts,
+        requests ending by length, pages running short) is resolved before the next plan is made."""
+        ended: List[Request] = []
+        if self._pending is not None and not self._can_chain():
+            ended += self._resolve_pending()
         plan = self.scheduler.schedule()
         if not plan:
-            return []
+            if self._pending is not None:
+                ended += self._resolve_pending()
+            return self._forget(ended)
         entries = []
         sampling: List[Scheduled] = []
         for s in plan:
             toks = s.request.token_slice(s.start, s.count)
+            if self._pending is not None:
+                toks = [0]   # the real id is still on the device
             entries.append(StepEntry(s.request.rid, toks, [s.count - 1] if s.samples else []))
             if s.samples:
                 sampling.append(s)
-        logits = self.runner.step(entries)
-        sampled = {}
+        device_tokens = None
+        if self._pending is not None:
+            if [s.request.rid for s in plan] != self._pending.rids or any(s.count != 1 for s in plan):
+                raise RuntimeError("a chained step was planned for other requests than the step before it")
+            device_tokens = self._pending.ticket.device_out
+        logits = self.runner.step(entries, device_tokens=device_tokens)
+        self.counters["steps"] += 1
+        self.counters["chained"] += device_tokens is not None
+        ticket = None
         if sampling:
-            toks = self.sampler.sample(logits, [s.request.params for s in sampling],
-                                       [len(s.request.generated) for s in sampling])
-            sampled = {s.request.rid: t for s, t in zip(sampling, toks)}
-        ended = self.scheduler.finish_step(plan, sampled)
+            ticket = self.sampler.launch(logits, [s.request.params for s in sampling],
+                                         [len(s.request.generated) for s in sampling])
+        previous = self._pending
+        finished = self.scheduler.finish_step(plan, {s.request.rid: PENDING for s in sampling})
+        self._pending = None
+        if ticket is not None:
+            self._pending = _Pending(ticket, [s.request for s in sampling],
+                                     [len(s.request.generated) - 1 for s in sampling])
+        if previous is not None:
+            ended += self._apply(previous)          # the ids of the step before: copied long ago
+        if finished:                                 # ended by length: their last id is needed now
+            ended += self._resolve_pending()
+            ended += [r for r in finished if r not in ended]
+        return self._forget(ended)
+
+    def _forget(self, ended: List[Request]) -> List[Request]:
         for r in ended:
             self.requests.pop(r.rid, None)
         return ended
+
+    def _can_chain(self) -> bool:
+        """True when the next plan is certain to be: the very requests that sampled last step, one
+        token each, nothing admitted, nothing pushed out."""
+        sched, pend = self.scheduler, self._pending
+        if sched.waiting or [r.rid for r in sched.running] != pend.rids:
+            return False
+        if any(r.remaining != 1 for r in sched.running):
+            return False
+        cache = self.runner.cache
+        need = [0] * len(cache.groups)
+        for r in sched.running:
+            for gi, m in enumerate(cache.pages_missing(r.rid, 1)):
+                need[gi] += m
+        return all(n <= g.pool.num_free for n, g in zip(need, cache.groups))
+
+    def _apply(self, pending: "_Pending") -> List[Request]:
+        """Writes a step's sampled ids where their placeholders stand; a request whose id is an
+        end-of-sequence token ends there (whatever it ran after that is dropped)."""
+        ended = []
+        for req, idx, tok in zip(pending.requests, pending.index, self.sampler.collect(pending.ticket)):
+            if idx >= len(req.generated):
+                continue   # the request ended before this id was sampled: a step too many
+            req.generated[idx] = tok
+            if req.state == RUNNING and self.scheduler.ends_sequence(req, tok):
+                del req.generated[idx + 1:]
+                self.scheduler.finish(req, "eos")
+                ended.append(req)
+        return ended
+
+    def _resolve_pending(self) -> List[Request]:
+        pending, self._pending = self._pending, None
+        return self._apply(pending) if pending is not None else []
 
     def has_work(self) -> bool:
         return self.scheduler.has_work()
@@ -96,6 +171,7 @@ class Pipeline:
             assert reqs[-1].rid == rid
         while self.has_work():
             self.step()
+        self._forget(self._resolve_pending())
         return [r.generated for r in reqs]
 
     generate = apply

@@ -25,6 +25,7 @@ from ..cache import CacheManager
 from ..sampling import SamplingParams
 
 WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
+PENDING = -1   # stands in a request's generated tokens for an id that was sampled but not read back yet
 
 
 @dataclass
@@ -179,17 +180,24 @@ class Scheduler:
             tok = sampled[req.rid]
             req.generated.append(tok)
             reason = None
-            if tok in self.eos and not req.params.ignore_eos:
+            if self.ends_sequence(req, tok):
                 reason = "eos"
             elif len(req.generated) >= req.params.max_new_tokens:
                 reason = "length"
             elif req.num_tokens >= self.max_positions:
                 reason = "positions"
             if reason:
-                req.state = FINISHED
-                req.finish_reason = reason
-                self.cache.free_request(req.rid)
-                self.running.remove(req)
-                self.counters["finished"] += 1
+                self.finish(req, reason)
                 ended.append(req)
         return ended
+
+    def ends_sequence(self, req: Request, tok: int) -> bool:
+        return tok in self.eos and not req.params.ignore_eos
+
+    def finish(self, req: Request, reason: str) -> None:
+        """The request has ended: its pages and slot go back at once."""
+        req.state = FINISHED
+        req.finish_reason = reason
+        self.cache.free_request(req.rid)
+        self.running.remove(req)
+        self.counters["finished"] += 1

@@ -179,7 +179,7 @@ class ModelRunner:
                 if not 0 <= w < n:
                     raise ValueError(f"request {e.rid!r}: wanted place {w} is outside its {n} tokens")
 
-    def build_batch(self, entries: Sequence[StepEntry]) -> StepBatch:
+    def build_batch(self, entries: Sequence[StepEntry], device_tokens=None) -> StepBatch:
         cache = self.cache
         r = len(entries)
         q_lens = [len(e.tokens) for e in entries]
@@ -192,7 +192,9 @@ class ModelRunner:
         host_meta = self._staging[slot]
         host = host_meta.numpy()
         if t == r:
-            return self._build_decode_batch(entries, starts, host_meta, host, slot)
+            return self._build_decode_batch(entries, starts, host_meta, host, slot, device_tokens)
+        if device_tokens is not None:
+            raise ValueError("token ids can stay on the device only in a step where every request brings one token")
         tok = self._region(host, "tokens", t)
         pos = self._region(host, "positions", t)
         req = self._region(host, "token_request", t)
@@ -275,7 +277,7 @@ class ModelRunner:
             held[1] = len(table)
         return row
 
-    def _build_decode_batch(self, entries, starts, host_meta, host, slot) -> StepBatch:
+    def _build_decode_batch(self, entries, starts, host_meta, host, slot, device_tokens=None) -> StepBatch:
         """The common step: every request brings one token.  Same layout as the general path, filled
         with whole-array writes; block tables come from rows cached per request."""
         cache = self.cache
@@ -319,6 +321,8 @@ class ModelRunner:
                 self._staging_done[slot] = torch.cuda.Event()
             self._staging_done[slot].record()
         dev = self._dev_meta
+        if device_tokens is not None:   # the ids were chosen on the device and have not been to the host yet
+            self._region(dev, "tokens", r).copy_(device_tokens[:r], non_blocking=True)
         groups = [GroupMeta(block_table=self._region(dev, f"block_table{gi}", r * max_blocks).view(r, max_blocks),
                             slot_mapping=self._region(dev, f"slot_mapping{gi}", r), max_blocks=max_blocks)
                   for gi in range(len(cache.groups))]
@@ -332,11 +336,14 @@ class ModelRunner:
             groups=groups, max_q_len=1, max_kv_len=max(kv_after), host_q_lens=[1] * r, host_kv_lens=kv_after)
 
     # ---- the step
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Runs exactly the tokens it is given, as one batch, from the cache earlier steps left.
         Returns float32 logits [number of wanted places, vocab] in the order of the entries and of
         their `want` lists, or None if nothing is wanted.  The returned tensor is workspace memory:
-        it is valid until the next step."""
+        it is valid until the next step.
+        `device_tokens` (int32 on the device, one id per entry, entries of one token each): the ids to
+        run instead of the entries' own, for a caller that chains steps without reading the sampled
+        ids back first."""
         cache = self.cache
         self.validate(entries)
         need = [0] * len(cache.groups)
@@ -349,7 +356,7 @@ class ModelRunner:
         for e in entries:
             ok = cache.reserve(e.rid, len(e.tokens))
             assert ok
-        batch = self.build_batch(entries)
+        batch = self.build_batch(entries, device_tokens)
         logits = self._run(entries, batch)
         for e in entries:
             cache.commit(e.rid, len(e.tokens))

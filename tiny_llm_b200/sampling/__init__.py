@@ -1,4 +1,4 @@
 from .params import SamplingParams
-from .sampler import Sampler, uniform_from
+from .sampler import Sampler, SampleTicket, uniform_from
 
-__all__ = ["SamplingParams", "Sampler", "uniform_from"]
+__all__ = ["SamplingParams", "Sampler", "SampleTicket", "uniform_from"]

@@ -22,18 +22,30 @@ def uniform_from(seed: int, counter: int) -> float:
     return (z >> 40) / 16777216.0
 
 
+class SampleTicket:
+    """A launched sampling call: the chosen ids are in `device_out` (stream-ordered) and on their
+    way to a pinned host buffer; `Sampler.collect` waits for them."""
+
+    def __init__(self, n: int, slot: int, event, device_out: torch.Tensor):
+        self.n, self.slot, self.event, self.device_out = n, slot, event, device_out
+
+
 class Sampler:
+    RING = 3   # host buffers in flight: a caller may launch the next step before it collects this one
+
     def __init__(self, device, vocab_size: int, max_rows: int = 256):
         self.device = torch.device(device)
         self.vocab_size = vocab_size
-        self.max_rows = max_rows
+        self.max_rows = max_rows + max_rows % 2   # the 64-bit regions of the block start at even words
         pin = self.device.type == "cuda"
         # one host block: temperature f32 | top_p f32 | top_k i32 | seeds i64 | counters i64, as int32 words
-        self._words = max_rows * 7
-        self._host = torch.zeros(self._words, dtype=torch.int32, pin_memory=pin)
+        self._words = self.max_rows * 7
+        self._host = [torch.zeros(self._words, dtype=torch.int32, pin_memory=pin) for _ in range(self.RING)]
+        self._host_free = [None] * self.RING      # event: the copy that last read this block has run
         self._dev = torch.zeros(self._words, dtype=torch.int32, device=self.device)
-        self._out = torch.zeros(max_rows, dtype=torch.int32, device=self.device)
-        self._out_host = torch.zeros(max_rows, dtype=torch.int32, pin_memory=pin)
+        self._out = torch.zeros(self.max_rows, dtype=torch.int32, device=self.device)
+        self._out_host = [torch.zeros(self.max_rows, dtype=torch.int32, pin_memory=pin) for _ in range(self.RING)]
+        self._next = 0
         self._work = None
 
     def _views(self, buf, n):
@@ -41,25 +53,49 @@ class Sampler:
         return (buf[0:n].view(torch.float32), buf[m:m + n].view(torch.float32), buf[2 * m:2 * m + n],
                 buf[3 * m:3 * m + 2 * n].view(torch.int64), buf[5 * m:5 * m + 2 * n].view(torch.int64))
 
-    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], counters: Sequence[int]) -> List[int]:
-        """One token per row of `logits`; `counters[i]` is how many tokens row i's request has drawn."""
+    def launch(self, logits: torch.Tensor, params: Sequence[SamplingParams], counters: Sequence[int]) -> SampleTicket:
+        """Enqueues the choice of one token per row of `logits` and its copy to the host;
+        `counters[i]` is how many tokens row i's request has drawn."""
         n = logits.shape[0]
         if n > self.max_rows:
             raise ValueError(f"{n} rows exceed the sampler's {self.max_rows}")
+        slot = self._next
+        self._next = (slot + 1) % self.RING
         out = self._out[:n]
         if all(not p.do_sample for p in params):
             ops.argmax(logits, out)
         else:
-            t, pp, k, s, c = self._views(self._host, n)
+            if self._host_free[slot] is not None:
+                self._host_free[slot].synchronize()
+            host = self._host[slot]
+            t, pp, k, s, c = self._views(host, n)
             t.numpy()[:] = [p.temperature if p.do_sample else 0.0 for p in params]
             pp.numpy()[:] = [p.top_p for p in params]
             k.numpy()[:] = [p.top_k for p in params]
             s.numpy()[:] = np.array([p.seed & 0x7FFFFFFFFFFFFFFF for p in params], dtype=np.int64)
             c.numpy()[:] = np.array(list(counters), dtype=np.int64)
-            self._dev.copy_(self._host, non_blocking=True)
+            self._dev.copy_(host, non_blocking=True)
+            if self.device.type == "cuda":
+                if self._host_free[slot] is None:
+                    self._host_free[slot] = torch.cuda.Event()
+                self._host_free[slot].record()
             if self._work is None or self._work.numel() < n * self.vocab_size:
                 self._work = torch.empty(max(n, 8) * self.vocab_size, dtype=torch.float32, device=self.device)
             dt, dpp, dk, ds, dc = self._views(self._dev, n)
             ops.sample(logits, self._work, dt, dk, dpp, ds, dc, out)
-        self._out_host[:n].copy_(out, non_blocking=False)
-        return self._out_host[:n].tolist()
+        self._out_host[slot][:n].copy_(out, non_blocking=True)
+        event = None
+        if self.device.type == "cuda":
+            event = torch.cuda.Event()
+            event.record()
+        return SampleTicket(n, slot, event, out)
+
+    def collect(self, ticket: SampleTicket) -> List[int]:
+        """Waits for a launched call's ids and returns them."""
+        if ticket.event is not None:
+            ticket.event.synchronize()
+        return self._out_host[ticket.slot][:ticket.n].tolist()
+
+    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], counters: Sequence[int]) -> List[int]:
+        """launch + collect."""
+        return self.collect(self.launch(logits, params, counters))
