@@ -157,6 +157,90 @@ struct SmemLayout {
   static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 1) * 8 + 16 + 1024;   // + alignment slack
 };
 
+// Epilogue of one 128 x BN tile of C in the NORMAL orientation: this thread owns row `row` of the
+// tile (tensor-memory lane), walks its BN columns in chunks of 32 and stores them as EPI says.
+template <int BN, int EPI>
+__device__ __forceinline__ void store_tile_normal(uint32_t taddr, int row, int tile_a, int tile_b, int rows_a,
+                                                  int rows_b, void* __restrict__ out, int ldo) {
+  // 16-byte stores need an aligned base and row stride
+  const bool vec_ok = (reinterpret_cast<uintptr_t>(out) & 15) == 0 &&
+                      ((EPI == EPI_BF16 || EPI == EPI_SWIGLU) ? (ldo & 7) == 0 : (ldo & 3) == 0);
+  const int m = tile_a * BM + row;
+  if (EPI == EPI_SWIGLU) {
+    // columns [0, BN/2) are gate, [BN/2, BN) the matching up columns; output tile is BN/2 wide
+    const int n0 = tile_b * (BN / 2);
+    const int n_out = rows_b / 2;
+#pragma unroll 1
+    for (int c = 0; c < BN / 2; c += 32) {
+      float g[32], u[32];
+      tmem_ld32(taddr + c, g);
+      tmem_ld32(taddr + BN / 2 + c, u);
+      if (m < rows_a && n0 + c < n_out) {
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)m * ldo + n0 + c;
+        if (n0 + c + 32 <= n_out && vec_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 pk;
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              h[e] = __floats2bfloat162_rn(silu_f(g[j + 2 * e]) * u[j + 2 * e], silu_f(g[j + 2 * e + 1]) * u[j + 2 * e + 1]);
+            *reinterpret_cast<uint4*>(dst + j) = pk;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (n0 + c + j < n_out) dst[j] = __float2bfloat16_rn(silu_f(g[j]) * u[j]);
+        }
+      }
+    }
+  } else {
+    const int n0 = tile_b * BN;
+#pragma unroll 1
+    for (int c = 0; c < BN; c += 32) {
+      float v[32];
+      tmem_ld32(taddr + c, v);
+      if (m < rows_a && n0 + c < rows_b) {
+        const bool full = n0 + c + 32 <= rows_b;
+        if (EPI == EPI_BF16) {
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)m * ldo + n0 + c;
+          if (full && vec_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint4 pk;
+              __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(v[j + 2 * e], v[j + 2 * e + 1]);
+              *reinterpret_cast<uint4*>(dst + j) = pk;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (n0 + c + j < rows_b) dst[j] = __float2bfloat16_rn(v[j]);
+          }
+        } else {
+          float* dst = reinterpret_cast<float*>(out) + (size_t)m * ldo + n0 + c;
+          if (full && vec_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+              if (EPI == EPI_ADD_F32) {
+                const float4 p = *reinterpret_cast<const float4*>(dst + j);
+                o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
+              }
+              *reinterpret_cast<float4*>(dst + j) = o;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (n0 + c + j < rows_b) dst[j] = EPI == EPI_ADD_F32 ? dst[j] + v[j] : v[j];
+          }
+        }
+      }
+    }
+  }
+}
+
 // rows_a / rows_b: extents of the 128-row operand and of the BN-row operand.  NORMAL: rows_a = M,
 // rows_b = N, out[M, N].  SWAP: rows_a = N (weights), rows_b = M (tokens), out[M, N] all the same.
 template <int BN, int STAGES, bool SWAP, int EPI>
@@ -250,84 +334,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       tc_fence_after();
       if (ok) {
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
-        // 16-byte stores need an aligned base and row stride
-        const bool vec_ok = (reinterpret_cast<uintptr_t>(out) & 15) == 0 &&
-                            ((EPI == EPI_BF16 || EPI == EPI_SWIGLU) ? (ldo & 7) == 0 : (ldo & 3) == 0);
         if (!SWAP) {
-          const int m = tile_a * BM + row;
-          if (EPI == EPI_SWIGLU) {
-            // columns [0, BN/2) are gate, [BN/2, BN) the matching up columns; output tile is BN/2 wide
-            const int n0 = tile_b * (BN / 2);
-            const int n_out = rows_b / 2;
-#pragma unroll 1
-            for (int c = 0; c < BN / 2; c += 32) {
-              float g[32], u[32];
-              tmem_ld32(taddr + c, g);
-              tmem_ld32(taddr + BN / 2 + c, u);
-              if (m < rows_a && n0 + c < n_out) {
-                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)m * ldo + n0 + c;
-                if (n0 + c + 32 <= n_out && vec_ok) {
-#pragma unroll
-                  for (int j = 0; j < 32; j += 8) {
-                    uint4 pk;
-                    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-                    for (int e = 0; e < 4; ++e)
-                      h[e] = __floats2bfloat162_rn(silu_f(g[j + 2 * e]) * u[j + 2 * e], silu_f(g[j + 2 * e + 1]) * u[j + 2 * e + 1]);
-                    *reinterpret_cast<uint4*>(dst + j) = pk;
-                  }
-                } else {
-#pragma unroll
-                  for (int j = 0; j < 32; ++j)
-                    if (n0 + c + j < n_out) dst[j] = __float2bfloat16_rn(silu_f(g[j]) * u[j]);
-                }
-              }
-            }
-          } else {
-            const int n0 = tile_b * BN;
-#pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-              float v[32];
-              tmem_ld32(taddr + c, v);
-              if (m < rows_a && n0 + c < rows_b) {
-                const bool full = n0 + c + 32 <= rows_b;
-                if (EPI == EPI_BF16) {
-                  __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)m * ldo + n0 + c;
-                  if (full && vec_ok) {
-#pragma unroll
-                    for (int j = 0; j < 32; j += 8) {
-                      uint4 pk;
-                      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-                      for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(v[j + 2 * e], v[j + 2 * e + 1]);
-                      *reinterpret_cast<uint4*>(dst + j) = pk;
-                    }
-                  } else {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                      if (n0 + c + j < rows_b) dst[j] = __float2bfloat16_rn(v[j]);
-                  }
-                } else {
-                  float* dst = reinterpret_cast<float*>(out) + (size_t)m * ldo + n0 + c;
-                  if (full && vec_ok) {
-#pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                      float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                      if (EPI == EPI_ADD_F32) {
-                        const float4 p = *reinterpret_cast<const float4*>(dst + j);
-                        o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
-                      }
-                      *reinterpret_cast<float4*>(dst + j) = o;
-                    }
-                  } else {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                      if (n0 + c + j < rows_b) dst[j] = EPI == EPI_ADD_F32 ? dst[j] + v[j] : v[j];
-                  }
-                }
-              }
-            }
-          }
+          store_tile_normal<BN, EPI>(taddr, row, tile_a, tile_b, rows_a, rows_b, out, ldo);
         } else {
           // SWAP: this thread's row is weight row n; tensor-memory column j is token tile_b*BN + j.
           // For a fixed token the 32 lanes of a warp write 32 consecutive n: coalesced.
@@ -353,6 +361,137 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           }
         }
       }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------- persistent kernel, NORMAL orientation
+// One CTA per SM walks the 128 x BN tiles of C (tile t, t + grid, ...; the M tiles of one N tile
+// are neighbours, so CTAs running side by side share the weight tile in L2).  Two accumulators of BN
+// columns alternate in tensor memory: while the four epilogue warps drain tile i, the MMA thread
+// already accumulates tile i + 1, and the TMA thread runs ahead of both through the ring of stages.
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+template <int BN, int STAGES>
+struct PersistentSmem {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16 + 1024;
+};
+
+template <int BN, int STAGES, int EPI>
+__global__ void __launch_bounds__(THREADS, 1)
+linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                            void* __restrict__ out, int rows_a, int rows_b, int k_blocks, int ldo,
+                            int* __restrict__ status) {
+  static_assert(2 * BN <= 512, "two accumulators must fit tensor memory");
+  using L = PersistentSmem<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* acc_full = empty_bar + STAGES;      // [2]: accumulator b holds a finished tile
+  uint64_t* acc_empty = acc_full + 2;           // [2]: the epilogue has drained accumulator b
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (rows_a + BM - 1) / BM, tiles_n = (rows_b + BN - 1) / BN;
+  const int n_tiles = tiles_m * tiles_n;
+  constexpr uint32_t TMEM_COLS = 2 * BN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // The weight operand depends on no earlier kernel: the first stages of the first tile are requested
+  // before this grid waits for its predecessors.
+  pdl_trigger();
+  const int first_tile = blockIdx.x;
+  const int n_pre = first_tile < n_tiles ? min(k_blocks, STAGES) : 0;
+  if (warp == 0 && lane == 0) {
+    const int tn = first_tile / tiles_m;
+    for (int i = 0; i < n_pre; ++i) {
+      mbar_expect_tx(&full_bar[i], L::STAGE_BYTES);
+      tma_load_2d(smem + i * L::STAGE_BYTES + L::A_BYTES, &map_b, i * BK, tn * BN, &full_bar[i]);
+    }
+  }
+  pdl_wait();
+
+  if (warp == 0 && lane == 0) {
+    // ---------------- TMA producer
+    int it = 0;   // k-blocks issued so far, over all tiles: stage = it % STAGES
+    bool ok = true;
+    for (int t = first_tile; t < n_tiles && ok; t += gridDim.x) {
+      const int tm = t % tiles_m, tn = t / tiles_m;
+      for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        const int s = it % STAGES;
+        uint8_t* a_dst = smem + s * L::STAGE_BYTES;
+        const bool pre = it < n_pre;
+        if (!pre) {
+          if (!mbar_wait(&empty_bar[s], ((it / STAGES) & 1) ^ 1, abort_flag)) { *abort_flag = 1; atomicExch(status, ERR_PRODUCER); ok = false; break; }
+          mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
+          tma_load_2d(a_dst + L::A_BYTES, &map_b, kb * BK, tn * BN, &full_bar[s]);
+        }
+        tma_load_2d(a_dst, &map_a, kb * BK, tm * BM, &full_bar[s]);
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---------------- MMA issuer
+    const uint32_t idesc = instr_desc_bf16(BN);
+    int it = 0, local = 0;
+    bool ok = true;
+    for (int t = first_tile; t < n_tiles && ok; t += gridDim.x, ++local) {
+      const int buf = local & 1;
+      if (!mbar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1, abort_flag)) { *abort_flag = 1; atomicExch(status, ERR_MMA); break; }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + buf * BN;
+      for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        const int s = it % STAGES;
+        if (!mbar_wait(&full_bar[s], (it / STAGES) & 1, abort_flag)) { *abort_flag = 1; atomicExch(status, ERR_MMA); ok = false; break; }
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(smem + s * L::STAGE_BYTES);
+        const uint32_t b_addr = a_addr + L::A_BYTES;
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k)
+          umma_bf16(d_tmem, smem_desc_sw128(a_addr + k * UMMA_K * 2), smem_desc_sw128(b_addr + k * UMMA_K * 2), idesc,
+                    (kb > 0 || k > 0) ? 1u : 0u);
+        umma_commit(&empty_bar[s]);
+      }
+      umma_commit(&acc_full[buf]);   // arrives when this tile's MMAs have completed
+    }
+  } else if (warp >= 2) {
+    // ---------------- epilogue: warp w reads tensor-memory lanes [32 (w % 4), +32)
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    int local = 0;
+    for (int t = first_tile; t < n_tiles; t += gridDim.x, ++local) {
+      const int buf = local & 1;
+      bool ok = mbar_wait(&acc_full[buf], (local >> 1) & 1, abort_flag);
+      if (!ok) { *abort_flag = 1; atomicExch(status, ERR_EPILOGUE); }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quad * 32) << 16);
+      store_tile_normal<BN, EPI>(taddr, row, t % tiles_m, t / tiles_m, rows_a, rows_b, out, ldo);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);   // four arrivals free the accumulator
     }
   }
   tc_fence_before();
@@ -421,6 +560,28 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int r
   return TLLM_OK;
 }
 
+template <int EPI>
+static int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int m, int n, int k, int ldo,
+                             int* status, cudaStream_t s) {
+  constexpr int BN = 256, STAGES = 4;
+  using L = PersistentSmem<BN, STAGES>;
+  auto kern = linear_tc_persistent_kernel<BN, STAGES, EPI>;
+  static bool configured = false;
+  static int sm_count = 0;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (e != cudaSuccess) TLLM_FAIL(TLLM_ERR_CUDA, "linear_tc: cannot reserve %d bytes of shared memory: %s", L::TOTAL, cudaGetErrorString(e));
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    configured = true;
+  }
+  const int tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
+  const int grid = tiles < sm_count ? tiles : sm_count;
+  TLLM_LAUNCH("linear_tc_persistent", kern, grid, THREADS, L::TOTAL, s, ma, mb, out, m, n, (k + BK - 1) / BK, ldo, status);
+  return TLLM_OK;
+}
+
 }  // namespace tllm
 
 using namespace tllm;
@@ -446,10 +607,10 @@ extern "C" int tllm_linear_tc(const void* a, const void* w, void* out, int m, in
     if (!make_map(&ma, a, m, k, lda, BM) || !make_map(&mb, w, n, k, k, 256))
       TLLM_FAIL(TLLM_ERR_CUDA, "linear_tc: cuTensorMapEncodeTiled failed");
     switch (epi) {
-      case EPI_BF16: return launch<256, 4, false, EPI_BF16>(ma, mb, out, m, n, k, 1, ldo, status, s);
-      case EPI_F32: return launch<256, 4, false, EPI_F32>(ma, mb, out, m, n, k, 1, ldo, status, s);
-      case EPI_ADD_F32: return launch<256, 4, false, EPI_ADD_F32>(ma, mb, out, m, n, k, 1, ldo, status, s);
-      case EPI_SWIGLU: return launch<256, 4, false, EPI_SWIGLU>(ma, mb, out, m, n, k, 1, ldo, status, s);
+      case EPI_BF16: return launch_persistent<EPI_BF16>(ma, mb, out, m, n, k, ldo, status, s);
+      case EPI_F32: return launch_persistent<EPI_F32>(ma, mb, out, m, n, k, ldo, status, s);
+      case EPI_ADD_F32: return launch_persistent<EPI_ADD_F32>(ma, mb, out, m, n, k, ldo, status, s);
+      case EPI_SWIGLU: return launch_persistent<EPI_SWIGLU>(ma, mb, out, m, n, k, ldo, status, s);
     }
     TLLM_FAIL(TLLM_ERR_ARG, "linear_tc: unknown epilogue %d", epi);
   }
