@@ -84,23 +84,28 @@ struct AttnParams {
   float scale_log2;              // scale * log2(e)
 };
 
-// Gathers keys (or values) [j0, j0 + BN) of the request into a shared tile; rows outside
-// [j_begin, j_end] are zero and their pages are not touched (a window may have given them back).
-template <int WARPS>
-__device__ __forceinline__ void load_kv_tile(__nv_bfloat16* dst, const __nv_bfloat16* cache, const int* table,
-                                             int j0, int j_begin, int j_end, int kvh, const AttnParams& p) {
-  for (int idx = threadIdx.x; idx < BN * CHUNKS; idx += WARPS * 32) {
+// A tile is 128 rows, 64 keys then 64 values; warp w gathers rows [32 w, 32 w + 32).  Each lane looks
+// up the page of one row; the copies are then issued so that consecutive lanes fetch consecutive
+// 16-byte pieces of a row (whole 128-byte lines per instruction), the row's address coming from
+// its lane by shuffle.
+__device__ __forceinline__ void load_kv_rows(__nv_bfloat16* k_dst, __nv_bfloat16* v_dst, const int* table, int j0,
+                                             int j_begin, int j_end, int kvh, const AttnParams& p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = warp * 32 + lane;            // 0..63 keys, 64..127 values
+  const bool is_v = row >= BN;
+  const int j = j0 + (row & (BN - 1));
+  bool ok = j >= j_begin && j <= j_end && j / p.page_size < p.max_blocks;
+  const int page = ok ? table[j / p.page_size] : -1;
+  ok = ok && page >= 0;
+  const __nv_bfloat16* src = is_v ? p.vcache : p.kcache;
+  if (ok) src += (long long)page * p.page_stride + (long long)kvh * p.head_stride + (long long)(j % p.page_size) * HD;
+  __nv_bfloat16* dst = (warp < 2 ? k_dst : v_dst) + (warp & 1) * 32 * LDS;   // this warp's 32 rows
+#pragma unroll
+  for (int idx = lane; idx < 32 * CHUNKS; idx += 32) {
     const int r = idx / CHUNKS, c = idx % CHUNKS;
-    const int j = j0 + r;
-    bool ok = j >= j_begin && j <= j_end && j / p.page_size < p.max_blocks;
-    const __nv_bfloat16* src = cache;
-    const int page = ok ? table[j / p.page_size] : -1;
-    ok = ok && page >= 0;   // a table entry that names no page is never followed
-    if (ok) {
-      src = cache + (long long)page * p.page_stride + (long long)kvh * p.head_stride +
-            (long long)(j % p.page_size) * HD + c * 8;
-    }
-    cp_async16(dst + r * LDS + c * 8, src, ok);
+    const unsigned long long a = __shfl_sync(0xffffffffu, (unsigned long long)src, r);
+    const int okr = __shfl_sync(0xffffffffu, (int)ok, r);
+    cp_async16(dst + r * LDS + c * 8, reinterpret_cast<const __nv_bfloat16*>(a) + (okr ? c * 8 : 0), okr != 0);
   }
 }
 
@@ -108,6 +113,7 @@ template <int WARPS, int STAGES>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_mma_kernel(const AttnParams p) {
   constexpr int BM = WARPS * 16;   // rows per CTA
+  static_assert(WARPS == 4, "the tile loader gives one row of keys or values to each of 128 threads");
   extern __shared__ __align__(16) uint8_t smem_raw[];
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   __nv_bfloat16* k_s = q_s + BM * LDS;                 // STAGES tiles
@@ -153,10 +159,8 @@ attention_mma_kernel(const AttnParams p) {
   // prologue: the first STAGES - 1 tiles are requested; every stage is one commit group, empty or not
 #pragma unroll
   for (int st = 0; st < STAGES - 1; ++st) {
-    if (t_begin + st < t_end) {
-      load_kv_tile<WARPS>(k_s + st * BN * LDS, p.kcache, table, (t_begin + st) * BN, key_lo, key_hi, kvh, p);
-      load_kv_tile<WARPS>(v_s + st * BN * LDS, p.vcache, table, (t_begin + st) * BN, key_lo, key_hi, kvh, p);
-    }
+    if (t_begin + st < t_end)
+      load_kv_rows(k_s + st * BN * LDS, v_s + st * BN * LDS, table, (t_begin + st) * BN, key_lo, key_hi, kvh, p);
     cp_async_commit();
   }
 
@@ -186,8 +190,7 @@ attention_mma_kernel(const AttnParams p) {
       const int nxt = tix + STAGES - 1;
       if (nxt < t_end) {
         const int ns = (nxt - t_begin) % STAGES;
-        load_kv_tile<WARPS>(k_s + ns * BN * LDS, p.kcache, table, nxt * BN, key_lo, key_hi, kvh, p);
-        load_kv_tile<WARPS>(v_s + ns * BN * LDS, p.vcache, table, nxt * BN, key_lo, key_hi, kvh, p);
+        load_kv_rows(k_s + ns * BN * LDS, v_s + ns * BN * LDS, table, nxt * BN, key_lo, key_hi, kvh, p);
       }
       cp_async_commit();
     }
@@ -301,31 +304,6 @@ attention_mma_kernel(const AttnParams p) {
 }
 
 // ---------------------------------------------------------------- decoded tokens
-// A tile is 128 rows, 64 keys then 64 values; warp w gathers rows [32 w, 32 w + 32).  Each lane looks
-// up the page of one row; the copies are then issued so that consecutive lanes fetch consecutive
-// 16-byte pieces of a row (whole 128-byte lines per instruction), the row's address coming from
-// its lane by shuffle.
-__device__ __forceinline__ void load_kv_rows(__nv_bfloat16* k_dst, __nv_bfloat16* v_dst, const int* table, int j0,
-                                             int j_begin, int j_end, int kvh, const AttnParams& p) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row = warp * 32 + lane;            // 0..63 keys, 64..127 values
-  const bool is_v = row >= BN;
-  const int j = j0 + (row & (BN - 1));
-  bool ok = j >= j_begin && j <= j_end && j / p.page_size < p.max_blocks;
-  const int page = ok ? table[j / p.page_size] : -1;
-  ok = ok && page >= 0;
-  const __nv_bfloat16* src = is_v ? p.vcache : p.kcache;
-  if (ok) src += (long long)page * p.page_stride + (long long)kvh * p.head_stride + (long long)(j % p.page_size) * HD;
-  __nv_bfloat16* dst = (warp < 2 ? k_dst : v_dst) + (warp & 1) * 32 * LDS;   // this warp's 32 rows
-#pragma unroll
-  for (int idx = lane; idx < 32 * CHUNKS; idx += 32) {
-    const int r = idx / CHUNKS, c = idx % CHUNKS;
-    const unsigned long long a = __shfl_sync(0xffffffffu, (unsigned long long)src, r);
-    const int okr = __shfl_sync(0xffffffffu, (int)ok, r);
-    cp_async16(dst + r * LDS + c * 8, reinterpret_cast<const __nv_bfloat16*>(a) + (okr ? c * 8 : 0), okr != 0);
-  }
-}
-
 template <int STAGES>
 __global__ void __launch_bounds__(128)
 attention_decode_kernel(const AttnParams p) {

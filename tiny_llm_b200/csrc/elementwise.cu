@@ -45,6 +45,51 @@ __global__ void rms_norm_kernel(const float* __restrict__ x, const float* __rest
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = from_f32<T>((w[i] * src[i]) / denom);
 }
 
+__device__ __forceinline__ void store4(float* p, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float a, float b, float c, float d) {
+  uint2 pk;
+  *reinterpret_cast<__nv_bfloat162*>(&pk.x) = __floats2bfloat162_rn(a, b);
+  *reinterpret_cast<__nv_bfloat162*>(&pk.y) = __floats2bfloat162_rn(c, d);
+  *reinterpret_cast<uint2*>(p) = pk;
+}
+
+// The same for widths that are multiples of 4 and at most 4 * VEC * blockDim: the row is read once,
+// with 16-byte loads, and kept in registers between the two passes.
+template <typename T, int VEC>
+__global__ void rms_norm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                    T* __restrict__ out, const int* __restrict__ rows, int n_rows,
+                                    int hidden, float eps) {
+  __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x;
+  if (r >= n_rows) return;
+  const float4* src = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * hidden);
+  const int n4 = hidden / 4;
+  float4 v[VEC];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    const int idx = threadIdx.x + i * blockDim.x;
+    v[i] = idx < n4 ? src[idx] : make_float4(0.f, 0.f, 0.f, 0.f);
+    ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+  }
+  ss = block_sum(ss, scratch);
+  const float denom = sqrtf(ss / (float)hidden + eps);
+  T* dst = out + (size_t)r * hidden;
+  const float4* w4 = reinterpret_cast<const float4*>(w);
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    const int idx = threadIdx.x + i * blockDim.x;
+    if (idx < n4) {
+      const float4 g = w4[idx];
+      store4(dst + 4 * idx, (g.x * v[i].x) / denom, (g.y * v[i].y) / denom, (g.z * v[i].z) / denom, (g.w * v[i].w) / denom);
+    }
+  }
+}
+
 // ---------------------------------------------------------------- SiLU(gate) * up
 // `gu` rows hold gate and up interleaved in blocks: [2 g B, 2 g B + B) gate, next B up.  With
 // ZERO the source is a float32 accumulation buffer (split-K partial sums land there) that this
@@ -128,6 +173,91 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, float* __restrict__ sr
   }
 }
 
+// ---- the same with 16-byte accesses, for head sizes that are multiples of 16 and aligned rows:
+// one thread rotates eight consecutive pairs (i, i + hd/2).
+__device__ __forceinline__ void load8(const float* p, float* v) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float* v) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+}
+__device__ __forceinline__ void store8(float* p, const float* v) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float* v) {
+  uint4 u;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+
+template <typename T>
+__global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, float* __restrict__ src, int src_stride,
+                                         const int* __restrict__ positions,
+                                         const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                         int n_tokens, int nq, int nkv, int hd, int row_stride,
+                                         T* __restrict__ kcache, T* __restrict__ vcache,
+                                         const int* __restrict__ slot_mapping, int page_size,
+                                         long long page_stride, long long head_stride) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  if (t >= n_tokens) return;
+  const int pos = positions[t];
+  T* row = qkv + (size_t)t * row_stride;
+  float* srow = src ? src + (size_t)t * src_stride : nullptr;
+  const bool write_kv = slot_mapping != nullptr;
+  const int heads = write_kv ? nq + nkv : nq;
+  const int half_hd = hd / 2, groups = half_hd / 8;   // groups of eight pairs per head
+  long long slot_base = 0;
+  if (write_kv) {
+    const int slot = slot_mapping[t];
+    if (slot < 0) return;
+    slot_base = (long long)(slot / page_size) * page_stride + (long long)(slot % page_size) * hd;
+  }
+  const float zeros[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int idx = threadIdx.x; idx < heads * groups; idx += blockDim.x) {
+    const int h = idx / groups, i = (idx % groups) * 8;
+    const int e = h * hd + i;
+    float va[8], vb[8], oa[8], ob[8];
+    if (srow) {
+      load8(srow + e, va); load8(srow + e + half_hd, vb);
+      store8(srow + e, zeros); store8(srow + e + half_hd, zeros);
+    } else {
+      load8(row + e, va); load8(row + e + half_hd, vb);
+    }
+    if (cos_t) {
+      float c[8], sn[8];
+      load8(cos_t + (size_t)pos * half_hd + i, c);
+      load8(sin_t + (size_t)pos * half_hd + i, sn);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { oa[j] = c[j] * va[j] - sn[j] * vb[j]; ob[j] = sn[j] * va[j] + c[j] * vb[j]; }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { oa[j] = va[j]; ob[j] = vb[j]; }
+    }
+    T* dst = h < nq ? row + (size_t)h * hd : kcache + slot_base + (long long)(h - nq) * head_stride;
+    store8(dst + i, oa);
+    store8(dst + i + half_hd, ob);
+  }
+  if (write_kv) {
+    const int v0 = (nq + nkv) * hd;
+    for (int idx = threadIdx.x; idx < nkv * hd / 8; idx += blockDim.x) {
+      const int h = (idx * 8) / hd, i = (idx * 8) % hd;
+      float v[8];
+      if (srow) { load8(srow + v0 + idx * 8, v); store8(srow + v0 + idx * 8, zeros); }
+      else load8(row + v0 + idx * 8, v);
+      store8(vcache + slot_base + (long long)h * head_stride + i, v);
+    }
+  }
+}
+
 }  // namespace tllm
 
 using namespace tllm;
@@ -149,14 +279,31 @@ extern "C" int tllm_embedding(const int* tokens, const void* table, float* out, 
 extern "C" int tllm_rms_norm(const float* x, const float* w, void* out, const int* rows, int n_rows, int hidden,
                              float eps, int out_dtype, void* stream) {
   TLLM_REQUIRE(n_rows > 0 && hidden > 0, "rms_norm: empty input (%d rows, width %d)", n_rows, hidden);
-  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  TLLM_REQUIRE(out_dtype == TLLM_F32 || out_dtype == TLLM_BF16, "rms_norm: unknown dtype code %d", out_dtype);
   cudaStream_t s = (cudaStream_t)stream;
+  const bool aligned = hidden % 4 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0 && ((uintptr_t)out % 16) == 0;
+  if (aligned && hidden <= 4 * 4 * 256) {
+    // 128 or 256 threads, up to four 16-byte loads each
+    const int n4 = hidden / 4;
+    const int threads = n4 <= 128 * 4 ? 128 : 256;
+    const int vec = (n4 + threads - 1) / threads;
+#define TLLM_NORM_CASE(V)                                                                                                   \
+  if (out_dtype == TLLM_F32)                                                                                               \
+    TLLM_LAUNCH("rms_norm", (rms_norm_vec_kernel<float, V>), n_rows, threads, 0, s, x, w, (float*)out, rows, n_rows, hidden, eps); \
+  else                                                                                                                     \
+    TLLM_LAUNCH("rms_norm", (rms_norm_vec_kernel<__nv_bfloat16, V>), n_rows, threads, 0, s, x, w, (__nv_bfloat16*)out, rows, n_rows, hidden, eps); \
+  return TLLM_OK;
+    if (vec <= 1) { TLLM_NORM_CASE(1) }
+    if (vec == 2) { TLLM_NORM_CASE(2) }
+    if (vec == 3) { TLLM_NORM_CASE(3) }
+    { TLLM_NORM_CASE(4) }
+#undef TLLM_NORM_CASE
+  }
+  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
   if (out_dtype == TLLM_F32)
     TLLM_LAUNCH("rms_norm", rms_norm_kernel<float>, n_rows, threads, 0, s, x, w, (float*)out, rows, n_rows, hidden, eps);
-  else if (out_dtype == TLLM_BF16)
-    TLLM_LAUNCH("rms_norm", rms_norm_kernel<__nv_bfloat16>, n_rows, threads, 0, s, x, w, (__nv_bfloat16*)out, rows, n_rows, hidden, eps);
   else
-    TLLM_FAIL(TLLM_ERR_ARG, "rms_norm: unknown dtype code %d", out_dtype);
+    TLLM_LAUNCH("rms_norm", rms_norm_kernel<__nv_bfloat16>, n_rows, threads, 0, s, x, w, (__nv_bfloat16*)out, rows, n_rows, hidden, eps);
   return TLLM_OK;
 }
 
@@ -197,6 +344,22 @@ extern "C" int tllm_rope_kv_write(void* qkv, float* src, int src_stride, const i
   cudaStream_t s = (cudaStream_t)stream;
   const float* c = rot_dim ? cos_t : nullptr;
   const float* sn = rot_dim ? sin_t : nullptr;
+  const int esz = dtype == TLLM_F32 ? 4 : 2;
+  const bool vec = hd % 16 == 0 && ((uintptr_t)qkv % 16) == 0 && ((long long)row_stride * esz) % 16 == 0 &&
+                   (!src || (((uintptr_t)src % 16) == 0 && src_stride % 4 == 0)) &&
+                   (!slot_mapping || (((uintptr_t)kcache % 16) == 0 && ((uintptr_t)vcache % 16) == 0 &&
+                                      (page_stride * esz) % 16 == 0 && (head_stride * esz) % 16 == 0)) &&
+                   (!c || (((uintptr_t)c % 16) == 0 && ((uintptr_t)sn % 16) == 0));
+  if (vec) {
+    const int vthreads = (nq + nkv) * (hd / 16) >= 256 ? 256 : 128;
+    if (dtype == TLLM_F32)
+      TLLM_LAUNCH("rope_kv_write", rope_kv_write_vec_kernel<float>, n_tokens, vthreads, 0, s, (float*)qkv, src, src_stride, positions, c, sn, n_tokens, nq, nkv, hd, row_stride, (float*)kcache, (float*)vcache, slot_mapping, page_size, page_stride, head_stride);
+    else if (dtype == TLLM_BF16)
+      TLLM_LAUNCH("rope_kv_write", rope_kv_write_vec_kernel<__nv_bfloat16>, n_tokens, vthreads, 0, s, (__nv_bfloat16*)qkv, src, src_stride, positions, c, sn, n_tokens, nq, nkv, hd, row_stride, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, slot_mapping, page_size, page_stride, head_stride);
+    else
+      TLLM_FAIL(TLLM_ERR_ARG, "rope_kv_write: unknown dtype code %d", dtype);
+    return TLLM_OK;
+  }
   if (dtype == TLLM_F32)
     TLLM_LAUNCH("rope_kv_write", rope_kv_write_kernel<float>, n_tokens, threads, 0, s, (float*)qkv, src, src_stride, positions, c, sn, n_tokens, nq, nkv, hd, row_stride, (float*)kcache, (float*)vcache, slot_mapping, page_size, page_stride, head_stride);
   else if (dtype == TLLM_BF16)
