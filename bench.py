@@ -246,8 +246,16 @@ def main():
         # a small, single-purpose run for a profiler capture: one plain line, no record
         if args.only == "decode":
             ms, launched = timed_decode(runner, args.batch, start_len, steps, warmup, out)
-            print(json.dumps({"only": "decode", "batch": args.batch, "layers": args.layers, "ms_per_step": round(ms, 4),
-                              "gpu_launches": launched}))
+            rec = {"only": "decode", "batch": args.batch, "layers": args.layers, "ms_per_step": round(ms, 4),
+                   "gpu_launches": launched, "fused_decode_step": runner._fused is not None}
+            if runner._fused is not None and os.environ.get("TLLM_STEP_TIMING"):
+                # device cycles one CTA of the fused decode step spent per kind of phase, per step
+                names = ["norm_load", "qkv", "grid_barriers", "attention", "combine", "plain_load", "o_proj", "gate_up",
+                         "down", "lm_head", "producer_waits_for_free_stage", "producer_total", "consumer_waits_for_weights",
+                         "reduce_and_epilogue"]
+                cycles = ops.decode_step_timing(cfg.head_dim)
+                rec["cycles_per_step"] = {n: round(v / (steps + warmup)) for n, v in zip(names, cycles)}
+            print(json.dumps(rec))
         else:
             print(json.dumps({"only": "prefill", "layers": args.layers, "tokens": 2048,
                               "ms": round(timed_prefill(runner, 2048, repeats=2), 3)}))

@@ -20,94 +20,11 @@
 //
 // Reference counterpart: tiny_llm/ops/cuda/flash_attention.cu:338-442 (32-bit SIMT, one lane per
 // key, 64-key tiles, chunk-local causal mask).
-#include <math_constants.h>
-
-#include "common.cuh"
-
-#ifndef TLLM_HEAD_DIM
-#error "compile with -DTLLM_HEAD_DIM=<multiple of 16 up to 256>"
-#endif
+#include "attention_tiles.cuh"
 
 TLLM_DEFINE_LAST_ERROR
 
 namespace tllm {
-
-constexpr int HD = TLLM_HEAD_DIM;
-static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multiple of 16 up to 256");
-constexpr int BN = 64;            // keys per tile
-constexpr int LDS = HD + 8;       // shared-memory row stride in elements: +16 bytes keeps ldmatrix conflict-free
-constexpr int CHUNKS = HD / 8;    // 16-byte chunks per row
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool pred) {
-  const int bytes = pred ? 16 : 0;   // 0: the destination is zero-filled
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-__device__ __forceinline__ void ldmatrix_x4(uint32_t* r, const void* p) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t* r, const void* p) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
-}
-__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-// 2^x in one instruction; 2^(-inf) = 0
-__device__ __forceinline__ float ex2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
-
-struct AttnParams {
-  const __nv_bfloat16* q;        // rows of q_row_stride elements; queries first in each row
-  const __nv_bfloat16* kcache;   // [pages, kv_heads, page_size, HD]
-  const __nv_bfloat16* vcache;
-  const int* block_table;        // [R, max_blocks]
-  const int* cu_q;               // [R + 1]
-  const int* q_start;            // [R]: position of the request's first token in this step
-  __nv_bfloat16* out;            // [T, nq * HD]
-  float* part_o;                 // [T * nq, splits, HD]   (splits > 1)
-  float* part_ml;                // [T * nq, splits, 2]
-  long long page_stride, head_stride;
-  int q_row_stride, max_blocks, nq, nkv, page_size, window, tiles_per_req, splits;
-  float scale_log2;              // scale * log2(e)
-};
-
-// A tile is 128 rows, 64 keys then 64 values; warp w gathers rows [32 w, 32 w + 32).  Each lane looks
-// up the page of one row; the copies are then issued so that consecutive lanes fetch consecutive
-// 16-byte pieces of a row (whole 128-byte lines per instruction), the row's address coming from
-// its lane by shuffle.
-__device__ __forceinline__ void load_kv_rows(__nv_bfloat16* k_dst, __nv_bfloat16* v_dst, const int* table, int j0,
-                                             int j_begin, int j_end, int kvh, const AttnParams& p) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row = warp * 32 + lane;            // 0..63 keys, 64..127 values
-  const bool is_v = row >= BN;
-  const int j = j0 + (row & (BN - 1));
-  bool ok = j >= j_begin && j <= j_end && j / p.page_size < p.max_blocks;
-  const int page = ok ? table[j / p.page_size] : -1;
-  ok = ok && page >= 0;
-  const __nv_bfloat16* src = is_v ? p.vcache : p.kcache;
-  if (ok) src += (long long)page * p.page_stride + (long long)kvh * p.head_stride + (long long)(j % p.page_size) * HD;
-  __nv_bfloat16* dst = (warp < 2 ? k_dst : v_dst) + (warp & 1) * 32 * LDS;   // this warp's 32 rows
-#pragma unroll
-  for (int idx = lane; idx < 32 * CHUNKS; idx += 32) {
-    const int r = idx / CHUNKS, c = idx % CHUNKS;
-    const unsigned long long a = __shfl_sync(0xffffffffu, (unsigned long long)src, r);
-    const int okr = __shfl_sync(0xffffffffu, (int)ok, r);
-    cp_async16(dst + r * LDS + c * 8, reinterpret_cast<const __nv_bfloat16*>(a) + (okr ? c * 8 : 0), okr != 0);
-  }
-}
 
 template <int WARPS, int STAGES>
 __global__ void __launch_bounds__(WARPS * 32)
@@ -160,7 +77,7 @@ attention_mma_kernel(const AttnParams p) {
 #pragma unroll
   for (int st = 0; st < STAGES - 1; ++st) {
     if (t_begin + st < t_end)
-      load_kv_rows(k_s + st * BN * LDS, v_s + st * BN * LDS, table, (t_begin + st) * BN, key_lo, key_hi, kvh, p);
+      load_kv_rows(k_s + st * BN * LDS, v_s + st * BN * LDS, table, (t_begin + st) * BN, key_lo, key_hi, kvh, p, threadIdx.x);
     cp_async_commit();
   }
 
@@ -190,7 +107,7 @@ attention_mma_kernel(const AttnParams p) {
       const int nxt = tix + STAGES - 1;
       if (nxt < t_end) {
         const int ns = (nxt - t_begin) % STAGES;
-        load_kv_rows(k_s + ns * BN * LDS, v_s + ns * BN * LDS, table, nxt * BN, key_lo, key_hi, kvh, p);
+        load_kv_rows(k_s + ns * BN * LDS, v_s + ns * BN * LDS, table, nxt * BN, key_lo, key_hi, kvh, p, threadIdx.x);
       }
       cp_async_commit();
     }
@@ -307,207 +224,22 @@ attention_mma_kernel(const AttnParams p) {
 template <int STAGES>
 __global__ void __launch_bounds__(128)
 attention_decode_kernel(const AttnParams p) {
-  static_assert(BN == 64, "one thread per key row and per value row of a tile");
   extern __shared__ __align__(16) uint8_t smem_raw[];
-  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // 16 rows
-  __nv_bfloat16* k_s = q_s + 16 * LDS;                               // STAGES tiles
-  __nv_bfloat16* v_s = k_s + STAGES * BN * LDS;
   pdl_trigger();
   pdl_wait();
-
-  const int req = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
-  const int group = p.nq / p.nkv;
-  const int tok0 = p.cu_q[req];
-  const int q_len = p.cu_q[req + 1] - tok0;
-  const int rows_total = q_len * group;        // <= 16 by the launch condition
-  const int start = p.q_start[req];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int g = lane >> 2, t4 = lane & 3;
-  const int* table = p.block_table + (size_t)req * p.max_blocks;
-
-  const int key_hi = start + q_len - 1;
-  const int key_lo = p.window > 0 ? max(0, start - p.window + 1) : 0;
-  const int first_tile = key_lo / BN, last_tile = key_hi / BN;
-  const int n_tiles = last_tile - first_tile + 1;
-  const int per_split = (n_tiles + p.splits - 1) / p.splits;
-  const int t_begin = first_tile + split * per_split;
-  const int t_end = min(last_tile + 1, t_begin + per_split);
-
-  for (int idx = threadIdx.x; idx < 16 * CHUNKS; idx += 128) {
-    const int r = idx / CHUNKS, c = idx % CHUNKS;
-    const bool ok = r < rows_total;
-    const __nv_bfloat16* src = p.q;
-    if (ok) src = p.q + (size_t)(tok0 + r / group) * p.q_row_stride + (size_t)(kvh * group + r % group) * HD + c * 8;
-    cp_async16(q_s + r * LDS + c * 8, src, ok);
-  }
-  cp_async_commit();
-#pragma unroll
-  for (int st = 0; st < STAGES - 1; ++st) {
-    if (t_begin + st < t_end)
-      load_kv_rows(k_s + st * BN * LDS, v_s + st * BN * LDS, table, (t_begin + st) * BN, key_lo, key_hi, kvh, p);
-    cp_async_commit();
-  }
-
-  const int pos_a = start + g / group, pos_b = start + (g + 8) / group;
-  const bool live_a = g < rows_total, live_b = g + 8 < rows_total;
-  const int lo_a = p.window > 0 ? pos_a - p.window + 1 : 0, lo_b = p.window > 0 ? pos_b - p.window + 1 : 0;
-  // what all rows can see: keys up to the first new token's position, from the last one's window on
-  // (rows beyond the request's last hold zero queries and are never stored)
-  const int lo_max = p.window > 0 ? start + q_len - 1 - p.window + 1 : 0;
-  float m_a = -CUDART_INF_F, m_b = -CUDART_INF_F, l_a = 0.f, l_b = 0.f;
-  float o[HD / 8][4];
-#pragma unroll
-  for (int i = 0; i < HD / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
-  uint32_t qf[HD / 16][4];
-
-  for (int tix = t_begin; tix < t_end; ++tix) {
-    const int stage = (tix - t_begin) % STAGES;
-    const __nv_bfloat16* kt = k_s + stage * BN * LDS + warp * 16 * LDS;   // this warp's 16 keys of the tile
-    const __nv_bfloat16* vt = v_s + stage * BN * LDS + warp * 16 * LDS;
-    cp_async_wait<STAGES - 2>();
-    __syncthreads();
-    {
-      const int nxt = tix + STAGES - 1;
-      if (nxt < t_end) {
-        const int ns = (nxt - t_begin) % STAGES;
-        load_kv_rows(k_s + ns * BN * LDS, v_s + ns * BN * LDS, table, nxt * BN, key_lo, key_hi, kvh, p);
-      }
-      cp_async_commit();
-    }
-    if (tix == t_begin) {
-#pragma unroll
-      for (int k0 = 0; k0 < HD; k0 += 16) ldmatrix_x4(qf[k0 / 16], q_s + (lane & 15) * LDS + k0 + (lane >> 4) * 8);
-    }
-    float s[2][4];
-#pragma unroll
-    for (int i = 0; i < 2; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
-#pragma unroll
-    for (int k0 = 0; k0 < HD; k0 += 16) {
-      uint32_t b[4];
-      ldmatrix_x4(b, kt + ((lane & 7) + (lane >> 4) * 8) * LDS + k0 + ((lane >> 3) & 1) * 8);
-      mma_bf16(s[0], qf[k0 / 16], b[0], b[1]);
-      mma_bf16(s[1], qf[k0 / 16], b[2], b[3]);
-    }
-    const int j_base = tix * BN + warp * 16;
-    const float c = p.scale_log2;
-    if (!(j_base + 15 <= start && j_base >= lo_max)) {   // else every row sees these 16 keys
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int j = j_base + i * 8 + t4 * 2 + e;
-          if (!(live_a && j <= pos_a && j >= lo_a)) s[i][e] = -CUDART_INF_F;
-          if (!(live_b && j <= pos_b && j >= lo_b)) s[i][2 + e] = -CUDART_INF_F;
-        }
-      }
-    }
-    float mx_a = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
-    float mx_b = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
-    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
-    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
-    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
-    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
-    const float mn_a = fmaxf(m_a, mx_a * c), mn_b = fmaxf(m_b, mx_b * c);
-    const float ms_a = mn_a == -CUDART_INF_F ? 0.f : mn_a, ms_b = mn_b == -CUDART_INF_F ? 0.f : mn_b;
-    const float corr_a = ex2(m_a - ms_a), corr_b = ex2(m_b - ms_b);
-    m_a = mn_a; m_b = mn_b;
-    uint32_t pf[4];
-    float sum_a = 0.f, sum_b = 0.f;
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const float p0 = ex2(fmaf(s[i][0], c, -ms_a)), p1 = ex2(fmaf(s[i][1], c, -ms_a));
-      const float p2 = ex2(fmaf(s[i][2], c, -ms_b)), p3 = ex2(fmaf(s[i][3], c, -ms_b));
-      sum_a += p0 + p1;
-      sum_b += p2 + p3;
-      pf[i * 2] = pack_bf16(p0, p1);
-      pf[i * 2 + 1] = pack_bf16(p2, p3);
-    }
-    l_a = l_a * corr_a + sum_a;
-    l_b = l_b * corr_b + sum_b;
-#pragma unroll
-    for (int i = 0; i < HD / 8; ++i) { o[i][0] *= corr_a; o[i][1] *= corr_a; o[i][2] *= corr_b; o[i][3] *= corr_b; }
-#pragma unroll
-    for (int d0 = 0; d0 < HD; d0 += 16) {
-      uint32_t b[4];
-      ldmatrix_x4_trans(b, vt + ((lane & 7) + ((lane >> 3) & 1) * 8) * LDS + d0 + (lane >> 4) * 8);
-      mma_bf16(o[d0 / 8], pf, b[0], b[1]);
-      mma_bf16(o[d0 / 8 + 1], pf, b[2], b[3]);
-    }
-  }
-  cp_async_wait<0>();
-  l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
-  l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
-  l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
-  l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
-
-  // ---- merge the four warps' running softmaxes through shared memory (the tile buffers are free now)
-  __syncthreads();
-  float* o_sh = reinterpret_cast<float*>(k_s);        // [4 warps][16 rows][HD]
-  float* ml_sh = o_sh + 4 * 16 * HD;                  // [4 warps][16 rows][2]
-#pragma unroll
-  for (int i = 0; i < HD / 8; ++i) {
-    *reinterpret_cast<float2*>(o_sh + (warp * 16 + g) * HD + i * 8 + t4 * 2) = make_float2(o[i][0], o[i][1]);
-    *reinterpret_cast<float2*>(o_sh + (warp * 16 + g + 8) * HD + i * 8 + t4 * 2) = make_float2(o[i][2], o[i][3]);
-  }
-  if (t4 == 0) {
-    ml_sh[(warp * 16 + g) * 2] = m_a; ml_sh[(warp * 16 + g) * 2 + 1] = l_a;
-    ml_sh[(warp * 16 + g + 8) * 2] = m_b; ml_sh[(warp * 16 + g + 8) * 2 + 1] = l_b;
-  }
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < rows_total * (HD / 2); idx += 128) {
-    const int r = idx / (HD / 2), d = (idx % (HD / 2)) * 2;
-    float m = -CUDART_INF_F;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) m = fmaxf(m, ml_sh[(w * 16 + r) * 2]);
-    const float m_ref = m == -CUDART_INF_F ? 0.f : m;
-    float l = 0.f, acc0 = 0.f, acc1 = 0.f;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      const float f = exp2f(ml_sh[(w * 16 + r) * 2] - m_ref);   // 0 for a warp that saw no key of the row
-      l += f * ml_sh[(w * 16 + r) * 2 + 1];
-      const float2 ov = *reinterpret_cast<const float2*>(o_sh + (w * 16 + r) * HD + d);
-      acc0 += f * ov.x;
-      acc1 += f * ov.y;
-    }
-    const size_t th = (size_t)(tok0 + r / group) * p.nq + (size_t)(kvh * group + r % group);
-    if (p.splits == 1) {
-      const float inv = 1.f / l;
-      *reinterpret_cast<uint32_t*>(p.out + th * HD + d) = pack_bf16(acc0 * inv, acc1 * inv);
-    } else {
-      *reinterpret_cast<float2*>(p.part_o + (th * p.splits + split) * HD + d) = make_float2(acc0, acc1);
-      if (d == 0) {
-        p.part_ml[(th * p.splits + split) * 2] = m;
-        p.part_ml[(th * p.splits + split) * 2 + 1] = l;
-      }
-    }
-  }
+  attention_decode_item<STAGES>(p, blockIdx.x, blockIdx.y, blockIdx.z, threadIdx.x, smem_raw, [] { __syncthreads(); });
 }
 
-// Merges the slices of every (token, head): out = sum_s 2^(m_s - m) o_s / sum_s 2^(m_s - m) l_s.
-// A slice that saw no key of the row has m_s = -inf and l_s = 0 and drops out.
+// Merges the slices of every (token, head), one CTA each.
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          __nv_bfloat16* __restrict__ out, int splits) {
   pdl_trigger();
   pdl_wait();
-  const size_t th = blockIdx.x;
-  float m = -CUDART_INF_F;
-  for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[(th * splits + s) * 2]);
-  float l = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float ms = part_ml[(th * splits + s) * 2];
-    if (ms != -CUDART_INF_F) l += exp2f(ms - m) * part_ml[(th * splits + s) * 2 + 1];
-  }
-  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
-    float acc = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const float ms = part_ml[(th * splits + s) * 2];
-      if (ms != -CUDART_INF_F) acc += exp2f(ms - m) * part_o[(th * splits + s) * HD + d];
-    }
-    out[th * HD + d] = __float2bfloat16_rn(acc / l);
-  }
+  attention_combine_row(part_o, part_ml, out, splits, blockIdx.x, threadIdx.x, blockDim.x);
 }
 
 }  // namespace tllm
+
 
 using namespace tllm;
 

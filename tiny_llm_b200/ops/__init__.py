@@ -172,8 +172,9 @@ def check_status() -> None:
         code = int(t.item())
         if code:
             t.zero_()
-            raise KernelError(f"a tensor-core kernel on device {key} gave up waiting (code {code}: "
-                              f"1 = TMA producer, 2 = MMA issuer, 3 = epilogue); its output is not valid")
+            raise KernelError(f"a kernel on device {key} gave up waiting (code {code}: 1 = TMA producer, "
+                              f"2 = MMA issuer, 3 = epilogue of a matrix product; 4 = weight producer, "
+                              f"5 = consumer, 6 = grid barrier of the fused decode step); its output is not valid")
 
 
 def _tc_ok(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
@@ -318,6 +319,66 @@ def paged_attention(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_d
         ctypes.c_float(scale), int(window or 0), _code(qkv.dtype), _stream()))
 
 
+# ----------------------------------------------------------------------------- fused decode step
+
+
+class DecodeLayer(ctypes.Structure):
+    """One run-order entry of the fused decode step; the layout of `DecodeLayer` in csrc/decode_step.cu."""
+    _fields_ = [(n, ctypes.c_void_p) for n in ("w_qkv", "w_o", "w_gate_up", "w_down", "norm1", "norm2", "cos", "sin",
+                                               "kcache", "vcache", "block_table", "slot_mapping")] + \
+               [("eps1", ctypes.c_float), ("eps2", ctypes.c_float), ("scale_log2", ctypes.c_float),
+                ("window", ctypes.c_int)]
+
+
+class DecodeParams(ctypes.Structure):
+    """The layout of `DecodeParams` in csrc/decode_step.cu."""
+    _fields_ = [(n, ctypes.c_void_p) for n in ("layers", "tokens", "positions", "cu_q", "embed", "final_norm", "lm_head",
+                                               "resid", "q_buf", "attn_out", "ffn_act", "logits", "part_o", "part_ml",
+                                               "ssq_part", "sync_words", "status")] + \
+               [(n, ctypes.c_int) for n in ("n_layers", "m", "hidden", "nq", "nkv", "inter", "gu_block", "vocab",
+                                            "page_size", "max_blocks", "splits", "stages", "act_ld")] + \
+               [("final_eps", ctypes.c_float)]
+
+
+def decode_step_library(head_dim: int):
+    if head_dim % 16 or not 16 <= head_dim <= 256:
+        raise KernelError(f"decode_step: head size {head_dim} is not a multiple of 16 up to 256")
+    flags = (f"-DTLLM_HEAD_DIM={head_dim}",)
+    timed_cta = os.environ.get("TLLM_STEP_TIMING")   # a switch for measurements: 1 + the CTA whose phases are timed
+    if timed_cta:
+        flags += (f"-DTLLM_STEP_TIMING={int(timed_cta)}",)
+    if os.environ.get("TLLM_STEP_KC"):
+        flags += (f"-DTLLM_STEP_KC={int(os.environ['TLLM_STEP_KC'])}",)
+    lib = build.load_library("decode_step", flags=flags)
+    if lib.tllm_decode_step_layer_bytes() != ctypes.sizeof(DecodeLayer) or \
+            lib.tllm_decode_step_params_bytes() != ctypes.sizeof(DecodeParams):
+        raise KernelError("decode_step: the Python and CUDA sides disagree about the parameter layout")
+    return lib
+
+
+def decode_step_timing(head_dim: int):
+    """Cycles per phase kind that the timed CTA spent since the last call (needs TLLM_STEP_TIMING):
+    norm load, qkv, grid barriers, attention, combine, plain load, o, gate/up, down, lm head."""
+    out = (ctypes.c_ulonglong * 16)()
+    decode_step_library(head_dim).tllm_decode_step_timing(out)
+    return list(out)
+
+
+def decode_step_refusal(head_dim: int, params: DecodeParams) -> Optional[str]:
+    """None if the fused kernel takes these sizes, else the reason it does not."""
+    lib = decode_step_library(head_dim)
+    if lib.tllm_decode_step(ctypes.byref(params), 0, None) != 0:
+        return lib.tllm_last_error().decode()
+    return None
+
+
+def decode_step(head_dim: int, params: DecodeParams) -> None:
+    """One whole decode step (every layer, final norm, LM head) of at most eight one-token requests
+    as one persistent kernel on the current stream."""
+    lib = decode_step_library(head_dim)
+    _check(lib, lib.tllm_decode_step(ctypes.byref(params), 1, _stream()))
+
+
 # ----------------------------------------------------------------------------- sampling
 
 
@@ -359,6 +420,7 @@ ATTENTION_HEAD_DIMS = (16, 32, 48, 64, 128)   # head sizes `build_all` compiles 
 def build_all(verbose: bool = True):
     """Compiles every library (what `__graft_entry__.build()` calls); returns their paths."""
     paths = [build.compile_library(n, verbose=verbose) for n in ALL_LIBRARIES]
-    paths += [build.compile_library("attention_mma", flags=(f"-DTLLM_HEAD_DIM={hd}",), verbose=verbose)
-              for hd in ATTENTION_HEAD_DIMS]
+    for name in ("attention_mma", "decode_step"):
+        paths += [build.compile_library(name, flags=(f"-DTLLM_HEAD_DIM={hd}",), verbose=verbose)
+                  for hd in ATTENTION_HEAD_DIMS]
     return paths

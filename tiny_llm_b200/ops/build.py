@@ -22,7 +22,8 @@ CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-shared", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 HEADERS = ["common.cuh"]
-EXTRA_HEADERS = {"sampling": ["sampling_noalloc.h"]}   # per-source headers that enter the hash
+EXTRA_HEADERS = {"sampling": ["sampling_noalloc.h"], "attention_mma": ["attention_tiles.cuh"],
+                 "decode_step": ["attention_tiles.cuh"]}   # per-source headers that enter the hash
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
