@@ -100,6 +100,93 @@ def test_silu_mul(ops, dtype, m, inter, block):
         assert torch.equal(out2, out) and float(acc.abs().sum()) == 0.0
 
 
+@pytest.mark.parametrize("m,n,k", [(8, 640, 1024), (1, 2048, 2048), (40, 384, 1536), (100, 200, 4096), (16, 128, 512)])
+def test_linear_with_k_slices_reduced_in_a_cluster(ops, m, n, k, monkeypatch):
+    """Few rows and a long K: the slices of K of a weight tile meet in a thread-block cluster (an option
+    for the plain products, whose default is float32 atomics).  Sums are exact to 32-bit accuracy, and
+    two runs give the same bits (one writer per element, fixed order)."""
+    monkeypatch.setattr(ops, "cluster_mask", 7)
+    torch.manual_seed(12)
+    a = torch.randn(m, k).to(torch.bfloat16)
+    w = torch.randn(n, k).to(torch.bfloat16)
+    assert ops._cluster_slices(n, k) > 1
+    ref = pl.linear(a.float().double(), w.float().double()).float()
+    scale = float(ref.abs().max())
+    runs = []
+    for _ in range(2):
+        acc = torch.full((m, n), 0.25, device=DEV)
+        ops.linear(a.to(DEV), w.to(DEV), acc, accumulate=True)
+        runs.append(acc.cpu())
+    assert float((runs[0] - ref - 0.25).abs().max()) <= 2e-5 * max(scale, 1)
+    assert torch.equal(runs[0], runs[1])
+    same = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    ops.linear(a.to(DEV), w.to(DEV), same)
+    assert float((same.float().cpu() - ref).abs().max()) <= tol("bfloat16", scale)
+    ops.check_status()
+
+
+@pytest.mark.parametrize("m,nq,nkv,hd,k,page", [(7, 6, 3, 32, 1024, 8), (1, 32, 4, 64, 2048, 16), (33, 2, 2, 128, 512, 4),
+                                              (5, 5, 1, 16, 80, 8)])
+def test_qkv_projection_with_rotation_and_cache_write_in_its_epilogue(ops, m, nq, nkv, hd, k, page):
+    torch.manual_seed(13)
+    n_pages, max_pos = -(-m // page) + 6, 91
+    cos, sin = pl.rope_tables(max_pos, hd, 5000.0)
+    h = torch.randn(m, k).to(torch.bfloat16)
+    w = (torch.randn((nq + 2 * nkv) * hd, k) / math.sqrt(k)).to(torch.bfloat16)
+    pos = torch.randint(0, max_pos, (m,), dtype=torch.int32)
+    slots = torch.randperm(n_pages * page)[:m].to(torch.int32)
+    kc = torch.zeros(n_pages, nkv, page, hd, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    qkv = torch.full((m, (nq + 2 * nkv) * hd), 7.0, dtype=torch.bfloat16, device=DEV)
+    assert ops.linear_rope_kv(h.to(DEV), w.to(DEV), qkv, pos.to(DEV), cos.to(DEV), sin.to(DEV), nq, nkv, hd, kc, vc,
+                              slots.to(DEV))
+    ops.check_status()
+    proj = pl.bf16_quant(pl.linear(h.float(), w.float()))
+    q_ref = pl.apply_rope(proj[:, : nq * hd].view(m, nq, hd), cos, sin, pos)
+    k_ref = pl.apply_rope(proj[:, nq * hd: (nq + nkv) * hd].view(m, nkv, hd), cos, sin, pos)
+    v_ref = proj[:, (nq + nkv) * hd:].view(m, nkv, hd)
+    e = tol("bfloat16", 4.0)
+    assert float((qkv[:, : nq * hd].float().cpu().view(m, nq, hd) - q_ref).abs().max()) <= e
+    assert float((qkv[:, nq * hd:].float().cpu() - 7.0).abs().max()) == 0     # the rest of the row is not written
+    kc, vc = kc.cpu(), vc.cpu()
+    for i in range(m):
+        pg, off = int(slots[i]) // page, int(slots[i]) % page
+        assert float((kc[pg, :, off].float() - k_ref[i]).abs().max()) <= e
+        assert float((vc[pg, :, off].float() - v_ref[i]).abs().max()) <= e
+    written = torch.zeros(n_pages * page, dtype=torch.bool)
+    written[slots.long()] = True
+    assert float(kc.permute(0, 2, 1, 3).reshape(n_pages * page, -1)[~written].abs().sum()) == 0   # nothing else touched
+    # queries only (a layer that reads another layer's cache), no rotation
+    q_only = torch.empty(m, nq * hd, dtype=torch.bfloat16, device=DEV)
+    assert ops.linear_rope_kv(h.to(DEV), w[: nq * hd].contiguous().to(DEV), q_only, pos.to(DEV), None, None, nq, nkv, hd,
+                              None, None, None)
+    assert float((q_only.float().cpu() - proj[:, : nq * hd]).abs().max()) <= e
+
+
+def test_qkv_epilogue_declines_head_sizes_that_do_not_tile(ops):
+    h = torch.zeros(4, 64, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(3 * 48, 64, dtype=torch.bfloat16, device=DEV)
+    out = torch.zeros(4, 3 * 48, dtype=torch.bfloat16, device=DEV)
+    pos = torch.zeros(4, dtype=torch.int32, device=DEV)
+    assert not ops.linear_rope_kv(h, w, out, pos, None, None, 1, 1, 48, None, None, None)
+
+
+@pytest.mark.parametrize("m,inter,k", [(8, 5632, 2048), (3, 256, 64), (70, 384, 1024)])
+def test_swiglu_projection_in_a_cluster(ops, m, inter, k):
+    """Gate tile, up tile and their K slices as one cluster, SiLU * up in the epilogue."""
+    from tiny_llm_b200.engine import Workspace
+    from tiny_llm_b200.parts import interleave_gate_up
+    torch.manual_seed(14)
+    a = torch.randn(m, k).to(torch.bfloat16)
+    wg = (torch.randn(inter, k) / math.sqrt(k)).to(torch.bfloat16)
+    wu = (torch.randn(inter, k) / math.sqrt(k)).to(torch.bfloat16)
+    out = torch.empty(m, inter, dtype=torch.bfloat16, device=DEV)
+    ops.linear_swiglu(a.to(DEV), interleave_gate_up(wg, wu, 128).to(DEV), out, 128, Workspace(DEV))
+    ops.check_status()
+    ref = pl.silu(pl.linear(a.float(), wg.float())) * pl.linear(a.float(), wu.float())
+    assert float((out.float().cpu() - ref).abs().max()) <= tol("bfloat16", max(1.0, float(ref.abs().max())))
+
+
 def paged_setup(dtype, n_req, lens, nkv, hd, page, seed, spare_pages=3):
     """Random keys/values for n_req sequences scattered over shuffled pages; unwritten slots are NaN."""
     g = torch.Generator().manual_seed(seed)

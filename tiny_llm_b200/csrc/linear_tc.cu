@@ -38,7 +38,9 @@ constexpr int BK = 64;         // K elements per stage = one 128-byte swizzle ro
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;   // warp 0: TMA, warp 1: MMA + tensor-memory allocation, warps 2-5: epilogue
 
-enum Epilogue { EPI_BF16 = 0, EPI_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU = 3, EPI_ATOMIC_F32 = 4 };
+enum Epilogue { EPI_BF16 = 0, EPI_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU = 3, EPI_ATOMIC_F32 = 4,
+                // cluster kernel: K slices reduced through distributed shared memory
+                EPI_CL_ADD_F32 = 5, EPI_CL_ROPE_KV = 6, EPI_CL_SWIGLU = 7, EPI_CL_BF16 = 8 };
 
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // a wait gives up after two seconds
 constexpr int ERR_PRODUCER = 1, ERR_MMA = 2, ERR_EPILOGUE = 3;
@@ -368,6 +370,222 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
+// ---------------------------------------------------------------- cluster kernel, SWAP orientation
+// Few rows of A (decode): a weight tile of 128 rows has too little work for an SM unless K is split,
+// and there are too few tiles for all SMs unless K is split too.  Here the CZ slices of K of one tile
+// (and, for SiLU*up, the gate tile and the up tile beside it: CY = 2) run as one thread-block
+// cluster.  Every CTA accumulates its slice in tensor memory as in linear_tc_kernel, leaves the
+// 128 x BN accumulators in its own shared memory, and after a cluster barrier each CTA reduces its
+// share of the tile's rows over the peers' shared memory (ld.shared::cluster) and applies the
+// epilogue once: no atomics, no float32 scratch for a later kernel to convert, and the order of the
+// sum is fixed.  Epilogues: add into the float32 residual stream; round to bfloat16, rotate Q and K
+// by position and write K, V into their pages (a tile holds whole heads, so both halves of a rotation
+// pair are at hand); SiLU(gate) * up; plain bfloat16 store.
+struct ClusterArgs {
+  int cy, cz;                      // cluster extent over row tiles (1, or 2 for gate/up pairs) and over K slices
+  const int* positions;            // [tokens]
+  const float* cos;                // [positions, hd / 2] or null: no rotation
+  const float* sin;
+  __nv_bfloat16* kcache;           // [pages, nkv, page_size, hd]
+  __nv_bfloat16* vcache;
+  const int* slot_mapping;         // [tokens] or null: the rows hold queries only
+  long long page_stride, head_stride;
+  int nq, nkv, hd, page_size;
+};
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// float at byte address `addr` of this CTA's shared memory, read from the CTA of rank `rank` in the cluster
+__device__ __forceinline__ float ld_cluster_f32(uint32_t addr, uint32_t rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
+template <int BN, int STAGES, int EPI>
+__global__ void __launch_bounds__(THREADS, 2)
+linear_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         void* __restrict__ out, int rows_a, int rows_b, int k_blocks, int k_blocks_per_split, int ldo,
+                         const ClusterArgs ca, int* __restrict__ status) {
+  using L = SmemLayout<BN, STAGES>;
+  static_assert(BN * BM * 4 <= STAGES * L::STAGE_BYTES, "the accumulators are parked in the pipeline's stages");
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* acc_bar = empty_bar + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  float* parked = reinterpret_cast<float*>(smem);   // [BN tokens][128 rows] once the MMAs are done
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile_a = blockIdx.y, tile_b = blockIdx.x;
+  const int kb_begin = blockIdx.z * k_blocks_per_split;
+  const int kb_end = min(k_blocks, kb_begin + k_blocks_per_split);
+  const int n_kb = max(0, kb_end - kb_begin);
+  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(acc_bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // the first weight tiles are requested before this grid waits for its predecessors
+  pdl_trigger();
+  const int n_pre = min(n_kb, STAGES);
+  if (warp == 0 && lane == 0) {
+    for (int i = 0; i < n_pre; ++i) {
+      mbar_expect_tx(&full_bar[i], L::STAGE_BYTES);
+      tma_load_2d(smem + i * L::STAGE_BYTES, &map_a, (kb_begin + i) * BK, tile_a * BM, &full_bar[i]);
+    }
+  }
+  pdl_wait();
+
+  if (warp == 0 && lane == 0) {
+    // ---------------- TMA producer
+    for (int i = 0; i < n_kb; ++i) {
+      const int s = i % STAGES;
+      uint8_t* a_dst = smem + s * L::STAGE_BYTES;
+      const bool pre = i < n_pre;
+      if (!pre) {
+        const uint32_t parity = ((i / STAGES) & 1) ^ 1;
+        if (!mbar_wait(&empty_bar[s], parity, abort_flag)) { *abort_flag = 1; atomicExch(status, ERR_PRODUCER); break; }
+        mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
+        tma_load_2d(a_dst, &map_a, (kb_begin + i) * BK, tile_a * BM, &full_bar[s]);
+      }
+      tma_load_2d(a_dst + L::A_BYTES, &map_b, (kb_begin + i) * BK, tile_b * BN, &full_bar[s]);
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---------------- MMA issuer
+    const uint32_t idesc = instr_desc_bf16(BN);
+    for (int i = 0; i < n_kb; ++i) {
+      const int s = i % STAGES;
+      const uint32_t parity = (i / STAGES) & 1;
+      if (!mbar_wait(&full_bar[s], parity, abort_flag)) { *abort_flag = 1; atomicExch(status, ERR_MMA); break; }
+      tc_fence_after();
+      const uint32_t a_addr = smem_u32(smem + s * L::STAGE_BYTES);
+      const uint32_t b_addr = a_addr + L::A_BYTES;
+#pragma unroll
+      for (int k = 0; k < BK / UMMA_K; ++k) {
+        umma_bf16(tmem_base, smem_desc_sw128(a_addr + k * UMMA_K * 2), smem_desc_sw128(b_addr + k * UMMA_K * 2),
+                  idesc, (i > 0 || k > 0) ? 1u : 0u);
+      }
+      umma_commit(&empty_bar[s]);
+    }
+    umma_commit(acc_bar);
+  } else if (warp >= 2) {
+    // ---------------- park the accumulators: warp w reads tensor-memory lanes [32 (w % 4), +32)
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    bool ok = true;
+    if (n_kb > 0) {
+      ok = mbar_wait(acc_bar, 0, abort_flag);
+      if (!ok) { *abort_flag = 1; atomicExch(status, ERR_EPILOGUE); }
+      ok = __all_sync(0xffffffffu, ok);
+      tc_fence_after();
+    }
+    const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
+#pragma unroll 1
+    for (int c = 0; c < BN; c += 16) {
+      float v[16];
+      if (n_kb > 0 && ok) {
+        tmem_ld16(taddr + c, v);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = 0.f;   // a slice without K blocks adds nothing
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) parked[(c + j) * BM + row] = v[j];
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+
+  // ---------------- every CTA of the cluster has parked its slice: reduce and store
+  cluster_sync_all();
+  const int CY = ca.cy, CZ = ca.cz;
+  const int my_y = blockIdx.y % CY, my_z = blockIdx.z;
+  const uint32_t base = smem_u32(parked);
+  const int m0 = tile_b * BN;
+  if (EPI == EPI_CL_SWIGLU) {
+    // ranks (0, z) hold the gate tile's slices, ranks (1, z) the up tile's; the 128 rows are dealt to all CY * CZ CTAs
+    const int rows_per = BM / (CY * CZ), r0 = (my_y + my_z * CY) * rows_per;
+    const int col0 = (tile_a / 2) * BM;            // first output column of this gate/up pair
+    for (int idx = threadIdx.x; idx < rows_per * BN; idx += THREADS) {
+      const int j = idx / rows_per, r = r0 + idx % rows_per;
+      const int m = m0 + j, col = col0 + r;
+      if (m >= rows_b || 2 * col0 + BM + r >= rows_a) continue;   // the matching up row exists
+      const uint32_t at = base + (uint32_t)(j * BM + r) * 4u;
+      float gate = 0.f, up = 0.f;
+      for (int z = 0; z < CZ; ++z) { gate += ld_cluster_f32(at, z * CY); up += ld_cluster_f32(at, z * CY + 1); }
+      reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * ldo + col] = __float2bfloat16_rn((gate / (1.f + expf(-gate))) * up);
+    }
+  } else if (EPI == EPI_CL_ROPE_KV) {
+    // pairs (d, d + hd/2) of whole heads: 64 pairs per tile, dealt to the CZ CTAs
+    const int half = ca.hd / 2;
+    const int pairs_per = (BM / 2) / CZ, p0 = my_z * pairs_per;
+    for (int idx = threadIdx.x; idx < pairs_per * BN; idx += THREADS) {
+      const int j = idx / pairs_per, q = p0 + idx % pairs_per;
+      const int r_lo = (q / half) * ca.hd + q % half, r_hi = r_lo + half;
+      const int m = m0 + j, n_lo = tile_a * BM + r_lo;
+      if (m >= rows_b || n_lo + half >= rows_a) continue;
+      const uint32_t at_lo = base + (uint32_t)(j * BM + r_lo) * 4u, at_hi = base + (uint32_t)(j * BM + r_hi) * 4u;
+      float lo = 0.f, hi = 0.f;
+      for (int z = 0; z < CZ; ++z) { lo += ld_cluster_f32(at_lo, z); hi += ld_cluster_f32(at_hi, z); }
+      // the projection's output is a bfloat16 tensor of the model: rounded before the rotation
+      lo = __bfloat162float(__float2bfloat16_rn(lo));
+      hi = __bfloat162float(__float2bfloat16_rn(hi));
+      const int head = n_lo / ca.hd, d = n_lo % ca.hd;
+      float o_lo = lo, o_hi = hi;
+      if (head < ca.nq + ca.nkv && ca.cos != nullptr) {
+        const size_t t = (size_t)ca.positions[m] * half + d;
+        const float cs = ca.cos[t], sn = ca.sin[t];
+        o_lo = cs * lo - sn * hi;
+        o_hi = sn * lo + cs * hi;
+      }
+      __nv_bfloat16* dst;
+      if (head < ca.nq) {
+        dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)m * ldo + (size_t)head * ca.hd;
+      } else {
+        if (ca.slot_mapping == nullptr) continue;
+        const int slot = ca.slot_mapping[m];
+        if (slot < 0) continue;
+        const bool is_v = head >= ca.nq + ca.nkv;
+        dst = (is_v ? ca.vcache : ca.kcache) + (long long)(slot / ca.page_size) * ca.page_stride +
+              (long long)(head - ca.nq - (is_v ? ca.nkv : 0)) * ca.head_stride + (long long)(slot % ca.page_size) * ca.hd;
+      }
+      dst[d] = __float2bfloat16_rn(o_lo);
+      dst[d + half] = __float2bfloat16_rn(o_hi);
+    }
+  } else {
+    const int rows_per = BM / CZ, r0 = my_z * rows_per;
+    for (int idx = threadIdx.x; idx < rows_per * BN; idx += THREADS) {
+      const int j = idx / rows_per, r = r0 + idx % rows_per;
+      const int m = m0 + j, n = tile_a * BM + r;
+      if (m >= rows_b || n >= rows_a) continue;
+      const uint32_t at = base + (uint32_t)(j * BM + r) * 4u;
+      float sum = 0.f;
+      for (int z = 0; z < CZ; ++z) sum += ld_cluster_f32(at, z);
+      const size_t o = (size_t)m * ldo + n;
+      if (EPI == EPI_CL_ADD_F32) reinterpret_cast<float*>(out)[o] += sum;
+      else reinterpret_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(sum);
+    }
+  }
+  cluster_sync_all();   // no CTA leaves while a peer still reads its shared memory
+}
+
 // ---------------------------------------------------------------- persistent kernel, NORMAL orientation
 // One CTA per SM walks the 128 x BN tiles of C (tile t, t + grid, ...; the M tiles of one N tile
 // are neighbours, so CTAs running side by side share the weight tile in L2).  Two accumulators of BN
@@ -582,6 +800,39 @@ static int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, void*
   return TLLM_OK;
 }
 
+template <int BN, int STAGES, int EPI>
+static int launch_cluster(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int rows_a, int rows_b, int k, int ldo,
+                          const ClusterArgs& ca, int* status, cudaStream_t s) {
+  using L = SmemLayout<BN, STAGES>;
+  auto kern = linear_tc_cluster_kernel<BN, STAGES, EPI>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (e != cudaSuccess) TLLM_FAIL(TLLM_ERR_CUDA, "linear_tc: cannot reserve %d bytes of shared memory: %s", L::TOTAL, cudaGetErrorString(e));
+    configured = true;
+  }
+  const int k_blocks = (k + BK - 1) / BK;
+  const int per_split = (k_blocks + ca.cz - 1) / ca.cz;
+  const int row_tiles = (rows_a + BM - 1) / BM;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((rows_b + BN - 1) / BN, (row_tiles + ca.cy - 1) / ca.cy * ca.cy, ca.cz);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = L::TOTAL;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = ca.cy;
+  attr[0].val.clusterDim.z = ca.cz;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ma, mb, out, rows_a, rows_b, k_blocks, per_split, ldo, ca, status);
+  if (e != cudaSuccess) TLLM_FAIL(TLLM_ERR_CUDA, "linear_tc_cluster: %s", cudaGetErrorString(e));
+  return TLLM_OK;
+}
+
 }  // namespace tllm
 
 using namespace tllm;
@@ -638,4 +889,63 @@ extern "C" int tllm_linear_tc(const void* a, const void* w, void* out, int m, in
   }
 #undef TLLM_SWAP_CASE
   TLLM_FAIL(TLLM_ERR_ARG, "linear_tc: unknown epilogue %d", epi);
+}
+
+// The same product for at most 128 rows of A with the K slices of a weight tile reduced inside a
+// thread-block cluster (`slices` = 1, 2, 4 or 8) and one of these epilogues:
+//   5: out (float32 [M, N]) += product;
+//   6: Q/K/V projection: out (bfloat16, row stride ldo) gets the rotated queries; rotated keys and the values
+//      go to their pages at slot_mapping (null: the rows are queries only).  N = (nq + 2 nkv) hd (or nq hd),
+//      hd divides 128; cos/sin null: no rotation;
+//   7: SiLU(gate) * up with gate/up rows of w interleaved in blocks of 128, out bfloat16 [M, N/2]
+//      (slices <= 4: the cluster also spans the gate tile and the up tile);
+//   8: out (bfloat16 [M, N]) = product.
+extern "C" int tllm_linear_tc_cluster(const void* a, const void* w, void* out, int m, int n, int k, int lda, int ldo,
+                                      int epi, int slices, const int* positions, const float* cos, const float* sin,
+                                      int nq, int nkv, int hd, void* kcache, void* vcache, const int* slot_mapping,
+                                      int page_size, long long page_stride, long long head_stride, int* status,
+                                      void* stream) {
+  TLLM_REQUIRE(m > 0 && m <= 128 && n > 0 && k > 0, "linear_tc_cluster: product %d x %d x %d (at most 128 rows)", m, n, k);
+  TLLM_REQUIRE(k % 8 == 0 && lda % 8 == 0, "linear_tc_cluster: K (%d) and the row stride of A (%d) must be multiples of 8", k, lda);
+  TLLM_REQUIRE(((uintptr_t)a % 16) == 0 && ((uintptr_t)w % 16) == 0, "linear_tc_cluster: operands must be 16-byte aligned");
+  TLLM_REQUIRE(status != nullptr, "linear_tc_cluster: needs a status word");
+  TLLM_REQUIRE(slices == 1 || slices == 2 || slices == 4 || slices == 8, "linear_tc_cluster: %d slices of K (1, 2, 4 or 8)", slices);
+  TLLM_REQUIRE(slices <= (k + BK - 1) / BK, "linear_tc_cluster: %d slices of a K of %d", slices, k);
+  ClusterArgs ca = {};
+  ca.cy = 1; ca.cz = slices;
+  if (epi == EPI_CL_SWIGLU) {
+    TLLM_REQUIRE(n % 256 == 0 && slices <= 4, "linear_tc_cluster: SiLU*up needs gate/up blocks of 128 rows (N = %d) and at most 4 slices", n);
+    ca.cy = 2;
+  } else if (epi == EPI_CL_ROPE_KV) {
+    TLLM_REQUIRE(hd >= 2 && 128 % hd == 0 && nq >= 1 && nkv >= 0, "linear_tc_cluster: head size %d must divide 128", hd);
+    TLLM_REQUIRE(n == (slot_mapping ? (nq + 2 * nkv) * hd : nq * hd), "linear_tc_cluster: %d rows of weights for %d + 2 x %d heads of %d", n, nq, nkv, hd);
+    TLLM_REQUIRE(positions != nullptr || cos == nullptr, "linear_tc_cluster: rotation needs positions");
+    TLLM_REQUIRE(slot_mapping == nullptr || (kcache && vcache && page_size > 0), "linear_tc_cluster: cache arguments missing");
+    ca.positions = positions; ca.cos = cos; ca.sin = sin; ca.kcache = (__nv_bfloat16*)kcache; ca.vcache = (__nv_bfloat16*)vcache;
+    ca.slot_mapping = slot_mapping; ca.page_stride = page_stride; ca.head_stride = head_stride;
+    ca.nq = nq; ca.nkv = nkv; ca.hd = hd; ca.page_size = page_size;
+  } else {
+    TLLM_REQUIRE(epi == EPI_CL_ADD_F32 || epi == EPI_CL_BF16, "linear_tc_cluster: unknown epilogue %d", epi);
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  CUtensorMap ma, mb;
+  const int bn = m <= 16 ? 16 : (m <= 32 ? 32 : (m <= 64 ? 64 : 128));
+  if (!make_map(&ma, w, n, k, k, BM) || !make_map(&mb, a, m, k, lda, bn))
+    TLLM_FAIL(TLLM_ERR_CUDA, "linear_tc_cluster: cuTensorMapEncodeTiled failed");
+#define TLLM_CL_CASE(BN_, ST_)                                                                                        \
+  switch (epi) {                                                                                                     \
+    case EPI_CL_ADD_F32: return launch_cluster<BN_, ST_, EPI_CL_ADD_F32>(ma, mb, out, n, m, k, ldo, ca, status, s);   \
+    case EPI_CL_ROPE_KV: return launch_cluster<BN_, ST_, EPI_CL_ROPE_KV>(ma, mb, out, n, m, k, ldo, ca, status, s);   \
+    case EPI_CL_SWIGLU: return launch_cluster<BN_, ST_, EPI_CL_SWIGLU>(ma, mb, out, n, m, k, ldo, ca, status, s);     \
+    case EPI_CL_BF16: return launch_cluster<BN_, ST_, EPI_CL_BF16>(ma, mb, out, n, m, k, ldo, ca, status, s);         \
+  }                                                                                                                  \
+  break;
+  switch (bn) {
+    case 16: TLLM_CL_CASE(16, 6)
+    case 32: TLLM_CL_CASE(32, 5)
+    case 64: TLLM_CL_CASE(64, 4)
+    case 128: TLLM_CL_CASE(128, 3)
+  }
+#undef TLLM_CL_CASE
+  TLLM_FAIL(TLLM_ERR_ARG, "linear_tc_cluster: unknown epilogue %d", epi);
 }

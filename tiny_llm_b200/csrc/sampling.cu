@@ -124,9 +124,29 @@ __device__ __forceinline__ float block_incl_scan_f(float v, float* total, BlockS
 __device__ __forceinline__ int block_argmax(const float* __restrict__ row, int v, BlockScratch& sc) {
   float best = -CUDART_INF_F;
   int idx = 0x7fffffff;
-  for (int i = threadIdx.x; i < v; i += blockDim.x) {
-    const float x = row[i];
-    if (idx == 0x7fffffff || x > best) { best = x; idx = i; }
+  if ((v & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    // 16-byte loads, two in flight per thread; a thread's elements come in ascending order
+    const float4* row4 = reinterpret_cast<const float4*>(row);
+    const int v4 = v >> 2;
+    for (int i = threadIdx.x; i < v4; i += 2 * blockDim.x) {
+      const int i2 = i + blockDim.x;
+      const float4 a = row4[i];
+      const float4 b = i2 < v4 ? row4[i2] : make_float4(-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F);
+      const float xa[4] = {a.x, a.y, a.z, a.w}, xb[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (idx == 0x7fffffff || xa[e] > best) { best = xa[e]; idx = 4 * i + e; }
+      if (i2 < v4) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (xb[e] > best) { best = xb[e]; idx = 4 * i2 + e; }
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < v; i += blockDim.x) {
+      const float x = row[i];
+      if (idx == 0x7fffffff || x > best) { best = x; idx = i; }
+    }
   }
   // pack (ordered value, inverted index) so that one max picks the value, then the lowest index
   unsigned long long key = idx == 0x7fffffff ? 0ull

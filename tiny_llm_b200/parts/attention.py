@@ -76,23 +76,28 @@ class GQAttention:
         qkv = ctx.workspace.get("qkv", (t, self.qkv_dim), ctx.dtype)
         pos = self.position
         fused = getattr(pos, "fused", False)
-        acc = None
-        if fused and ops.prefers_split(h, self.w_qkv):
-            # few rows: K is split over the SMs into a zeroed float32 buffer that the rotate-and-cache kernel consumes
-            acc = ctx.workspace.get_zeroed("qkv_f32", (t, self.qkv_dim))
-            ops.linear(h, self.w_qkv, acc, accumulate=True)
+        kv_slots = None if self.shares_cache else cache.slot_mapping
+        if fused and ops.linear_rope_kv(h, self.w_qkv, qkv, ctx.batch.positions, pos.cos, pos.sin, self.num_heads,
+                                        self.num_kv_heads, self.head_dim, cache.k, cache.v, kv_slots):
+            pass    # few tokens: projection, rotation and cache write were one kernel
         else:
-            ops.linear(h, self.w_qkv, qkv)
-        if not fused:
-            q = qkv[:, : self.q_dim].view(t, self.num_heads, self.head_dim)
-            k = None if self.shares_cache else \
-                qkv[:, self.q_dim: self.q_dim + self.kv_dim].view(t, self.num_kv_heads, self.head_dim)
-            pos.apply(ctx, q, k)
-        ops.rope_kv_write(
-            qkv, ctx.batch.positions,
-            pos.cos if fused else None, pos.sin if fused else None, pos.rot_dim if fused else 0,
-            self.num_heads, self.num_kv_heads, self.head_dim,
-            cache.k, cache.v, None if self.shares_cache else cache.slot_mapping, src=acc)
+            acc = None
+            if fused and ops.prefers_split(h, self.w_qkv):
+                # few rows: K is split over the SMs into a zeroed float32 buffer that the rotate-and-cache kernel consumes
+                acc = ctx.workspace.get_zeroed("qkv_f32", (t, self.qkv_dim))
+                ops.linear(h, self.w_qkv, acc, accumulate=True)
+            else:
+                ops.linear(h, self.w_qkv, qkv)
+            if not fused:
+                q = qkv[:, : self.q_dim].view(t, self.num_heads, self.head_dim)
+                k = None if self.shares_cache else \
+                    qkv[:, self.q_dim: self.q_dim + self.kv_dim].view(t, self.num_kv_heads, self.head_dim)
+                pos.apply(ctx, q, k)
+            ops.rope_kv_write(
+                qkv, ctx.batch.positions,
+                pos.cos if fused else None, pos.sin if fused else None, pos.rot_dim if fused else 0,
+                self.num_heads, self.num_kv_heads, self.head_dim,
+                cache.k, cache.v, kv_slots, src=acc)
         out = ctx.workspace.get("attn_out", (t, self.q_dim), ctx.dtype)
         ops.paged_attention(qkv, self.num_heads, self.num_kv_heads, self.head_dim, cache.k, cache.v,
                             cache.block_table, ctx.batch, out, self.scale, self.window, ctx.workspace)
