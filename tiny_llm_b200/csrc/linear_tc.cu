@@ -397,12 +397,12 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// float at byte address `addr` of this CTA's shared memory, read from the CTA of rank `rank` in the cluster
-__device__ __forceinline__ float ld_cluster_f32(uint32_t addr, uint32_t rank) {
+// four floats at byte address `addr` of this CTA's shared memory, read from the CTA of rank `rank` in the cluster
+__device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t addr, uint32_t rank) {
   uint32_t remote;
-  float v;
+  float4 v;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
   return v;
 }
 
@@ -514,6 +514,7 @@ linear_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 
   // ---------------- every CTA of the cluster has parked its slice: reduce and store
+  // Work items are four consecutive rows of one token: one 16-byte load per peer, all peers' loads in flight.
   cluster_sync_all();
   const int CY = ca.cy, CZ = ca.cz;
   const int my_y = blockIdx.y % CY, my_z = blockIdx.z;
@@ -521,40 +522,57 @@ linear_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   const int m0 = tile_b * BN;
   if (EPI == EPI_CL_SWIGLU) {
     // ranks (0, z) hold the gate tile's slices, ranks (1, z) the up tile's; the 128 rows are dealt to all CY * CZ CTAs
-    const int rows_per = BM / (CY * CZ), r0 = (my_y + my_z * CY) * rows_per;
+    const int rows_per = BM / (CY * CZ), r0 = (my_y + my_z * CY) * rows_per, quads = rows_per / 4;
     const int col0 = (tile_a / 2) * BM;            // first output column of this gate/up pair
-    for (int idx = threadIdx.x; idx < rows_per * BN; idx += THREADS) {
-      const int j = idx / rows_per, r = r0 + idx % rows_per;
+    for (int idx = threadIdx.x; idx < quads * BN; idx += THREADS) {
+      const int j = idx / quads, r = r0 + (idx % quads) * 4;
       const int m = m0 + j, col = col0 + r;
-      if (m >= rows_b || 2 * col0 + BM + r >= rows_a) continue;   // the matching up row exists
+      if (m >= rows_b) continue;
       const uint32_t at = base + (uint32_t)(j * BM + r) * 4u;
-      float gate = 0.f, up = 0.f;
-      for (int z = 0; z < CZ; ++z) { gate += ld_cluster_f32(at, z * CY); up += ld_cluster_f32(at, z * CY + 1); }
-      reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * ldo + col] = __float2bfloat16_rn((gate / (1.f + expf(-gate))) * up);
+      float4 part[8];
+#pragma unroll
+      for (int z = 0; z < 4; ++z) {
+        if (z < CZ) { part[2 * z] = ld_cluster_f32x4(at, z * CY); part[2 * z + 1] = ld_cluster_f32x4(at, z * CY + 1); }
+      }
+      float gate[4] = {0.f, 0.f, 0.f, 0.f}, up[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int z = 0; z < 4; ++z) {
+        if (z < CZ) {
+          gate[0] += part[2 * z].x; gate[1] += part[2 * z].y; gate[2] += part[2 * z].z; gate[3] += part[2 * z].w;
+          up[0] += part[2 * z + 1].x; up[1] += part[2 * z + 1].y; up[2] += part[2 * z + 1].z; up[3] += part[2 * z + 1].w;
+        }
+      }
+      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)m * ldo + col;
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (2 * col0 + BM + r + e < rows_a)   // the matching up row exists
+          dst[e] = __float2bfloat16_rn((gate[e] / (1.f + expf(-gate[e]))) * up[e]);
     }
   } else if (EPI == EPI_CL_ROPE_KV) {
-    // pairs (d, d + hd/2) of whole heads: 64 pairs per tile, dealt to the CZ CTAs
+    // pairs (d, d + hd/2) of whole heads: 64 pairs per tile, dealt to the CZ CTAs, four neighbouring pairs per item
     const int half = ca.hd / 2;
-    const int pairs_per = (BM / 2) / CZ, p0 = my_z * pairs_per;
-    for (int idx = threadIdx.x; idx < pairs_per * BN; idx += THREADS) {
-      const int j = idx / pairs_per, q = p0 + idx % pairs_per;
+    const int pairs_per = (BM / 2) / CZ, p0 = my_z * pairs_per, quads = pairs_per / 4;
+    for (int idx = threadIdx.x; idx < quads * BN; idx += THREADS) {
+      const int j = idx / quads, q = p0 + (idx % quads) * 4;
       const int r_lo = (q / half) * ca.hd + q % half, r_hi = r_lo + half;
       const int m = m0 + j, n_lo = tile_a * BM + r_lo;
-      if (m >= rows_b || n_lo + half >= rows_a) continue;
+      if (m >= rows_b || n_lo + half >= rows_a) continue;   // heads are whole: the four pairs exist together
       const uint32_t at_lo = base + (uint32_t)(j * BM + r_lo) * 4u, at_hi = base + (uint32_t)(j * BM + r_hi) * 4u;
-      float lo = 0.f, hi = 0.f;
-      for (int z = 0; z < CZ; ++z) { lo += ld_cluster_f32(at_lo, z); hi += ld_cluster_f32(at_hi, z); }
-      // the projection's output is a bfloat16 tensor of the model: rounded before the rotation
-      lo = __bfloat162float(__float2bfloat16_rn(lo));
-      hi = __bfloat162float(__float2bfloat16_rn(hi));
-      const int head = n_lo / ca.hd, d = n_lo % ca.hd;
-      float o_lo = lo, o_hi = hi;
-      if (head < ca.nq + ca.nkv && ca.cos != nullptr) {
-        const size_t t = (size_t)ca.positions[m] * half + d;
-        const float cs = ca.cos[t], sn = ca.sin[t];
-        o_lo = cs * lo - sn * hi;
-        o_hi = sn * lo + cs * hi;
+      float4 pl[8], ph[8];
+#pragma unroll
+      for (int z = 0; z < 8; ++z) {
+        if (z < CZ) { pl[z] = ld_cluster_f32x4(at_lo, z); ph[z] = ld_cluster_f32x4(at_hi, z); }
       }
+      float lo[4] = {0.f, 0.f, 0.f, 0.f}, hi[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int z = 0; z < 8; ++z) {
+        if (z < CZ) {
+          lo[0] += pl[z].x; lo[1] += pl[z].y; lo[2] += pl[z].z; lo[3] += pl[z].w;
+          hi[0] += ph[z].x; hi[1] += ph[z].y; hi[2] += ph[z].z; hi[3] += ph[z].w;
+        }
+      }
+      const int head = n_lo / ca.hd, d = n_lo % ca.hd;
+      const bool rotate = head < ca.nq + ca.nkv && ca.cos != nullptr;
       __nv_bfloat16* dst;
       if (head < ca.nq) {
         dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)m * ldo + (size_t)head * ca.hd;
@@ -566,21 +584,43 @@ linear_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         dst = (is_v ? ca.vcache : ca.kcache) + (long long)(slot / ca.page_size) * ca.page_stride +
               (long long)(head - ca.nq - (is_v ? ca.nkv : 0)) * ca.head_stride + (long long)(slot % ca.page_size) * ca.hd;
       }
-      dst[d] = __float2bfloat16_rn(o_lo);
-      dst[d + half] = __float2bfloat16_rn(o_hi);
+      const size_t t = rotate ? (size_t)ca.positions[m] * half + d : 0;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        // the projection's output is a bfloat16 tensor of the model: rounded before the rotation
+        const float x = __bfloat162float(__float2bfloat16_rn(lo[e])), y = __bfloat162float(__float2bfloat16_rn(hi[e]));
+        float o_lo = x, o_hi = y;
+        if (rotate) {
+          const float cs = ca.cos[t + e], sn = ca.sin[t + e];
+          o_lo = cs * x - sn * y;
+          o_hi = sn * x + cs * y;
+        }
+        dst[d + e] = __float2bfloat16_rn(o_lo);
+        dst[d + half + e] = __float2bfloat16_rn(o_hi);
+      }
     }
   } else {
-    const int rows_per = BM / CZ, r0 = my_z * rows_per;
-    for (int idx = threadIdx.x; idx < rows_per * BN; idx += THREADS) {
-      const int j = idx / rows_per, r = r0 + idx % rows_per;
+    const int rows_per = BM / CZ, r0 = my_z * rows_per, quads = rows_per / 4;
+    for (int idx = threadIdx.x; idx < quads * BN; idx += THREADS) {
+      const int j = idx / quads, r = r0 + (idx % quads) * 4;
       const int m = m0 + j, n = tile_a * BM + r;
       if (m >= rows_b || n >= rows_a) continue;
       const uint32_t at = base + (uint32_t)(j * BM + r) * 4u;
-      float sum = 0.f;
-      for (int z = 0; z < CZ; ++z) sum += ld_cluster_f32(at, z);
-      const size_t o = (size_t)m * ldo + n;
-      if (EPI == EPI_CL_ADD_F32) reinterpret_cast<float*>(out)[o] += sum;
-      else reinterpret_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(sum);
+      float4 part[8];
+#pragma unroll
+      for (int z = 0; z < 8; ++z)
+        if (z < CZ) part[z] = ld_cluster_f32x4(at, z);
+      float sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int z = 0; z < 8; ++z)
+        if (z < CZ) { sum[0] += part[z].x; sum[1] += part[z].y; sum[2] += part[z].z; sum[3] += part[z].w; }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        if (n + e >= rows_a) break;
+        const size_t o = (size_t)m * ldo + n + e;
+        if (EPI == EPI_CL_ADD_F32) reinterpret_cast<float*>(out)[o] += sum[e];
+        else reinterpret_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(sum[e]);
+      }
     }
   }
   cluster_sync_all();   // no CTA leaves while a peer still reads its shared memory
@@ -917,7 +957,7 @@ extern "C" int tllm_linear_tc_cluster(const void* a, const void* w, void* out, i
     TLLM_REQUIRE(n % 256 == 0 && slices <= 4, "linear_tc_cluster: SiLU*up needs gate/up blocks of 128 rows (N = %d) and at most 4 slices", n);
     ca.cy = 2;
   } else if (epi == EPI_CL_ROPE_KV) {
-    TLLM_REQUIRE(hd >= 2 && 128 % hd == 0 && nq >= 1 && nkv >= 0, "linear_tc_cluster: head size %d must divide 128", hd);
+    TLLM_REQUIRE(hd >= 16 && 128 % hd == 0 && nq >= 1 && nkv >= 0, "linear_tc_cluster: head size %d must be 16, 32, 64 or 128", hd);
     TLLM_REQUIRE(n == (slot_mapping ? (nq + 2 * nkv) * hd : nq * hd), "linear_tc_cluster: %d rows of weights for %d + 2 x %d heads of %d", n, nq, nkv, hd);
     TLLM_REQUIRE(positions != nullptr || cos == nullptr, "linear_tc_cluster: rotation needs positions");
     TLLM_REQUIRE(slot_mapping == nullptr || (kcache && vcache && page_size > 0), "linear_tc_cluster: cache arguments missing");

@@ -236,7 +236,7 @@ def linear_rope_kv(h: torch.Tensor, w_qkv: torch.Tensor, qkv: torch.Tensor, posi
     values straight into their pages (slot_mapping None: `w_qkv` holds the query rows only).  Returns
     False, having done nothing, where the fused kernel does not apply (then: linear + rope_kv_write)."""
     m = h.shape[0]
-    if not ((cluster_mask & 2) and _tc_ok(h, w_qkv, qkv) and m <= 128 and 128 % head_dim == 0 and head_dim >= 2 and
+    if not ((cluster_mask & 2) and _tc_ok(h, w_qkv, qkv) and m <= 128 and head_dim in (16, 32, 64, 128) and
             qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1 and w_qkv.is_contiguous() and
             (cos is None or cos.shape[1] * 2 == head_dim)):
         return False
