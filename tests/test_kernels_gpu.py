@@ -253,6 +253,52 @@ def test_paged_attention(ops, dtype, nq, nkv, hd, page, window):
         assert float(p[3]) > 0.9
 
 
+@pytest.mark.parametrize("nq,nkv,page", [(8, 1, 16), (32, 4, 16), (4, 4, 8), (2, 1, 64), (16, 2, 32)])
+def test_paged_attention_on_tcgen05(ops, nq, nkv, page):
+    """Head size 64 and portions of at least 128 rows: the tcgen05 kernel.  Portions that start in the
+    middle of a sequence, end in the middle of a page, and a one-token request beside them; unwritten
+    slots of the pages are NaN."""
+    hd, dtype = 64, "bfloat16"
+    lens = [700, 300, 129, 64]
+    q_lens = [389, 300, 17, 1]
+    table, k_cache, v_cache, ks, vs = paged_setup(dtype, 4, lens, nkv, hd, page, seed=nq + page)
+    g = torch.Generator().manual_seed(8)
+    t = sum(q_lens)
+    width = (nq + 2 * nkv) * hd
+    qkv = torch.randn(t, width, generator=g).to(DT[dtype])
+    # a far key among hundreds: request 0's last query and its key 5 are scaled so that this score stands out
+    last = q_lens[0] - 1
+    qkv[last, :hd] *= 6.0
+    ks[0][5, 0] = (qkv[last, :hd] / qkv[last, :hd].float().norm() * 8.0).to(DT[dtype])
+    k_cache[int(table[0, 5 // page]), 0, 5 % page] = ks[0][5, 0]
+    pos = torch.cat([torch.arange(l - n, l, dtype=torch.int32) for l, n in zip(lens, q_lens)])
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
+    starts = torch.tensor([l - n for l, n in zip(lens, q_lens)], dtype=torch.int32)
+    tok_req = torch.cat([torch.full((n,), r, dtype=torch.int32) for r, n in enumerate(q_lens)])
+    batch = types.SimpleNamespace(token_request=tok_req.to(DEV), positions=pos.to(DEV), cu_q=cu.to(DEV),
+                                  q_start=starts.to(DEV), num_requests=4, max_q_len=max(q_lens), max_kv_len=max(lens))
+    out = torch.full((t, nq * hd), float("nan"), dtype=DT[dtype], device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    from tiny_llm_b200 import ops as ops_mod
+    from tiny_llm_b200.engine import Workspace
+    before = set(ops_mod.build.loaded_libraries())
+    ops.paged_attention(qkv.to(DEV), nq, nkv, hd, k_cache.to(DEV), v_cache.to(DEV), table.to(DEV), batch, out,
+                        scale, None, Workspace(DEV))
+    ops.check_status()
+    assert "attention_tc_head_dim64" in set(ops_mod.build.loaded_libraries()) | before
+    out = out.float().cpu()
+    assert not torch.isnan(out).any()
+    cur = 0
+    for r, (l, n) in enumerate(zip(lens, q_lens)):
+        q = qkv[cur: cur + n, : nq * hd].float().view(n, nq, hd)
+        ref = pl.attention(q, ks[r].float(), vs[r].float(), pos[cur: cur + n], quant=pl.bf16_quant).reshape(n, nq * hd)
+        d = float((out[cur: cur + n] - ref).abs().max())
+        assert d <= tol(dtype, max(1.0, float(ref.abs().max()))), (r, d)
+        cur += n
+    p = torch.softmax((qkv[last, :hd].float() * scale) @ ks[0][:lens[0], 0].float().t(), 0)
+    assert float(p[5]) > 0.9
+
+
 def test_attention_refuses_sizes_it_is_not_built_for(ops):
     from tiny_llm_b200.ops import KernelError
     z = torch.zeros(2, dtype=torch.int32, device=DEV)

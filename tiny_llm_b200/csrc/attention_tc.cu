@@ -1,0 +1,401 @@
+// bfloat16 attention of prompt portions over the paged cache on the 5th-generation tensor cores
+// (tcgen05), for head size 64 (-DTLLM_HEAD_DIM=64).
+//
+// A CTA serves 128 rows of one (request, key/value head); a row is a (new token, query head of the
+// group) pair, so the heads of a group share every key/value tile.  Keys are walked in tiles of 64:
+//
+//   warp 0 (one thread): TMA.  The query tile comes as one 3-D box (head size x heads of the group x
+//     tokens) of the step's Q/K/V rows; a key tile and a value tile come page by page (one 2-D box of
+//     page_size rows each, looked up in the request's block table) into a ring of two stages.
+//   warp 1 (one thread): tcgen05.mma.  S = Q K^T (M 128, N 64, K = head size; both operands
+//     K-major in 128-byte-swizzled shared memory) into tensor memory; later O += P V (M 128, N = head
+//     size, K 64) with P from shared memory and V taken as it lies in the cache (rows = keys: the
+//     MN-major form of the B operand).  tcgen05.commit hands each result over on an mbarrier.
+//   warps 2-5: softmax.  A thread owns one row: it reads its 64 scores from tensor memory, applies
+//     the causal rule (key j is visible to the token at position p iff j <= p), keeps the running
+//     maximum and sum in 32-bit with the scale folded into exp2, writes P as bfloat16 into shared
+//     memory in the swizzled layout the MMA expects, and rescales its row of O in tensor memory when
+//     the maximum moved.  Rows of a value tile beyond the request's last key are zeroed first (a
+//     page may hold anything there, and 0 x NaN would spoil the product).
+//
+// Two or three such CTAs share an SM, so one CTA's softmax overlaps another's MMAs.  Every wait is
+// bounded (two seconds), after which the kernel records a code in the status word and stops.
+//
+// Sizes: head size 64; heads per key/value head a power of two up to 128; page size 8, 16, 32 or
+// 64; no window.  Other cases run on the mma.sync kernels of attention_mma.cu.
+//
+// Reference counterpart: tiny_llm/ops/cuda/flash_attention.cu:338-442 (32-bit SIMT, one lane per
+// key, 64-key tiles, chunk-local causal mask).
+#include <math_constants.h>
+
+#include <map>
+#include <tuple>
+
+#include "tc_common.cuh"
+
+#ifndef TLLM_HEAD_DIM
+#error "compile with -DTLLM_HEAD_DIM=64"
+#endif
+
+TLLM_DEFINE_LAST_ERROR
+
+namespace tllm {
+
+constexpr int HD = TLLM_HEAD_DIM;
+static_assert(HD == 64, "a row of keys must be one 128-byte swizzle row");
+constexpr int BM = 128;          // rows per CTA = MMA M
+constexpr int BNK = 64;          // keys per tile
+constexpr int KV_STAGES = 2;
+constexpr int THREADS = 192;     // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-5: softmax
+constexpr int UMMA_K = 16;
+constexpr int Q_BYTES = BM * HD * 2, K_BYTES = BNK * HD * 2, V_BYTES = BNK * HD * 2, P_BYTES = BM * BNK * 2;
+constexpr int OFF_K = Q_BYTES, OFF_V = OFF_K + KV_STAGES * K_BYTES, OFF_P = OFF_V + KV_STAGES * V_BYTES;
+constexpr int OFF_BAR = OFF_P + P_BYTES;
+constexpr int SMEM_TOTAL = OFF_BAR + 128 + 1024;   // barriers and the tensor-memory slot; alignment slack
+constexpr uint32_t TMEM_COLS = 128;                // S: columns [0, 64); O: columns [64, 64 + HD)
+constexpr int ERR_ATT_PRODUCER = 7, ERR_ATT_MMA = 8, ERR_ATT_SOFTMAX = 9;
+
+struct TcAttnParams {
+  const int* block_table;   // [R, max_blocks]
+  const int* cu_q;          // [R + 1]
+  const int* q_start;       // [R]: position of the request's first token in this step
+  __nv_bfloat16* out;       // [T, nq * HD]
+  int* status;
+  int max_blocks, nq, nkv, page_size, tiles_per_req;
+  float scale_log2;         // scale * log2(e)
+};
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+__global__ void __launch_bounds__(THREADS, 2)
+attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                    const __grid_constant__ CUtensorMap map_v, const TcAttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
+  uint64_t* q_full = bars;                       // [1]
+  uint64_t* k_full = bars + 1;                   // [KV_STAGES]
+  uint64_t* v_full = k_full + KV_STAGES;         // [KV_STAGES]
+  uint64_t* kv_empty = v_full + KV_STAGES;       // [KV_STAGES]
+  uint64_t* s_full = kv_empty + KV_STAGES;       // S of this tile is in tensor memory
+  uint64_t* p_full = s_full + 1;                 // P of this tile is in shared memory, O rescaled (128 arrivals)
+  uint64_t* pv_done = p_full + 1;                // O holds this tile too; P and the stage are free
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // the tiles of the latest tokens see the most keys: they are scheduled first
+  const int req = blockIdx.x / p.tiles_per_req, tile = p.tiles_per_req - 1 - blockIdx.x % p.tiles_per_req;
+  const int kvh = blockIdx.y;
+  const int group = p.nq / p.nkv;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 128);
+    mbar_init(pv_done, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_trigger();
+  pdl_wait();
+
+  const int tok0 = p.cu_q[req];
+  const int q_len = p.cu_q[req + 1] - tok0;
+  const int rows_total = q_len * group;
+  const int row0 = tile * BM;
+  const int start = p.q_start[req];
+  const int tok_lo = row0 / group;
+  const int tok_hi = min(q_len - 1, (row0 + BM - 1) / group);
+  const int kv_end = start + q_len;                         // keys that exist once this step's are written
+  const int n_tiles = row0 < rows_total ? (start + tok_hi) / BNK + 1 : 0;
+
+  if (warp == 0 && lane == 0) {
+    // ---------------- TMA producer
+    const int* table = p.block_table + (size_t)req * p.max_blocks;
+    const int pages_per_tile = BNK / p.page_size;
+    const uint32_t page_bytes = (uint32_t)p.page_size * HD * 2u;
+    if (n_tiles > 0) {
+      mbar_expect_tx(q_full, Q_BYTES);
+      tma_load_3d(smem, &map_q, 0, kvh * group, tok0 + tok_lo, q_full);
+    }
+    for (int i = 0; i < n_tiles; ++i) {
+      const int s = i % KV_STAGES;
+      if (i >= KV_STAGES) {
+        const uint32_t parity = ((i / KV_STAGES) & 1) ^ 1;
+        if (!mbar_wait(&kv_empty[s], parity, abort_flag)) { *abort_flag = 1; atomicExch(p.status, ERR_ATT_PRODUCER); break; }
+      }
+      // pages of keys [i * 64, i * 64 + 64) that hold at least one existing key
+      int pages[BNK / 8];
+      int n_valid = 0;
+      for (int g = 0; g < pages_per_tile; ++g) {
+        const int blk = i * pages_per_tile + g;
+        int page = -1;
+        if (blk < p.max_blocks && blk * p.page_size < kv_end) page = table[blk];
+        pages[g] = page;
+        n_valid += page >= 0 ? 1 : 0;
+      }
+      mbar_expect_tx(&k_full[s], (uint32_t)n_valid * page_bytes);
+      mbar_expect_tx(&v_full[s], (uint32_t)n_valid * page_bytes);
+      for (int g = 0; g < pages_per_tile; ++g) {
+        if (pages[g] < 0) continue;
+        const int row = (pages[g] * p.nkv + kvh) * p.page_size;
+        tma_load_2d(smem + OFF_K + s * K_BYTES + g * page_bytes, &map_k, 0, row, &k_full[s]);
+        tma_load_2d(smem + OFF_V + s * V_BYTES + g * page_bytes, &map_v, 0, row, &v_full[s]);
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---------------- MMA issuer
+    const uint32_t idesc_qk = instr_desc_bf16(BM, BNK);
+    const uint32_t idesc_pv = instr_desc_bf16(BM, HD, true);   // V as it lies: rows = keys (MN-major B)
+    const uint32_t q_addr = smem_u32(smem), p_addr = smem_u32(smem + OFF_P);
+    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + BNK;
+    bool ok = n_tiles == 0 || mbar_wait(q_full, 0, abort_flag);
+    if (!ok) { *abort_flag = 1; atomicExch(p.status, ERR_ATT_MMA); }
+    for (int i = 0; i < n_tiles && ok; ++i) {
+      const int s = i % KV_STAGES;
+      const uint32_t ring_parity = (i / KV_STAGES) & 1, tile_parity = i & 1;
+      if (!mbar_wait(&k_full[s], ring_parity, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t k_addr = smem_u32(smem + OFF_K + s * K_BYTES);
+#pragma unroll
+      for (int k = 0; k < HD / UMMA_K; ++k)
+        umma_bf16(tmem_s, smem_desc_sw128(q_addr + k * UMMA_K * 2), smem_desc_sw128(k_addr + k * UMMA_K * 2), idesc_qk, k > 0 ? 1u : 0u);
+      umma_commit(s_full);
+      if (!mbar_wait(p_full, tile_parity, abort_flag)) { ok = false; break; }
+      if (!mbar_wait(&v_full[s], ring_parity, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t v_addr = smem_u32(smem + OFF_V + s * V_BYTES);
+#pragma unroll
+      for (int kk = 0; kk < BNK / UMMA_K; ++kk)   // 16 keys per step: 32 bytes along a row of P, two 8-row groups of V
+        umma_bf16(tmem_o, smem_desc_sw128(p_addr + kk * UMMA_K * 2), smem_desc_sw128(v_addr + kk * UMMA_K * HD * 2), idesc_pv,
+                  (i > 0 || kk > 0) ? 1u : 0u);
+      umma_commit(&kv_empty[s]);
+      umma_commit(pv_done);
+    }
+    if (!ok && !*abort_flag) { *abort_flag = 1; atomicExch(p.status, ERR_ATT_MMA); }
+  } else if (warp >= 2) {
+    // ---------------- softmax: this thread owns row `row` of the tile (tensor-memory lane)
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const int grow = row0 + row;
+    const bool live = grow < rows_total;
+    const int pos = start + grow / group;
+    const uint32_t t_s = tmem_base + ((uint32_t)(quad * 32) << 16), t_o = t_s + BNK;
+    uint8_t* p_row = smem + OFF_P + row * 128;
+    const int soft_tid = (warp - 2) * 32 + lane;   // 0..127 among the softmax threads
+    const float c = p.scale_log2;
+    float m_run = -CUDART_INF_F, l_run = 0.f;
+    bool ok = true;
+    for (int i = 0; i < n_tiles; ++i) {
+      const int s = i % KV_STAGES;
+      ok = mbar_wait(s_full, i & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      float sc[BNK];
+      tmem_ld32(t_s, sc);
+      tmem_ld32(t_s + 32, sc + 32);
+      const int j0 = i * BNK;
+      if (!live || j0 + BNK - 1 > pos) {   // the tile touches this row's causal edge (or the row does not exist)
+#pragma unroll
+        for (int j = 0; j < BNK; ++j)
+          if (!(live && j0 + j <= pos)) sc[j] = -CUDART_INF_F;
+      }
+      float mx = sc[0];
+#pragma unroll
+      for (int j = 1; j < BNK; ++j) mx = fmaxf(mx, sc[j]);
+      const float mn = fmaxf(m_run, mx * c);
+      const float ms = mn == -CUDART_INF_F ? 0.f : mn;
+      const float corr = ex2(m_run - ms);   // 0 while nothing was seen
+      m_run = mn;
+      float sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < BNK; ++j) {
+        sc[j] = ex2(fmaf(sc[j], c, -ms));
+        sum += sc[j];
+      }
+      l_run = l_run * corr + sum;
+      if (i > 0) {   // the product before this one has read P and finished O
+        ok = mbar_wait(pv_done, (i - 1) & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+      }
+      // P as bfloat16, 16-byte chunk j of the row stored at chunk position j ^ (row % 8): the 128-byte swizzle
+#pragma unroll
+      for (int ch = 0; ch < BNK / 8; ++ch) {
+        uint4 v;
+        v.x = pack_bf16(sc[ch * 8 + 0], sc[ch * 8 + 1]);
+        v.y = pack_bf16(sc[ch * 8 + 2], sc[ch * 8 + 3]);
+        v.z = pack_bf16(sc[ch * 8 + 4], sc[ch * 8 + 5]);
+        v.w = pack_bf16(sc[ch * 8 + 6], sc[ch * 8 + 7]);
+        *reinterpret_cast<uint4*>(p_row + ((ch ^ (row & 7)) << 4)) = v;
+      }
+      if (i > 0 && !__all_sync(0xffffffffu, corr == 1.f)) {   // the maximum of some row of this warp moved
+#pragma unroll
+        for (int h = 0; h < HD; h += 32) {
+          float o[32];
+          tmem_ld32(t_o + h, o);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o[j] *= corr;
+          tmem_st32(t_o + h, o);
+        }
+      }
+      if (j0 + BNK > kv_end) {   // value rows past the last key hold whatever the page held: zero them
+        ok = mbar_wait(&v_full[s], (i / KV_STAGES) & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (soft_tid < BNK && j0 + soft_tid >= kv_end) {
+          uint4* vrow = reinterpret_cast<uint4*>(smem + OFF_V + s * V_BYTES + soft_tid * 128);
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) vrow[ch] = make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P (and V) were written by ordinary stores
+      tc_fence_before();
+      mbar_arrive(p_full);
+    }
+    if (ok && n_tiles > 0) {
+      ok = mbar_wait(pv_done, (n_tiles - 1) & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (!ok) {
+      if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, ERR_ATT_SOFTMAX); }
+    } else if (n_tiles > 0) {
+      tc_fence_after();
+      const float inv = 1.f / l_run;
+      const size_t th = (size_t)(tok0 + grow / group) * p.nq + (size_t)(kvh * group + grow % group);
+#pragma unroll
+      for (int h = 0; h < HD; h += 32) {
+        float o[32];
+        tmem_ld32(t_o + h, o);   // warp-wide: rows that do not exist read too, and store nothing
+        if (live) {
+          uint4* dst = reinterpret_cast<uint4*>(p.out + th * HD + h);
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            uint4 v;
+            v.x = pack_bf16(o[ch * 8 + 0] * inv, o[ch * 8 + 1] * inv);
+            v.y = pack_bf16(o[ch * 8 + 2] * inv, o[ch * 8 + 3] * inv);
+            v.z = pack_bf16(o[ch * 8 + 4] * inv, o[ch * 8 + 5] * inv);
+            v.w = pack_bf16(o[ch * 8 + 6] * inv, o[ch * 8 + 7] * inv);
+            dst[ch] = v;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------- host side
+// Tensor maps are cached by what they describe; the step's buffers and the cache keep their addresses.
+static bool make_map_rows(CUtensorMap* map, const void* ptr, long long rows, int box_rows) {
+  using Key = std::tuple<const void*, long long, int>;
+  static std::map<Key, CUtensorMap> cache;
+  static std::mutex mu;
+  const Key key(ptr, rows, box_rows);
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) { *map = it->second; return true; }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+  cuuint32_t box[2] = {(cuuint32_t)HD, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  if (fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  if (cache.size() > 1024) cache.clear();
+  cache[key] = *map;
+  return true;
+}
+
+// Queries: [tokens][heads][HD] inside rows of q_row_stride elements; a box is the heads of one group for 128 / group tokens.
+static bool make_map_q(CUtensorMap* map, const void* ptr, int tokens, int nq, int q_row_stride, int group) {
+  using Key = std::tuple<const void*, int, int, int, int>;
+  static std::map<Key, CUtensorMap> cache;
+  static std::mutex mu;
+  const Key key(ptr, tokens, nq, q_row_stride, group);
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) { *map = it->second; return true; }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)nq, (cuuint64_t)tokens};
+  cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)q_row_stride * 2};
+  cuuint32_t box[3] = {(cuuint32_t)HD, (cuuint32_t)group, (cuuint32_t)(BM / group)};
+  cuuint32_t elem[3] = {1, 1, 1};
+  if (fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, elem,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  if (cache.size() > 1024) cache.clear();
+  cache[key] = *map;
+  return true;
+}
+
+}  // namespace tllm
+
+using namespace tllm;
+
+extern "C" int tllm_attention_tc_head_dim() { return HD; }
+
+// 1 if the kernel takes these sizes (the caller then need not try and fail).
+extern "C" int tllm_attention_tc_fits(int nq, int nkv, int hd, int page_size, int window) {
+  if (hd != HD || nq <= 0 || nkv <= 0 || nq % nkv != 0 || window != 0) return 0;
+  const int group = nq / nkv;
+  if (group > BM || (group & (group - 1)) != 0) return 0;
+  return page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64;
+}
+
+extern "C" int tllm_attention_tc(const void* q, int q_row_stride, const void* kcache, const void* vcache,
+                                 long long cache_pages, const int* block_table, int max_blocks, const int* cu_q,
+                                 const int* q_start, void* out, int n_tokens, int n_requests, int max_q_len, int nq,
+                                 int nkv, int hd, int page_size, float scale, int* status, void* stream) {
+  TLLM_REQUIRE(tllm_attention_tc_fits(nq, nkv, hd, page_size, 0), "attention_tc: %d heads, %d key/value heads, head size %d, page size %d "
+               "(takes head size %d, a power-of-two group up to 128, pages of 8 to 64)", nq, nkv, hd, page_size, HD);
+  TLLM_REQUIRE(n_tokens > 0 && n_requests > 0 && max_q_len > 0 && max_blocks > 0 && cache_pages > 0 && scale > 0.f && status != nullptr,
+               "attention_tc: %d tokens, %d requests, %d blocks, %lld pages", n_tokens, n_requests, max_blocks, cache_pages);
+  TLLM_REQUIRE(((uintptr_t)q % 16) == 0 && (q_row_stride % 8) == 0 && ((uintptr_t)kcache % 128) == 0 && ((uintptr_t)vcache % 128) == 0 &&
+               ((uintptr_t)out % 16) == 0, "attention_tc: operands are not aligned for TMA");
+  const int group = nq / nkv;
+  CUtensorMap mq, mk, mv;
+  const long long rows = cache_pages * nkv * page_size;
+  if (!make_map_q(&mq, q, n_tokens, nq, q_row_stride, group) || !make_map_rows(&mk, kcache, rows, page_size) ||
+      !make_map_rows(&mv, vcache, rows, page_size))
+    TLLM_FAIL(TLLM_ERR_CUDA, "attention_tc: cuTensorMapEncodeTiled failed");
+  TcAttnParams p;
+  p.block_table = block_table; p.cu_q = cu_q; p.q_start = q_start; p.out = (__nv_bfloat16*)out; p.status = status;
+  p.max_blocks = max_blocks; p.nq = nq; p.nkv = nkv; p.page_size = page_size;
+  p.tiles_per_req = (int)(((long long)max_q_len * group + BM - 1) / BM);
+  p.scale_log2 = scale * 1.4426950408889634f;
+  const long long gx = (long long)n_requests * p.tiles_per_req;
+  TLLM_REQUIRE(gx <= 2147483647LL && nkv <= 65535, "attention_tc: grid too large");
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+    if (e != cudaSuccess) TLLM_FAIL(TLLM_ERR_CUDA, "attention_tc: cannot reserve %d bytes of shared memory: %s", SMEM_TOTAL, cudaGetErrorString(e));
+    configured = true;
+  }
+  TLLM_LAUNCH("attention_tc", attention_tc_kernel, dim3((unsigned)gx, nkv), THREADS, SMEM_TOTAL, (cudaStream_t)stream, mq, mk, mv, p);
+  return TLLM_OK;
+}

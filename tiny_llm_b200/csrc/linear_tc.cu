@@ -21,13 +21,11 @@
 //
 // Reference counterparts: tiny_llm/ops/cuda/gemm.cu:67-106 (SIMT tile product) and
 // gemm_q1_helper.cu:15-124 (warp-per-output GEMV for one row).
-#include <cuda.h>
-
 #include <map>
 #include <mutex>
 #include <tuple>
 
-#include "common.cuh"
+#include "tc_common.cuh"
 
 TLLM_DEFINE_LAST_ERROR
 
@@ -42,111 +40,7 @@ enum Epilogue { EPI_BF16 = 0, EPI_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU = 3, EPI_
                 // cluster kernel: K slices reduced through distributed shared memory
                 EPI_CL_ADD_F32 = 5, EPI_CL_ROPE_KV = 6, EPI_CL_SWIGLU = 7, EPI_CL_BF16 = 8 };
 
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // a wait gives up after two seconds
 constexpr int ERR_PRODUCER = 1, ERR_MMA = 2, ERR_EPILOGUE = 3;
-
-// ---------------------------------------------------------------- PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ unsigned long long global_timer_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-// Bounded wait: false if the phase did not complete within WAIT_LIMIT_NS, or another role gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = global_timer_ns();
-  for (;;) {
-#pragma unroll 1
-    for (int i = 0; i < 32; ++i)
-      if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (global_timer_ns() - t0 > WAIT_LIMIT_NS) return false;
-  }
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
-  uint32_t r[32];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr) : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
-  uint32_t r[16];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr) : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, stored with the
-// 128-byte swizzle: 8-row groups are 1024 bytes apart (stride byte offset), descriptor version 1.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((addr & 0x3FFFF) >> 4);    // start address, 16-byte units
-  d |= (uint64_t)1 << 16;                    // leading byte offset (unused with a swizzle, K-major)
-  d |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset
-  d |= (uint64_t)1 << 46;                    // descriptor version of sm_100
-  d |= (uint64_t)2 << 61;                    // SWIZZLE_128B
-  return d;
-}
-// Instruction descriptor: bfloat16 x bfloat16 -> float32, both operands K-major, M = 128, N = n.
-__device__ __forceinline__ uint32_t instr_desc_bf16(int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-}
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
 
@@ -309,7 +203,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       }
     } else if (warp == 1 && lane == 0) {
       // ---------------- MMA issuer
-      const uint32_t idesc = instr_desc_bf16(BN);
+      const uint32_t idesc = instr_desc_bf16(BM, BN);
       bool ok = true;
       for (int i = 0; i < n_kb && ok; ++i) {
         const int s = i % STAGES;
@@ -468,7 +362,7 @@ linear_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     }
   } else if (warp == 1 && lane == 0) {
     // ---------------- MMA issuer
-    const uint32_t idesc = instr_desc_bf16(BN);
+    const uint32_t idesc = instr_desc_bf16(BM, BN);
     for (int i = 0; i < n_kb; ++i) {
       const int s = i % STAGES;
       const uint32_t parity = (i / STAGES) & 1;
@@ -631,9 +525,6 @@ linear_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 // are neighbours, so CTAs running side by side share the weight tile in L2).  Two accumulators of BN
 // columns alternate in tensor memory: while the four epilogue warps drain tile i, the MMA thread
 // already accumulates tile i + 1, and the TMA thread runs ahead of both through the ring of stages.
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
 
 template <int BN, int STAGES>
 struct PersistentSmem {
@@ -711,7 +602,7 @@ linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     }
   } else if (warp == 1 && lane == 0) {
     // ---------------- MMA issuer
-    const uint32_t idesc = instr_desc_bf16(BN);
+    const uint32_t idesc = instr_desc_bf16(BM, BN);
     int it = 0, local = 0;
     bool ok = true;
     for (int t = first_tile; t < n_tiles && ok; t += gridDim.x, ++local) {
@@ -758,23 +649,6 @@ linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
 }
 
 // ---------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  });
-  return fn;
-}
-
 // A 2-D bfloat16 tensor [rows, k] with row stride ld (elements), tiled in boxes of box_rows x 64.
 static bool make_map(CUtensorMap* map, const void* ptr, int rows, int k, long long ld, int box_rows) {
   using Key = std::tuple<const void*, int, int, long long, int>;

@@ -181,7 +181,8 @@ def check_status() -> None:
             t.zero_()
             raise KernelError(f"a kernel on device {key} gave up waiting (code {code}: 1 = TMA producer, "
                               f"2 = MMA issuer, 3 = epilogue of a matrix product; 4 = weight producer, "
-                              f"5 = consumer, 6 = grid barrier of the fused decode step); its output is not valid")
+                              f"5 = consumer, 6 = grid barrier of the fused decode step; 7 = TMA producer, 8 = MMA issuer, "
+                              f"9 = softmax of the tensor-core attention); its output is not valid")
 
 
 def _tc_ok(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
@@ -337,6 +338,9 @@ def linear_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, b
 # ----------------------------------------------------------------------------- attention
 
 
+attention_tc = os.environ.get("TLLM_ATTENTION_TC", "1") != "0"   # tcgen05 attention for prompt portions (a switch for measurements)
+
+
 def _attention_splits(num_requests: int, max_q_len: int, group: int, num_kv_heads: int, max_kv_len: int) -> int:
     """Slices of keys per (request, key/value head).  Decoded tokens (at most 16 rows) run as small
     CTAs of which three share an SM: about that many are wanted, each with at least two 64-key
@@ -366,10 +370,22 @@ def paged_attention(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_d
             k_cache.stride(2) != head_dim or k_cache.shape[1] != num_kv_heads or k_cache.shape[3] != head_dim:
         raise KernelError("paged_attention: shapes or dtypes do not fit")
     page_size = k_cache.shape[2]
+    group = num_heads // num_kv_heads
+    if qkv.dtype == torch.bfloat16 and not force_generic and attention_tc and head_dim == 64 and not window and \
+            batch.max_q_len * group >= 128 and qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0 and \
+            k_cache.is_contiguous() and v_cache.is_contiguous():
+        # portions of prompts: 128 rows of (token, head of the group) per CTA on the tcgen05 tensor cores
+        lib = build.load_library("attention_tc", flags=("-DTLLM_HEAD_DIM=64",))
+        if lib.tllm_attention_tc_fits(num_heads, num_kv_heads, head_dim, page_size, 0):
+            _check(lib, lib.tllm_attention_tc(
+                _ptr(qkv), qkv.stride(0), _ptr(k_cache), _ptr(v_cache), ctypes.c_longlong(k_cache.shape[0]),
+                _ptr(block_table), block_table.shape[1], _ptr(batch.cu_q), _ptr(batch.q_start), _ptr(out), t,
+                batch.num_requests, batch.max_q_len, num_heads, num_kv_heads, head_dim, page_size,
+                ctypes.c_float(scale), _ptr(status_word(qkv.device)), _stream()))
+            return
     if qkv.dtype == torch.bfloat16 and not force_generic and head_dim % 16 == 0 and 16 <= head_dim <= 256 and \
             qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0:
         lib = build.load_library("attention_mma", flags=(f"-DTLLM_HEAD_DIM={head_dim}",))
-        group = num_heads // num_kv_heads
         splits = 1
         if workspace is not None:
             splits = _attention_splits(batch.num_requests, batch.max_q_len, group, num_kv_heads, batch.max_kv_len)
@@ -495,4 +511,5 @@ def build_all(verbose: bool = True):
     for name in ("attention_mma", "decode_step"):
         paths += [build.compile_library(name, flags=(f"-DTLLM_HEAD_DIM={hd}",), verbose=verbose)
                   for hd in ATTENTION_HEAD_DIMS]
+    paths.append(build.compile_library("attention_tc", flags=("-DTLLM_HEAD_DIM=64",), verbose=verbose))
     return paths
