@@ -6,9 +6,11 @@
 //
 //   warp 0 (one thread): TMA.  The query tile comes as one 3-D box (head size x heads of the group x
 //     tokens) of the step's Q/K/V rows; a key tile and a value tile come page by page (one 2-D box of
-//     page_size rows each, looked up in the request's block table) into a ring of two stages.
+//     page_size rows each, looked up in the request's block table, which sits in shared memory) into a
+//     ring of four stages.
 //   warp 1 (one thread): tcgen05.mma.  S = Q K^T (M 128, N 64, K = head size; both operands
-//     K-major in 128-byte-swizzled shared memory) into tensor memory; later O += P V (M 128, N = head
+//     K-major in 128-byte-swizzled shared memory) into one of two S buffers in tensor memory, one
+//     tile ahead of the softmax; then O += P V (M 128, N = head
 //     size, K 64) with P from shared memory and V taken as it lies in the cache (rows = keys: the
 //     MN-major form of the B operand).  tcgen05.commit hands each result over on an mbarrier.
 //   warps 2-5: softmax.  A thread owns one row: it reads its 64 scores from tensor memory, applies
@@ -18,7 +20,7 @@
 //     the maximum moved.  Rows of a value tile beyond the request's last key are zeroed first (a
 //     page may hold anything there, and 0 x NaN would spoil the product).
 //
-// Two or three such CTAs share an SM, so one CTA's softmax overlaps another's MMAs.  Every wait is
+// Two such CTAs share an SM, so one CTA's softmax overlaps the other's MMAs.  Every wait is
 // bounded (two seconds), after which the kernel records a code in the status word and stops.
 //
 // Sizes: head size 64; heads per key/value head a power of two up to 128; page size 8, 16, 32 or
@@ -45,14 +47,16 @@ constexpr int HD = TLLM_HEAD_DIM;
 static_assert(HD == 64, "a row of keys must be one 128-byte swizzle row");
 constexpr int BM = 128;          // rows per CTA = MMA M
 constexpr int BNK = 64;          // keys per tile
-constexpr int KV_STAGES = 2;
+constexpr int KV_STAGES = 4;
 constexpr int THREADS = 192;     // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-5: softmax
 constexpr int UMMA_K = 16;
 constexpr int Q_BYTES = BM * HD * 2, K_BYTES = BNK * HD * 2, V_BYTES = BNK * HD * 2, P_BYTES = BM * BNK * 2;
 constexpr int OFF_K = Q_BYTES, OFF_V = OFF_K + KV_STAGES * K_BYTES, OFF_P = OFF_V + KV_STAGES * V_BYTES;
 constexpr int OFF_BAR = OFF_P + P_BYTES;
-constexpr int SMEM_TOTAL = OFF_BAR + 128 + 1024;   // barriers and the tensor-memory slot; alignment slack
-constexpr uint32_t TMEM_COLS = 128;                // S: columns [0, 64); O: columns [64, 64 + HD)
+constexpr int MAX_TABLE = 1024;                    // block-table entries kept in shared memory (longer tables are read from global)
+constexpr int OFF_TABLE = OFF_BAR + 160;
+constexpr int SMEM_TOTAL = OFF_TABLE + MAX_TABLE * 4 + 1024;   // + alignment slack
+constexpr uint32_t TMEM_COLS = 256;                // S of even tiles: columns [0, 64); of odd tiles: [64, 128); O: [128, 128 + HD)
 constexpr int ERR_ATT_PRODUCER = 7, ERR_ATT_MMA = 8, ERR_ATT_SOFTMAX = 9;
 
 struct TcAttnParams {
@@ -61,7 +65,7 @@ struct TcAttnParams {
   const int* q_start;       // [R]: position of the request's first token in this step
   __nv_bfloat16* out;       // [T, nq * HD]
   int* status;
-  int max_blocks, nq, nkv, page_size, tiles_per_req;
+  int max_blocks, nq, nkv, page_size, tiles_per_req, n_requests;
   float scale_log2;         // scale * log2(e)
 };
 
@@ -85,22 +89,27 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   uint64_t* k_full = bars + 1;                   // [KV_STAGES]
   uint64_t* v_full = k_full + KV_STAGES;         // [KV_STAGES]
   uint64_t* kv_empty = v_full + KV_STAGES;       // [KV_STAGES]
-  uint64_t* s_full = kv_empty + KV_STAGES;       // S of this tile is in tensor memory
-  uint64_t* p_full = s_full + 1;                 // P of this tile is in shared memory, O rescaled (128 arrivals)
+  uint64_t* s_full = kv_empty + KV_STAGES;       // [2]: S of an even / odd tile is in tensor memory
+  uint64_t* p_full = s_full + 2;                 // P of this tile is in shared memory, O rescaled (128 arrivals)
   uint64_t* pv_done = p_full + 1;                // O holds this tile too; P and the stage are free
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  int* table_s = reinterpret_cast<int*>(smem + OFF_TABLE);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // the tiles of the latest tokens see the most keys: they are scheduled first
-  const int req = blockIdx.x / p.tiles_per_req, tile = p.tiles_per_req - 1 - blockIdx.x % p.tiles_per_req;
-  const int kvh = blockIdx.y;
+  // CTAs start in the order of blockIdx.x.  The tiles of the latest tokens see the most keys, so the
+  // order is: the last tile of every request and key/value head, then the tiles before them, and so
+  // on; the short ones fill the gaps at the end instead of the long ones trailing behind.
+  const int kvh = blockIdx.x % p.nkv;
+  const int req = (blockIdx.x / p.nkv) % p.n_requests;
+  const int tile = p.tiles_per_req - 1 - blockIdx.x / (p.nkv * p.n_requests);
   const int group = p.nq / p.nkv;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&kv_empty[s], 1); }
-    mbar_init(s_full, 1);
+    mbar_init(&s_full[0], 1);
+    mbar_init(&s_full[1], 1);
     mbar_init(p_full, 128);
     mbar_init(pv_done, 1);
     *abort_flag = 0;
@@ -113,6 +122,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   const uint32_t tmem_base = *tmem_slot;
   pdl_trigger();
   pdl_wait();
+  // the request's block table, so that the producer's page lookups are not a chain of global loads
+  for (int b = threadIdx.x; b < min(p.max_blocks, MAX_TABLE); b += THREADS)
+    table_s[b] = p.block_table[(size_t)req * p.max_blocks + b];
+  __syncthreads();
 
   const int tok0 = p.cu_q[req];
   const int q_len = p.cu_q[req + 1] - tok0;
@@ -145,7 +158,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       for (int g = 0; g < pages_per_tile; ++g) {
         const int blk = i * pages_per_tile + g;
         int page = -1;
-        if (blk < p.max_blocks && blk * p.page_size < kv_end) page = table[blk];
+        if (blk < p.max_blocks && blk * p.page_size < kv_end) page = blk < MAX_TABLE ? table_s[blk] : table[blk];
         pages[g] = page;
         n_valid += page >= 0 ? 1 : 0;
       }
@@ -163,21 +176,28 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const uint32_t idesc_qk = instr_desc_bf16(BM, BNK);
     const uint32_t idesc_pv = instr_desc_bf16(BM, HD, true);   // V as it lies: rows = keys (MN-major B)
     const uint32_t q_addr = smem_u32(smem), p_addr = smem_u32(smem + OFF_P);
-    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + BNK;
+    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * BNK;
     bool ok = n_tiles == 0 || mbar_wait(q_full, 0, abort_flag);
-    if (!ok) { *abort_flag = 1; atomicExch(p.status, ERR_ATT_MMA); }
-    for (int i = 0; i < n_tiles && ok; ++i) {
-      const int s = i % KV_STAGES;
-      const uint32_t ring_parity = (i / KV_STAGES) & 1, tile_parity = i & 1;
-      if (!mbar_wait(&k_full[s], ring_parity, abort_flag)) { ok = false; break; }
+    // S = Q K^T of tile t into the S buffer of its parity; it runs one tile ahead of O += P V
+    auto issue_qk = [&](int t) -> bool {
+      const int s = t % KV_STAGES;
+      if (!mbar_wait(&k_full[s], (t / KV_STAGES) & 1, abort_flag)) return false;
       tc_fence_after();
       const uint32_t k_addr = smem_u32(smem + OFF_K + s * K_BYTES);
 #pragma unroll
       for (int k = 0; k < HD / UMMA_K; ++k)
-        umma_bf16(tmem_s, smem_desc_sw128(q_addr + k * UMMA_K * 2), smem_desc_sw128(k_addr + k * UMMA_K * 2), idesc_qk, k > 0 ? 1u : 0u);
-      umma_commit(s_full);
-      if (!mbar_wait(p_full, tile_parity, abort_flag)) { ok = false; break; }
-      if (!mbar_wait(&v_full[s], ring_parity, abort_flag)) { ok = false; break; }
+        umma_bf16(tmem_s + (t & 1) * BNK, smem_desc_sw128(q_addr + k * UMMA_K * 2), smem_desc_sw128(k_addr + k * UMMA_K * 2),
+                  idesc_qk, k > 0 ? 1u : 0u);
+      umma_commit(&s_full[t & 1]);
+      return true;
+    };
+    if (ok && n_tiles > 0) ok = issue_qk(0);
+    for (int i = 0; i < n_tiles && ok; ++i) {
+      const int s = i % KV_STAGES;
+      // the other S buffer is free: the softmax of tile i - 1 has read it (its P was waited for below)
+      if (i + 1 < n_tiles && !issue_qk(i + 1)) { ok = false; break; }
+      if (!mbar_wait(p_full, i & 1, abort_flag)) { ok = false; break; }
+      if (!mbar_wait(&v_full[s], (i / KV_STAGES) & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const uint32_t v_addr = smem_u32(smem + OFF_V + s * V_BYTES);
 #pragma unroll
@@ -195,7 +215,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const int grow = row0 + row;
     const bool live = grow < rows_total;
     const int pos = start + grow / group;
-    const uint32_t t_s = tmem_base + ((uint32_t)(quad * 32) << 16), t_o = t_s + BNK;
+    const uint32_t t_s0 = tmem_base + ((uint32_t)(quad * 32) << 16), t_o = t_s0 + 2 * BNK;
     uint8_t* p_row = smem + OFF_P + row * 128;
     const int soft_tid = (warp - 2) * 32 + lane;   // 0..127 among the softmax threads
     const float c = p.scale_log2;
@@ -203,33 +223,48 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     bool ok = true;
     for (int i = 0; i < n_tiles; ++i) {
       const int s = i % KV_STAGES;
-      ok = mbar_wait(s_full, i & 1, abort_flag);
+      ok = mbar_wait(&s_full[i & 1], (i >> 1) & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
+      const uint32_t t_s = t_s0 + (i & 1) * BNK;
       float sc[BNK];
-      tmem_ld32(t_s, sc);
-      tmem_ld32(t_s + 32, sc + 32);
+      {
+        uint32_t raw[BNK];
+        tmem_ld32_issue(t_s, raw);          // both halves in flight, one wait
+        tmem_ld32_issue(t_s + 32, raw + 32);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < BNK; ++j) sc[j] = __uint_as_float(raw[j]);
+      }
       const int j0 = i * BNK;
       if (!live || j0 + BNK - 1 > pos) {   // the tile touches this row's causal edge (or the row does not exist)
 #pragma unroll
         for (int j = 0; j < BNK; ++j)
           if (!(live && j0 + j <= pos)) sc[j] = -CUDART_INF_F;
       }
-      float mx = sc[0];
+      // maximum and sum as four interleaved chains: 64 dependent steps would cost more than the arithmetic
+      float mx4[4] = {sc[0], sc[1], sc[2], sc[3]};
 #pragma unroll
-      for (int j = 1; j < BNK; ++j) mx = fmaxf(mx, sc[j]);
+      for (int j = 4; j < BNK; j += 4) {
+        mx4[0] = fmaxf(mx4[0], sc[j]); mx4[1] = fmaxf(mx4[1], sc[j + 1]);
+        mx4[2] = fmaxf(mx4[2], sc[j + 2]); mx4[3] = fmaxf(mx4[3], sc[j + 3]);
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float mn = fmaxf(m_run, mx * c);
       const float ms = mn == -CUDART_INF_F ? 0.f : mn;
       const float corr = ex2(m_run - ms);   // 0 while nothing was seen
       m_run = mn;
-      float sum = 0.f;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int j = 0; j < BNK; ++j) {
-        sc[j] = ex2(fmaf(sc[j], c, -ms));
-        sum += sc[j];
+      for (int j = 0; j < BNK; j += 4) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          sc[j + e] = ex2(fmaf(sc[j + e], c, -ms));
+          sum4[e] += sc[j + e];
+        }
       }
-      l_run = l_run * corr + sum;
+      l_run = l_run * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
       if (i > 0) {   // the product before this one has read P and finished O
         ok = mbar_wait(pv_done, (i - 1) & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
@@ -387,15 +422,16 @@ extern "C" int tllm_attention_tc(const void* q, int q_row_stride, const void* kc
   p.block_table = block_table; p.cu_q = cu_q; p.q_start = q_start; p.out = (__nv_bfloat16*)out; p.status = status;
   p.max_blocks = max_blocks; p.nq = nq; p.nkv = nkv; p.page_size = page_size;
   p.tiles_per_req = (int)(((long long)max_q_len * group + BM - 1) / BM);
+  p.n_requests = n_requests;
   p.scale_log2 = scale * 1.4426950408889634f;
-  const long long gx = (long long)n_requests * p.tiles_per_req;
-  TLLM_REQUIRE(gx <= 2147483647LL && nkv <= 65535, "attention_tc: grid too large");
+  const long long gx = (long long)n_requests * p.tiles_per_req * nkv;
+  TLLM_REQUIRE(gx <= 2147483647LL, "attention_tc: grid too large");
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
     if (e != cudaSuccess) TLLM_FAIL(TLLM_ERR_CUDA, "attention_tc: cannot reserve %d bytes of shared memory: %s", SMEM_TOTAL, cudaGetErrorString(e));
     configured = true;
   }
-  TLLM_LAUNCH("attention_tc", attention_tc_kernel, dim3((unsigned)gx, nkv), THREADS, SMEM_TOTAL, (cudaStream_t)stream, mq, mk, mv, p);
+  TLLM_LAUNCH("attention_tc", attention_tc_kernel, dim3((unsigned)gx), THREADS, SMEM_TOTAL, (cudaStream_t)stream, mq, mk, mv, p);
   return TLLM_OK;
 }
