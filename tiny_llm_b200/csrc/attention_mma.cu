@@ -38,9 +38,13 @@ attention_mma_kernel(const AttnParams p) {
   pdl_trigger();
   pdl_wait();
 
-  // the tiles of the latest tokens see the most keys: they are scheduled first
-  const int req = blockIdx.x / p.tiles_per_req, tile = p.tiles_per_req - 1 - blockIdx.x % p.tiles_per_req;
-  const int kvh = blockIdx.y, split = blockIdx.z;
+  // CTAs start in the order of blockIdx.x.  The tiles of the latest tokens see the most keys, so the
+  // order is: the last tile of every request and key/value head, then the tiles before them, and so
+  // on; the short ones fill the gaps at the end instead of the long ones trailing behind.
+  const int kvh = blockIdx.x % p.nkv;
+  const int req = (blockIdx.x / p.nkv) % p.n_requests;
+  const int tile = p.tiles_per_req - 1 - blockIdx.x / (p.nkv * p.n_requests);
+  const int split = blockIdx.z;
   const int group = p.nq / p.nkv;
   const int tok0 = p.cu_q[req];
   const int q_len = p.cu_q[req + 1] - tok0;
@@ -271,7 +275,7 @@ extern "C" int tllm_attention_mma(const void* q, int q_row_stride, const void* k
   p.part_o = (float*)scratch;
   p.part_ml = splits > 1 ? (float*)scratch + (size_t)n_tokens * nq * splits * HD : nullptr;
   p.page_stride = page_stride; p.head_stride = head_stride; p.q_row_stride = q_row_stride; p.max_blocks = max_blocks;
-  p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.window = window; p.splits = splits;
+  p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.window = window; p.splits = splits; p.n_requests = n_requests;
   p.scale_log2 = scale * 1.4426950408889634f;
   // decoded tokens (at most 16 rows per request and key/value head): one-warp CTAs, four stages
   const bool small = (long long)max_q_len * group <= 16;
@@ -300,7 +304,8 @@ extern "C" int tllm_attention_mma(const void* q, int q_row_stride, const void* k
       if (e != cudaSuccess) TLLM_FAIL(TLLM_ERR_CUDA, "attention_mma: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
       configured = true;
     }
-    TLLM_LAUNCH("attention_mma", (attention_mma_kernel<4, ST>), dim3((unsigned)gx, nkv, splits), 128, smem, s, p);
+    TLLM_REQUIRE(gx * nkv <= 2147483647LL, "attention_mma: grid too large");
+    TLLM_LAUNCH("attention_mma", (attention_mma_kernel<4, ST>), dim3((unsigned)(gx * nkv), 1, splits), 128, smem, s, p);
   }
   if (splits > 1)
     TLLM_LAUNCH("attention_combine", attention_combine_kernel, (unsigned)((size_t)n_tokens * nq), HD >= 128 ? 128 : 64, 0, s,

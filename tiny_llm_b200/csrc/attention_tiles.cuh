@@ -63,7 +63,7 @@ struct AttnParams {
   float* part_o;                 // [T * nq, splits, HD]   (splits > 1)
   float* part_ml;                // [T * nq, splits, 2]
   long long page_stride, head_stride;
-  int q_row_stride, max_blocks, nq, nkv, page_size, window, tiles_per_req, splits;
+  int q_row_stride, max_blocks, nq, nkv, page_size, window, tiles_per_req, splits, n_requests;
   float scale_log2;              // scale * log2(e)
 };
 

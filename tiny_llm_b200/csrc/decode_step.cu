@@ -598,7 +598,7 @@ __device__ __forceinline__ void attention_phase(const DecodeParams& p, const Dec
   ap.cu_q = p.cu_q; ap.q_start = p.positions; ap.out = p.attn_out; ap.part_o = p.part_o; ap.part_ml = p.part_ml;
   ap.head_stride = (long long)p.page_size * HD; ap.page_stride = ap.head_stride * p.nkv;
   ap.q_row_stride = p.nq * HD; ap.max_blocks = p.max_blocks; ap.nq = p.nq; ap.nkv = p.nkv; ap.page_size = p.page_size;
-  ap.window = L->window; ap.tiles_per_req = 1; ap.splits = p.splits; ap.scale_log2 = L->scale_log2;
+  ap.window = L->window; ap.tiles_per_req = 1; ap.splits = p.splits; ap.n_requests = p.m; ap.scale_log2 = L->scale_log2;
   const int items = p.m * p.nkv * p.splits;
   auto team_sync = [team] { named_sync(2 + team, 128); };
   for (int it = (int)blockIdx.x * TEAMS + team; it < items; it += (int)gridDim.x * TEAMS) {
