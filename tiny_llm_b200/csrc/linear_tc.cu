@@ -38,7 +38,9 @@ constexpr int THREADS = 192;   // warp 0: TMA, warp 1: MMA + tensor-memory alloc
 
 enum Epilogue { EPI_BF16 = 0, EPI_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU = 3, EPI_ATOMIC_F32 = 4,
                 // cluster kernel: K slices reduced through distributed shared memory
-                EPI_CL_ADD_F32 = 5, EPI_CL_ROPE_KV = 6, EPI_CL_SWIGLU = 7, EPI_CL_BF16 = 8 };
+                EPI_CL_ADD_F32 = 5, EPI_CL_ROPE_KV = 6, EPI_CL_SWIGLU = 7, EPI_CL_BF16 = 8,
+                // NORMAL orientation: Q/K/V projection with rotation and cache write (head size 64 or 128)
+                EPI_ROPE_KV = 9 };
 
 constexpr int ERR_PRODUCER = 1, ERR_MMA = 2, ERR_EPILOGUE = 3;
 
@@ -53,8 +55,93 @@ struct SmemLayout {
   static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 1) * 8 + 16 + 1024;   // + alignment slack
 };
 
+// What the rotate-and-cache epilogues need (either orientation); cy, cz only concern the cluster kernel.
+struct ClusterArgs {
+  int cy, cz;                      // cluster extent over row tiles (1, or 2 for gate/up pairs) and over K slices
+  const int* positions;            // [tokens]
+  const float* cos;                // [positions, hd / 2] or null: no rotation
+  const float* sin;
+  __nv_bfloat16* kcache;           // [pages, nkv, page_size, hd]
+  __nv_bfloat16* vcache;
+  const int* slot_mapping;         // [tokens] or null: the rows hold queries only
+  long long page_stride, head_stride;
+  int nq, nkv, hd, page_size;
+};
+
 // Epilogue of one 128 x BN tile of C in the NORMAL orientation: this thread owns row `row` of the
 // tile (tensor-memory lane), walks its BN columns in chunks of 32 and stores them as EPI says.
+// Q/K/V projection, NORMAL orientation: this thread owns token `m`; the tile's BN columns are whole
+// heads.  Per head the two halves of the rotation pairs are read 32 columns at a time, rounded to
+// bfloat16 (the projection's output is a bfloat16 tensor of the model), rotated in 32-bit and
+// written: queries to the row of `out`, keys and values to the token's slot of the cache.
+template <int BN>
+__device__ __forceinline__ void store_tile_rope_kv(uint32_t taddr, int m, int tile_b, int rows_a, int rows_b,
+                                                   void* __restrict__ out, int ldo, const ClusterArgs& ca) {
+  const int hd = ca.hd, half = hd / 2;   // 64 or 128: half = 32 or 64
+  const bool row_ok = m < rows_a;
+  int pos = 0, slot = -1;
+  if (row_ok) {
+    pos = ca.positions ? ca.positions[m] : 0;
+    slot = ca.slot_mapping ? ca.slot_mapping[m] : -1;
+  }
+  // 32 rotation pairs at a time: their cosines and sines are loaded once (16-byte loads from this token's
+  // row of the tables) and serve every head of the tile
+#pragma unroll 1
+  for (int sub = 0; sub < half; sub += 32) {
+    float cs[32], sn[32];
+    const bool tables = row_ok && ca.cos != nullptr;
+    if (tables) {
+      const float4* c4 = reinterpret_cast<const float4*>(ca.cos + (size_t)pos * half + sub);
+      const float4* s4 = reinterpret_cast<const float4*>(ca.sin + (size_t)pos * half + sub);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float4 c = c4[j], s = s4[j];
+        cs[4 * j] = c.x; cs[4 * j + 1] = c.y; cs[4 * j + 2] = c.z; cs[4 * j + 3] = c.w;
+        sn[4 * j] = s.x; sn[4 * j + 1] = s.y; sn[4 * j + 2] = s.z; sn[4 * j + 3] = s.w;
+      }
+    }
+#pragma unroll 1
+    for (int h0 = 0; h0 < BN; h0 += hd) {
+      const int n0 = tile_b * BN + h0;          // first column of this head
+      const int head = n0 / hd;
+      float lo[32], hi[32];
+      tmem_ld32(taddr + h0 + sub, lo);          // warp-wide: every lane reads, whatever it stores
+      tmem_ld32(taddr + h0 + half + sub, hi);
+      if (!row_ok || n0 >= rows_b) continue;
+      const bool is_q = head < ca.nq, is_v = head >= ca.nq + ca.nkv;
+      __nv_bfloat16* dst;
+      if (is_q) {
+        dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)m * ldo + n0;
+      } else {
+        if (slot < 0) continue;
+        dst = (is_v ? ca.vcache : ca.kcache) + (long long)(slot / ca.page_size) * ca.page_stride +
+              (long long)(head - ca.nq - (is_v ? ca.nkv : 0)) * ca.head_stride + (long long)(slot % ca.page_size) * hd;
+      }
+      const bool rotate = !is_v && tables;
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        uint4 pl, ph;
+        __nv_bfloat162* l2 = reinterpret_cast<__nv_bfloat162*>(&pl);
+        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&ph);
+#pragma unroll
+        for (int e = 0; e < 8; e += 2) {
+          float o_lo[2], o_hi[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const float x = __bfloat162float(__float2bfloat16_rn(lo[j + e + u])), y = __bfloat162float(__float2bfloat16_rn(hi[j + e + u]));
+            o_lo[u] = rotate ? cs[j + e + u] * x - sn[j + e + u] * y : x;
+            o_hi[u] = rotate ? sn[j + e + u] * x + cs[j + e + u] * y : y;
+          }
+          l2[e / 2] = __floats2bfloat162_rn(o_lo[0], o_lo[1]);
+          h2[e / 2] = __floats2bfloat162_rn(o_hi[0], o_hi[1]);
+        }
+        *reinterpret_cast<uint4*>(dst + sub + j) = pl;
+        *reinterpret_cast<uint4*>(dst + half + sub + j) = ph;
+      }
+    }
+  }
+}
+
 template <int BN, int EPI>
 __device__ __forceinline__ void store_tile_normal(uint32_t taddr, int row, int tile_a, int tile_b, int rows_a,
                                                   int rows_b, void* __restrict__ out, int ldo) {
@@ -275,18 +362,6 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 // sum is fixed.  Epilogues: add into the float32 residual stream; round to bfloat16, rotate Q and K
 // by position and write K, V into their pages (a tile holds whole heads, so both halves of a rotation
 // pair are at hand); SiLU(gate) * up; plain bfloat16 store.
-struct ClusterArgs {
-  int cy, cz;                      // cluster extent over row tiles (1, or 2 for gate/up pairs) and over K slices
-  const int* positions;            // [tokens]
-  const float* cos;                // [positions, hd / 2] or null: no rotation
-  const float* sin;
-  __nv_bfloat16* kcache;           // [pages, nkv, page_size, hd]
-  __nv_bfloat16* vcache;
-  const int* slot_mapping;         // [tokens] or null: the rows hold queries only
-  long long page_stride, head_stride;
-  int nq, nkv, hd, page_size;
-};
-
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -539,7 +614,7 @@ template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                             void* __restrict__ out, int rows_a, int rows_b, int k_blocks, int ldo,
-                            int* __restrict__ status) {
+                            const ClusterArgs ca, int* __restrict__ status) {
   static_assert(2 * BN <= 512, "two accumulators must fit tensor memory");
   using L = PersistentSmem<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
@@ -637,7 +712,8 @@ linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       if (!ok) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quad * 32) << 16);
-      store_tile_normal<BN, EPI>(taddr, row, t % tiles_m, t / tiles_m, rows_a, rows_b, out, ldo);
+      if (EPI == EPI_ROPE_KV) store_tile_rope_kv<BN>(taddr, (t % tiles_m) * BM + row, t / tiles_m, rows_a, rows_b, out, ldo, ca);
+      else store_tile_normal<BN, EPI>(taddr, row, t % tiles_m, t / tiles_m, rows_a, rows_b, out, ldo);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buf]);   // four arrivals free the accumulator
@@ -694,7 +770,7 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int r
 
 template <int EPI>
 static int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int m, int n, int k, int ldo,
-                             int* status, cudaStream_t s) {
+                             int* status, cudaStream_t s, const ClusterArgs& ca = ClusterArgs()) {
   constexpr int BN = 256, STAGES = 4;
   using L = PersistentSmem<BN, STAGES>;
   auto kern = linear_tc_persistent_kernel<BN, STAGES, EPI>;
@@ -710,7 +786,7 @@ static int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, void*
   }
   const int tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
   const int grid = tiles < sm_count ? tiles : sm_count;
-  TLLM_LAUNCH("linear_tc_persistent", kern, grid, THREADS, L::TOTAL, s, ma, mb, out, m, n, (k + BK - 1) / BK, ldo, status);
+  TLLM_LAUNCH("linear_tc_persistent", kern, grid, THREADS, L::TOTAL, s, ma, mb, out, m, n, (k + BK - 1) / BK, ldo, ca, status);
   return TLLM_OK;
 }
 
@@ -810,7 +886,8 @@ extern "C" int tllm_linear_tc(const void* a, const void* w, void* out, int m, in
 //   5: out (float32 [M, N]) += product;
 //   6: Q/K/V projection: out (bfloat16, row stride ldo) gets the rotated queries; rotated keys and the values
 //      go to their pages at slot_mapping (null: the rows are queries only).  N = (nq + 2 nkv) hd (or nq hd),
-//      hd divides 128; cos/sin null: no rotation;
+//      hd 16, 32, 64 or 128; cos/sin null: no rotation.  This one also takes more than 128 rows (head size
+//      64 or 128): then it runs as 128 x 256 tiles of C with the same epilogue per tile;
 //   7: SiLU(gate) * up with gate/up rows of w interleaved in blocks of 128, out bfloat16 [M, N/2]
 //      (slices <= 4: the cluster also spans the gate tile and the up tile);
 //   8: out (bfloat16 [M, N]) = product.
@@ -819,7 +896,8 @@ extern "C" int tllm_linear_tc_cluster(const void* a, const void* w, void* out, i
                                       int nq, int nkv, int hd, void* kcache, void* vcache, const int* slot_mapping,
                                       int page_size, long long page_stride, long long head_stride, int* status,
                                       void* stream) {
-  TLLM_REQUIRE(m > 0 && m <= 128 && n > 0 && k > 0, "linear_tc_cluster: product %d x %d x %d (at most 128 rows)", m, n, k);
+  TLLM_REQUIRE(m > 0 && n > 0 && k > 0 && (m <= 128 || epi == EPI_CL_ROPE_KV),
+               "linear_tc_cluster: product %d x %d x %d (at most 128 rows, except for the Q/K/V projection)", m, n, k);
   TLLM_REQUIRE(k % 8 == 0 && lda % 8 == 0, "linear_tc_cluster: K (%d) and the row stride of A (%d) must be multiples of 8", k, lda);
   TLLM_REQUIRE(((uintptr_t)a % 16) == 0 && ((uintptr_t)w % 16) == 0, "linear_tc_cluster: operands must be 16-byte aligned");
   TLLM_REQUIRE(status != nullptr, "linear_tc_cluster: needs a status word");
@@ -843,6 +921,13 @@ extern "C" int tllm_linear_tc_cluster(const void* a, const void* w, void* out, i
   }
   cudaStream_t s = (cudaStream_t)stream;
   CUtensorMap ma, mb;
+  if (m > 128) {
+    // many tokens: 128 x 256 tiles of C as in tllm_linear_tc, with the rotation and the cache write in the epilogue
+    TLLM_REQUIRE(hd == 64 || hd == 128, "linear_tc_cluster: the Q/K/V epilogue for more than 128 tokens takes head size 64 or 128 (got %d)", hd);
+    if (!make_map(&ma, a, m, k, lda, BM) || !make_map(&mb, w, n, k, k, 256))
+      TLLM_FAIL(TLLM_ERR_CUDA, "linear_tc_cluster: cuTensorMapEncodeTiled failed");
+    return launch_persistent<EPI_ROPE_KV>(ma, mb, out, m, n, k, ldo, status, s, ca);
+  }
   const int bn = m <= 16 ? 16 : (m <= 32 ? 32 : (m <= 64 ? 64 : 128));
   if (!make_map(&ma, w, n, k, k, BM) || !make_map(&mb, a, m, k, lda, bn))
     TLLM_FAIL(TLLM_ERR_CUDA, "linear_tc_cluster: cuTensorMapEncodeTiled failed");

@@ -232,12 +232,13 @@ def linear_rope_kv(h: torch.Tensor, w_qkv: torch.Tensor, qkv: torch.Tensor, posi
                    cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], num_heads: int, num_kv_heads: int,
                    head_dim: int, k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
                    slot_mapping: Optional[torch.Tensor]) -> bool:
-    """Q/K/V projection of at most 128 tokens with the rotation and the cache write in its epilogue:
+    """Q/K/V projection with the rotation and the cache write in its epilogue (a cluster per weight tile
+    for at most 128 tokens, 128 x 256 tiles of the product for more):
     the rotated queries go to the first num_heads*head_dim values of each `qkv` row, rotated keys and
     values straight into their pages (slot_mapping None: `w_qkv` holds the query rows only).  Returns
     False, having done nothing, where the fused kernel does not apply (then: linear + rope_kv_write)."""
     m = h.shape[0]
-    if not ((cluster_mask & 2) and _tc_ok(h, w_qkv, qkv) and m <= 128 and head_dim in (16, 32, 64, 128) and
+    if not ((cluster_mask & 2) and _tc_ok(h, w_qkv, qkv) and head_dim in ((16, 32, 64, 128) if m <= 128 else (64, 128)) and
             qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1 and w_qkv.is_contiguous() and
             (cos is None or cos.shape[1] * 2 == head_dim)):
         return False
@@ -250,7 +251,7 @@ def linear_rope_kv(h: torch.Tensor, w_qkv: torch.Tensor, qkv: torch.Tensor, posi
     if slot_mapping is not None and (k_cache.dtype != torch.bfloat16 or k_cache.stride() != v_cache.stride() or
                                      k_cache.stride(3) != 1 or k_cache.stride(2) != head_dim):
         raise KernelError("linear_rope_kv: cache layout does not fit")
-    _cluster_call(EPI_CL_ROPE_KV, h, w_qkv, qkv, _cluster_slices(want, h.shape[1]), positions, cos, sin, num_heads,
+    _cluster_call(EPI_CL_ROPE_KV, h, w_qkv, qkv, _cluster_slices(want, h.shape[1]) if m <= 128 else 1, positions, cos, sin, num_heads,
                   num_kv_heads, head_dim, k_cache if slot_mapping is not None else None,
                   v_cache if slot_mapping is not None else None, slot_mapping)
     return True
