@@ -122,6 +122,11 @@ def test_linear_with_k_slices_reduced_in_a_cluster(ops, m, n, k, monkeypatch):
     same = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
     ops.linear(a.to(DEV), w.to(DEV), same)
     assert float((same.float().cpu() - ref).abs().max()) <= tol("bfloat16", scale)
+    for slices in (3, 7):   # cluster extents that do not divide the tile's 128 rows
+        if slices <= -(-k // 64):
+            acc = torch.full((m, n), 0.25, device=DEV)
+            ops._cluster_call(ops.EPI_CL_ADD_F32, a.to(DEV), w.to(DEV), acc, slices)
+            assert float((acc.cpu() - ref - 0.25).abs().max()) <= 2e-5 * max(scale, 1), slices
     ops.check_status()
 
 

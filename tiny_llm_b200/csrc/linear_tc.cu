@@ -491,12 +491,13 @@ linear_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   const int m0 = tile_b * BN;
   if (EPI == EPI_CL_SWIGLU) {
     // ranks (0, z) hold the gate tile's slices, ranks (1, z) the up tile's; the 128 rows are dealt to all CY * CZ CTAs
-    const int rows_per = BM / (CY * CZ), r0 = (my_y + my_z * CY) * rows_per, quads = rows_per / 4;
+    // (shares are whole groups of four rows; with 6 CTAs the last share is short)
+    const int rows_per = ((BM + CY * CZ - 1) / (CY * CZ) + 3) & ~3, r0 = (my_y + my_z * CY) * rows_per, quads = rows_per / 4;
     const int col0 = (tile_a / 2) * BM;            // first output column of this gate/up pair
     for (int idx = threadIdx.x; idx < quads * BN; idx += THREADS) {
       const int j = idx / quads, r = r0 + (idx % quads) * 4;
       const int m = m0 + j, col = col0 + r;
-      if (m >= rows_b) continue;
+      if (m >= rows_b || r >= BM) continue;
       const uint32_t at = base + (uint32_t)(j * BM + r) * 4u;
       float4 part[8];
 #pragma unroll
@@ -520,12 +521,12 @@ linear_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   } else if (EPI == EPI_CL_ROPE_KV) {
     // pairs (d, d + hd/2) of whole heads: 64 pairs per tile, dealt to the CZ CTAs, four neighbouring pairs per item
     const int half = ca.hd / 2;
-    const int pairs_per = (BM / 2) / CZ, p0 = my_z * pairs_per, quads = pairs_per / 4;
+    const int pairs_per = ((BM / 2 + CZ - 1) / CZ + 3) & ~3, p0 = my_z * pairs_per, quads = pairs_per / 4;
     for (int idx = threadIdx.x; idx < quads * BN; idx += THREADS) {
       const int j = idx / quads, q = p0 + (idx % quads) * 4;
       const int r_lo = (q / half) * ca.hd + q % half, r_hi = r_lo + half;
       const int m = m0 + j, n_lo = tile_a * BM + r_lo;
-      if (m >= rows_b || n_lo + half >= rows_a) continue;   // heads are whole: the four pairs exist together
+      if (m >= rows_b || q >= BM / 2 || n_lo + half >= rows_a) continue;   // heads are whole: the four pairs exist together
       const uint32_t at_lo = base + (uint32_t)(j * BM + r_lo) * 4u, at_hi = base + (uint32_t)(j * BM + r_hi) * 4u;
       float4 pl[8], ph[8];
 #pragma unroll
@@ -569,11 +570,11 @@ linear_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       }
     }
   } else {
-    const int rows_per = BM / CZ, r0 = my_z * rows_per, quads = rows_per / 4;
+    const int rows_per = ((BM + CZ - 1) / CZ + 3) & ~3, r0 = my_z * rows_per, quads = rows_per / 4;
     for (int idx = threadIdx.x; idx < quads * BN; idx += THREADS) {
       const int j = idx / quads, r = r0 + (idx % quads) * 4;
       const int m = m0 + j, n = tile_a * BM + r;
-      if (m >= rows_b || n >= rows_a) continue;
+      if (m >= rows_b || r >= BM || n >= rows_a) continue;
       const uint32_t at = base + (uint32_t)(j * BM + r) * 4u;
       float4 part[8];
 #pragma unroll
@@ -882,7 +883,7 @@ extern "C" int tllm_linear_tc(const void* a, const void* w, void* out, int m, in
 }
 
 // The same product for at most 128 rows of A with the K slices of a weight tile reduced inside a
-// thread-block cluster (`slices` = 1, 2, 4 or 8) and one of these epilogues:
+// thread-block cluster (`slices` = 1 to 8) and one of these epilogues:
 //   5: out (float32 [M, N]) += product;
 //   6: Q/K/V projection: out (bfloat16, row stride ldo) gets the rotated queries; rotated keys and the values
 //      go to their pages at slot_mapping (null: the rows are queries only).  N = (nq + 2 nkv) hd (or nq hd),
@@ -901,7 +902,7 @@ extern "C" int tllm_linear_tc_cluster(const void* a, const void* w, void* out, i
   TLLM_REQUIRE(k % 8 == 0 && lda % 8 == 0, "linear_tc_cluster: K (%d) and the row stride of A (%d) must be multiples of 8", k, lda);
   TLLM_REQUIRE(((uintptr_t)a % 16) == 0 && ((uintptr_t)w % 16) == 0, "linear_tc_cluster: operands must be 16-byte aligned");
   TLLM_REQUIRE(status != nullptr, "linear_tc_cluster: needs a status word");
-  TLLM_REQUIRE(slices == 1 || slices == 2 || slices == 4 || slices == 8, "linear_tc_cluster: %d slices of K (1, 2, 4 or 8)", slices);
+  TLLM_REQUIRE(slices >= 1 && slices <= 8, "linear_tc_cluster: %d slices of K (1 to 8: a cluster has at most 8 CTAs)", slices);
   TLLM_REQUIRE(slices <= (k + BK - 1) / BK, "linear_tc_cluster: %d slices of a K of %d", slices, k);
   ClusterArgs ca = {};
   ca.cy = 1; ca.cz = slices;
