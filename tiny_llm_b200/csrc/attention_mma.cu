@@ -234,12 +234,14 @@ attention_decode_kernel(const AttnParams p) {
   attention_decode_item<STAGES>(p, blockIdx.x, blockIdx.y, blockIdx.z, threadIdx.x, smem_raw, [] { __syncthreads(); });
 }
 
-// Merges the slices of every (token, head), one CTA each.
-__global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                         __nv_bfloat16* __restrict__ out, int splits) {
+// Merges the slices of every (token, head), one warp each.
+__global__ void __launch_bounds__(128)
+attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                         __nv_bfloat16* __restrict__ out, int splits, int rows) {
   pdl_trigger();
   pdl_wait();
-  attention_combine_row(part_o, part_ml, out, splits, blockIdx.x, threadIdx.x, blockDim.x);
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (row < rows) attention_combine_row(part_o, part_ml, out, splits, (size_t)row, threadIdx.x & 31);
 }
 
 }  // namespace tllm
@@ -308,7 +310,7 @@ extern "C" int tllm_attention_mma(const void* q, int q_row_stride, const void* k
     TLLM_LAUNCH("attention_mma", (attention_mma_kernel<4, ST>), dim3((unsigned)(gx * nkv), 1, splits), 128, smem, s, p);
   }
   if (splits > 1)
-    TLLM_LAUNCH("attention_combine", attention_combine_kernel, (unsigned)((size_t)n_tokens * nq), HD >= 128 ? 128 : 64, 0, s,
-                p.part_o, p.part_ml, p.out, splits);
+    TLLM_LAUNCH("attention_combine", attention_combine_kernel, (unsigned)(((size_t)n_tokens * nq + 3) / 4), 128, 0, s,
+                p.part_o, p.part_ml, p.out, splits, n_tokens * nq);
   return TLLM_OK;
 }

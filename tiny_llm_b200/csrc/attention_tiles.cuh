@@ -274,26 +274,46 @@ __device__ __forceinline__ void attention_decode_item(const AttnParams& p, int r
   }
 }
 
-// Merges the slices of one (token, head) `th`: out = sum_s 2^(m_s - m) o_s / sum_s 2^(m_s - m) l_s for
-// the elements d_first, d_first + d_step, ...  A slice that saw no key of the row has m_s = -inf
-// and l_s = 0 and drops out.  The partials are read past L1: inside a persistent kernel other SMs
-// wrote them, and the same addresses held another layer's partials a moment ago.
+// Merges the slices of one (token, head) `th` by one warp: out = sum_s 2^(m_s - m) o_s / sum_s 2^(m_s - m) l_s.
+// Lane s reads the maximum and sum of slices s, s + 32, ...; the weights 2^(m_s - m) go round by
+// shuffle while every lane gathers its elements of o, so no load waits for another.  A slice that
+// saw no key of the row has m_s = -inf and l_s = 0 and drops out.  The partials are read past L1:
+// inside a persistent kernel other SMs wrote them, and the same addresses held another layer's
+// partials a moment ago.  All 32 lanes must call this together.
 __device__ __forceinline__ void attention_combine_row(const float* part_o, const float* part_ml, __nv_bfloat16* out,
-                                                      int splits, size_t th, int d_first, int d_step) {
+                                                      int splits, size_t th, int lane) {
+  const size_t base = th * splits;
   float m = -CUDART_INF_F;
-  for (int s = 0; s < splits; ++s) m = fmaxf(m, __ldcg(part_ml + (th * splits + s) * 2));
+  for (int s0 = 0; s0 < splits; s0 += 32)
+    if (s0 + lane < splits) m = fmaxf(m, __ldcg(part_ml + (base + s0 + lane) * 2));
+  m = warp_max(m);
   float l = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float ms = __ldcg(part_ml + (th * splits + s) * 2);
-    if (ms != -CUDART_INF_F) l += exp2f(ms - m) * __ldcg(part_ml + (th * splits + s) * 2 + 1);
-  }
-  for (int d = d_first; d < HD; d += d_step) {
-    float acc = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const float ms = __ldcg(part_ml + (th * splits + s) * 2);
-      if (ms != -CUDART_INF_F) acc += exp2f(ms - m) * __ldcg(part_o + (th * splits + s) * HD + d);
+  float acc[(HD + 31) / 32];
+#pragma unroll
+  for (int i = 0; i < (HD + 31) / 32; ++i) acc[i] = 0.f;
+  for (int s0 = 0; s0 < splits; s0 += 32) {
+    float f = 0.f;
+    if (s0 + lane < splits) {
+      const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml) + base + s0 + lane);
+      f = ml.x == -CUDART_INF_F ? 0.f : exp2f(ml.x - m);
+      l += f * ml.y;
     }
-    out[th * HD + d] = __float2bfloat16_rn(acc / l);
+    const int n = min(32, splits - s0);
+#pragma unroll 4
+    for (int sl = 0; sl < n; ++sl) {
+      const float fs = __shfl_sync(0xffffffffu, f, sl);
+#pragma unroll
+      for (int i = 0; i < (HD + 31) / 32; ++i) {
+        const int d = i * 32 + lane;
+        if (d < HD) acc[i] += fs * __ldcg(part_o + (base + s0 + sl) * HD + d);
+      }
+    }
+  }
+  const float inv = 1.f / warp_sum(l);
+#pragma unroll
+  for (int i = 0; i < (HD + 31) / 32; ++i) {
+    const int d = i * 32 + lane;
+    if (d < HD) out[th * HD + d] = __float2bfloat16_rn(acc[i] * inv);
   }
 }
 

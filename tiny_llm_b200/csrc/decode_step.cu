@@ -608,31 +608,12 @@ __device__ __forceinline__ void attention_phase(const DecodeParams& p, const Dec
   }
 }
 
-// Merges the slices of every (token, head), one warp per row: lane s reads the maximum and sum of slice
-// s (at most 32 slices), the weights 2^(m_s - m) go round by shuffle.
+// Merges the slices of every (token, head), one warp per row.
 __device__ __forceinline__ void combine_phase(const DecodeParams& p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int rows = p.m * p.nq, S = p.splits;
-  for (int row = (int)blockIdx.x * CONSUMER_WARPS + warp; row < rows; row += (int)gridDim.x * CONSUMER_WARPS) {
-    const size_t base = (size_t)row * S;
-    float ms = -CUDART_INF_F, ls = 0.f;
-    if (lane < S) {
-      const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.part_ml) + base + lane);
-      ms = ml.x; ls = ml.y;
-    }
-    const float m = warp_max(ms);
-    const float f = ms == -CUDART_INF_F ? 0.f : exp2f(ms - m);
-    const float inv = 1.f / warp_sum(f * ls);
-    for (int d0 = 0; d0 < HD; d0 += 32) {   // every lane takes every turn: the shuffles need the whole warp
-      const int d = d0 + lane;
-      float acc = 0.f;
-      for (int sl = 0; sl < S; ++sl) {
-        const float fs = __shfl_sync(0xffffffffu, f, sl);
-        if (d < HD) acc += fs * __ldcg(p.part_o + (base + sl) * HD + d);
-      }
-      if (d < HD) p.attn_out[(size_t)row * HD + d] = __float2bfloat16_rn(acc * inv);
-    }
-  }
+  const int rows = p.m * p.nq;
+  for (int row = (int)blockIdx.x * CONSUMER_WARPS + warp; row < rows; row += (int)gridDim.x * CONSUMER_WARPS)
+    attention_combine_row(p.part_o, p.part_ml, p.attn_out, p.splits, (size_t)row, lane);
 }
 
 __device__ void consume(const DecodeParams& p, uint8_t* ring, float* red, uint8_t* uni, uint64_t* full_bar,
