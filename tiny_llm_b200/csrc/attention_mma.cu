@@ -230,8 +230,8 @@ __global__ void __launch_bounds__(128)
 attention_decode_kernel(const AttnParams p) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   pdl_trigger();
-  pdl_wait();
-  attention_decode_item<STAGES>(p, blockIdx.x, blockIdx.y, blockIdx.z, threadIdx.x, smem_raw, [] { __syncthreads(); });
+  attention_decode_item<STAGES>(p, blockIdx.x, blockIdx.y, blockIdx.z, threadIdx.x, smem_raw, [] { __syncthreads(); },
+                                [] { pdl_wait(); });
 }
 
 // Merges the slices of every (token, head), one warp each.

@@ -97,6 +97,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   int* table_s = reinterpret_cast<int*>(smem + OFF_TABLE);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) { tma_prefetch_map(&map_q); tma_prefetch_map(&map_k); tma_prefetch_map(&map_v); }
   // CTAs start in the order of blockIdx.x.  The tiles of the latest tokens see the most keys, so the
   // order is: the last tile of every request and key/value head, then the tiles before them, and so
   // on; the short ones fill the gaps at the end instead of the long ones trailing behind.

@@ -99,9 +99,14 @@ __device__ __forceinline__ void load_kv_rows(__nv_bfloat16* k_dst, __nv_bfloat16
 // through shared memory at the end.  With p.splits == 1 the rows are normalised and written to
 // p.out; else the unnormalised partial (o, max, sum) goes to p.part_o / p.part_ml.  The caller
 // synchronises the 128 threads before the shared memory is used again.
-template <int STAGES, typename Sync>
+//
+// `dep()` is called once, before the first read of what the kernel before this one wrote (the step's
+// queries, and the keys and values of the step's own tokens).  The request's older keys and values
+// and the step's tables are older than that kernel: their tiles are asked for before `dep()`, so that
+// under programmatic dependent launch they travel while the projection before attention still runs.
+template <int STAGES, typename Sync, typename Dep>
 __device__ __forceinline__ void attention_decode_item(const AttnParams& p, int req, int kvh, int split, int tid,
-                                                      uint8_t* smem_raw, Sync sync) {
+                                                      uint8_t* smem_raw, Sync sync, Dep dep) {
   static_assert(BN == 64, "one thread per key row and per value row of a tile");
   static_assert(4 * 16 * (HD + 2) * 4 <= STAGES * BN * LDS * 2, "merge buffers must fit the key stages");
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // 16 rows
@@ -124,6 +129,15 @@ __device__ __forceinline__ void attention_decode_item(const AttnParams& p, int r
   const int t_begin = first_tile + split * per_split;
   const int t_end = min(last_tile + 1, t_begin + per_split);
 
+  // the first STAGES - 1 tiles: those that end before the step's first token are older than the step
+  bool early[STAGES - 1];
+#pragma unroll
+  for (int st = 0; st < STAGES - 1; ++st) {
+    early[st] = t_begin + st < t_end && (t_begin + st + 1) * BN <= start;
+    if (early[st])
+      load_kv_rows(k_s + st * BN * LDS, v_s + st * BN * LDS, table, (t_begin + st) * BN, key_lo, key_hi, kvh, p, tid);
+  }
+  dep();
   for (int idx = tid; idx < 16 * CHUNKS; idx += 128) {
     const int r = idx / CHUNKS, c = idx % CHUNKS;
     const bool ok = r < rows_total;
@@ -131,10 +145,10 @@ __device__ __forceinline__ void attention_decode_item(const AttnParams& p, int r
     if (ok) src = p.q + (size_t)(tok0 + r / group) * p.q_row_stride + (size_t)(kvh * group + r % group) * HD + c * 8;
     cp_async16(q_s + r * LDS + c * 8, src, ok);
   }
-  cp_async_commit();
+  cp_async_commit();   // the queries and the early tiles
 #pragma unroll
   for (int st = 0; st < STAGES - 1; ++st) {
-    if (t_begin + st < t_end)
+    if (!early[st] && t_begin + st < t_end)
       load_kv_rows(k_s + st * BN * LDS, v_s + st * BN * LDS, table, (t_begin + st) * BN, key_lo, key_hi, kvh, p, tid);
     cp_async_commit();
   }

@@ -603,7 +603,7 @@ __device__ __forceinline__ void attention_phase(const DecodeParams& p, const Dec
   auto team_sync = [team] { named_sync(2 + team, 128); };
   for (int it = (int)blockIdx.x * TEAMS + team; it < items; it += (int)gridDim.x * TEAMS) {
     const int split = it % p.splits, kvh = (it / p.splits) % p.nkv, req = it / (p.splits * p.nkv);
-    attention_decode_item<ATT_STAGES>(ap, req, kvh, split, tid, team_smem + (size_t)team * TEAM_BYTES, team_sync);
+    attention_decode_item<ATT_STAGES>(ap, req, kvh, split, tid, team_smem + (size_t)team * TEAM_BYTES, team_sync, [] {});
     team_sync();
   }
 }

@@ -241,6 +241,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) { tma_prefetch_map(&map_a); tma_prefetch_map(&map_b); }   // the descriptors are on their way while the barriers are set up
   const int tile_a = blockIdx.y, tile_b = blockIdx.x;
   const int kb_begin = blockIdx.z * k_blocks_per_split;
   const int kb_end = min(k_blocks, kb_begin + k_blocks_per_split);
@@ -392,6 +393,7 @@ linear_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   float* parked = reinterpret_cast<float*>(smem);   // [BN tokens][128 rows] once the MMAs are done
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) { tma_prefetch_map(&map_a); tma_prefetch_map(&map_b); }   // the descriptors are on their way while the barriers are set up
   const int tile_a = blockIdx.y, tile_b = blockIdx.x;
   const int kb_begin = blockIdx.z * k_blocks_per_split;
   const int kb_end = min(k_blocks, kb_begin + k_blocks_per_split);
@@ -628,6 +630,7 @@ linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) { tma_prefetch_map(&map_a); tma_prefetch_map(&map_b); }   // the descriptors are on their way while the barriers are set up
   const int tiles_m = (rows_a + BM - 1) / BM, tiles_n = (rows_b + BN - 1) / BN;
   const int n_tiles = tiles_m * tiles_n;
   constexpr uint32_t TMEM_COLS = 2 * BN;

@@ -133,6 +133,10 @@ __device__ __forceinline__ uint32_t instr_desc_bf16(int m, int n, bool b_mn_majo
          ((uint32_t)(m >> 4) << 24);
 }
 
+// Asks for a tensor map's descriptor ahead of the first copy that uses it
+__device__ __forceinline__ void tma_prefetch_map(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
