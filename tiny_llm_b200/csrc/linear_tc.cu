@@ -376,6 +376,44 @@ __device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t addr, uint32_t rank)
   return v;
 }
 
+// One work item of the rotate-and-cache epilogue: four neighbouring rotation pairs of one token.  What it
+// needs from global memory (position, slot, cosines, sines) depends on the step's tables only, so the
+// first item of every thread is fetched when the kernel starts and waits in registers.
+struct RopeItem {
+  bool valid;
+  bool rotate;
+  int j, r_lo, d, head, m;
+  int slot;
+  float4 cs, sn;
+};
+template <int BN>
+__device__ __forceinline__ RopeItem rope_item(const ClusterArgs& ca, int idx, int tile_a, int m0, int rows_a, int rows_b) {
+  RopeItem it;
+  const int half = ca.hd / 2, CZ = ca.cz;
+  const int pairs_per = ((BM / 2 + CZ - 1) / CZ + 3) & ~3, p0 = (int)blockIdx.z * pairs_per, quads = pairs_per / 4;
+  it.j = idx / quads;
+  const int q = p0 + (idx % quads) * 4;
+  it.r_lo = (q / half) * ca.hd + q % half;
+  it.m = m0 + it.j;
+  const int n_lo = tile_a * BM + it.r_lo;
+  it.valid = idx < quads * BN && it.m < rows_b && q < BM / 2 && n_lo + half < rows_a;   // heads are whole: the four pairs exist together
+  it.head = n_lo / ca.hd;
+  it.d = n_lo % ca.hd;
+  it.rotate = false;
+  it.slot = -1;
+  it.cs = it.sn = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (it.valid) {
+    it.rotate = it.head < ca.nq + ca.nkv && ca.cos != nullptr;
+    if (it.head >= ca.nq && ca.slot_mapping != nullptr) it.slot = ca.slot_mapping[it.m];
+    if (it.rotate) {
+      const size_t t = (size_t)ca.positions[it.m] * half + it.d;   // d is a multiple of four: 16-byte loads
+      it.cs = *reinterpret_cast<const float4*>(ca.cos + t);
+      it.sn = *reinterpret_cast<const float4*>(ca.sin + t);
+    }
+  }
+  return it;
+}
+
 template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(THREADS, 2)
 linear_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -399,6 +437,8 @@ linear_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   const int kb_end = min(k_blocks, kb_begin + k_blocks_per_split);
   const int n_kb = max(0, kb_end - kb_begin);
   constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+  RopeItem first_item = {};
+  if (EPI == EPI_CL_ROPE_KV) first_item = rope_item<BN>(ca, threadIdx.x, tile_a, tile_b * BN, rows_a, rows_b);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -523,13 +563,11 @@ linear_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   } else if (EPI == EPI_CL_ROPE_KV) {
     // pairs (d, d + hd/2) of whole heads: 64 pairs per tile, dealt to the CZ CTAs, four neighbouring pairs per item
     const int half = ca.hd / 2;
-    const int pairs_per = ((BM / 2 + CZ - 1) / CZ + 3) & ~3, p0 = my_z * pairs_per, quads = pairs_per / 4;
+    const int pairs_per = ((BM / 2 + CZ - 1) / CZ + 3) & ~3, quads = pairs_per / 4;
     for (int idx = threadIdx.x; idx < quads * BN; idx += THREADS) {
-      const int j = idx / quads, q = p0 + (idx % quads) * 4;
-      const int r_lo = (q / half) * ca.hd + q % half, r_hi = r_lo + half;
-      const int m = m0 + j, n_lo = tile_a * BM + r_lo;
-      if (m >= rows_b || q >= BM / 2 || n_lo + half >= rows_a) continue;   // heads are whole: the four pairs exist together
-      const uint32_t at_lo = base + (uint32_t)(j * BM + r_lo) * 4u, at_hi = base + (uint32_t)(j * BM + r_hi) * 4u;
+      const RopeItem it = idx == (int)threadIdx.x ? first_item : rope_item<BN>(ca, idx, tile_a, m0, rows_a, rows_b);
+      if (!it.valid) continue;
+      const uint32_t at_lo = base + (uint32_t)(it.j * BM + it.r_lo) * 4u, at_hi = at_lo + (uint32_t)half * 4u;
       float4 pl[8], ph[8];
 #pragma unroll
       for (int z = 0; z < 8; ++z) {
@@ -543,32 +581,24 @@ linear_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           hi[0] += ph[z].x; hi[1] += ph[z].y; hi[2] += ph[z].z; hi[3] += ph[z].w;
         }
       }
-      const int head = n_lo / ca.hd, d = n_lo % ca.hd;
-      const bool rotate = head < ca.nq + ca.nkv && ca.cos != nullptr;
       __nv_bfloat16* dst;
-      if (head < ca.nq) {
-        dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)m * ldo + (size_t)head * ca.hd;
+      if (it.head < ca.nq) {
+        dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)it.m * ldo + (size_t)it.head * ca.hd;
       } else {
-        if (ca.slot_mapping == nullptr) continue;
-        const int slot = ca.slot_mapping[m];
-        if (slot < 0) continue;
-        const bool is_v = head >= ca.nq + ca.nkv;
-        dst = (is_v ? ca.vcache : ca.kcache) + (long long)(slot / ca.page_size) * ca.page_stride +
-              (long long)(head - ca.nq - (is_v ? ca.nkv : 0)) * ca.head_stride + (long long)(slot % ca.page_size) * ca.hd;
+        if (it.slot < 0) continue;
+        const bool is_v = it.head >= ca.nq + ca.nkv;
+        dst = (is_v ? ca.vcache : ca.kcache) + (long long)(it.slot / ca.page_size) * ca.page_stride +
+              (long long)(it.head - ca.nq - (is_v ? ca.nkv : 0)) * ca.head_stride + (long long)(it.slot % ca.page_size) * ca.hd;
       }
-      const size_t t = rotate ? (size_t)ca.positions[m] * half + d : 0;
+      const float cs[4] = {it.cs.x, it.cs.y, it.cs.z, it.cs.w}, sn[4] = {it.sn.x, it.sn.y, it.sn.z, it.sn.w};
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         // the projection's output is a bfloat16 tensor of the model: rounded before the rotation
         const float x = __bfloat162float(__float2bfloat16_rn(lo[e])), y = __bfloat162float(__float2bfloat16_rn(hi[e]));
-        float o_lo = x, o_hi = y;
-        if (rotate) {
-          const float cs = ca.cos[t + e], sn = ca.sin[t + e];
-          o_lo = cs * x - sn * y;
-          o_hi = sn * x + cs * y;
-        }
-        dst[d + e] = __float2bfloat16_rn(o_lo);
-        dst[d + half + e] = __float2bfloat16_rn(o_hi);
+        const float o_lo = it.rotate ? cs[e] * x - sn[e] * y : x;
+        const float o_hi = it.rotate ? sn[e] * x + cs[e] * y : y;
+        dst[it.d + e] = __float2bfloat16_rn(o_lo);
+        dst[it.d + half + e] = __float2bfloat16_rn(o_hi);
       }
     }
   } else {
