@@ -111,6 +111,22 @@ def weight_bytes(model):
     return total
 
 
+TRACE = os.environ.get("TLLM_TRACE") == "1"   # kernels built with timeline notes (a build for measurements)
+
+
+def timeline_summary(records):
+    """Per kind of launch (library, grid, block): how many, and the mean time in us from the moment the
+    kernel before it had finished to the moment it had finished itself, inside the replayed graph."""
+    kinds = {}
+    for i, r in enumerate(records[:-1]):
+        name = f"{r[6]} grid {r[2]}x{r[3]}x{r[4]} block {r[5]}"
+        k = kinds.setdefault(name, [0, 0.0])
+        k[0] += 1
+        k[1] += (records[i + 1][1] - r[1]) / 1e3
+    out = {n: {"launches": c, "mean_us": round(t / c, 2), "total_us": round(t, 1)} for n, (c, t) in kinds.items()}
+    return dict(sorted(out.items(), key=lambda kv: -kv[1]["total_us"]))
+
+
 def timed_decode(runner, batch, start_len, steps, warmup, sampler_out):
     """Prefills `batch` requests to start_len tokens, then runs warmup + steps decode steps enqueued
     back to back; returns (ms per step over the timed steps, kernels launched in them)."""
@@ -138,9 +154,14 @@ def timed_decode(runner, batch, start_len, steps, warmup, sampler_out):
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0.record()
     for i in range(warmup, warmup + steps):
+        if TRACE and i == warmup + steps - 1:   # the last step alone, between two reads of the timeline notes
+            torch.cuda.synchronize()
+            ops.trace_dump()
         one(i)
     t1.record()
     torch.cuda.synchronize()
+    if TRACE:
+        timed_decode.timeline = ops.trace_dump()
     ms = t0.elapsed_time(t1) / steps
     launched = ops.launches - before
     for rid in rids:
@@ -248,6 +269,8 @@ def main():
             ms, launched = timed_decode(runner, args.batch, start_len, steps, warmup, out)
             rec = {"only": "decode", "batch": args.batch, "layers": args.layers, "ms_per_step": round(ms, 4),
                    "gpu_launches": launched, "fused_decode_step": runner._fused is not None}
+            if TRACE:
+                rec["timeline"] = timeline_summary(timed_decode.timeline)
             if runner._fused is not None and os.environ.get("TLLM_STEP_TIMING"):
                 # device cycles one CTA of the fused decode step spent per kind of phase, per step
                 names = ["norm_load", "qkv", "grid_barriers", "attention", "combine", "plain_load", "o_proj", "gate_up",

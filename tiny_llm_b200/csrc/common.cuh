@@ -83,8 +83,45 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 // still reads.  What a kernel does before pdl_wait() must depend on nothing but constants of the
 // model (weights): that part overlaps the tail of its predecessor.  Without the launch attribute
 // both instructions do nothing, so the same kernels run in plain stream order too.
-__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+//
+// With -DTLLM_TRACE (a build for measurements) the first thread of the first CTA of every launch also
+// notes the global timer at both points: when the CTA started, and when its wait for the kernel
+// before it returned -- which is when that kernel had finished.  The notes of one step, read back
+// with tllm_trace_dump(), are the timeline of the step inside its CUDA graph.
+#ifdef TLLM_TRACE
+struct TraceRec {
+  unsigned long long t_enter, t_ready;
+  unsigned int gx, gy, gz, bx;
+};
+__device__ TraceRec g_trace[8192];
+__device__ unsigned int g_trace_n;
+__shared__ unsigned int s_trace_slot;
+__device__ __forceinline__ unsigned long long trace_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ bool trace_here() { return (blockIdx.x | blockIdx.y | blockIdx.z | threadIdx.x) == 0; }
+#endif
+
+__device__ __forceinline__ void pdl_trigger() {
+#ifdef TLLM_TRACE
+  if (trace_here()) {
+    const unsigned int i = atomicAdd(&g_trace_n, 1u) & 8191u;
+    s_trace_slot = i;
+    g_trace[i].t_enter = trace_now();
+    g_trace[i].t_ready = 0;
+    g_trace[i].gx = gridDim.x; g_trace[i].gy = gridDim.y; g_trace[i].gz = gridDim.z; g_trace[i].bx = blockDim.x;
+  }
+#endif
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+#ifdef TLLM_TRACE
+  if (trace_here()) g_trace[s_trace_slot].t_ready = trace_now();
+#endif
+}
 
 inline int& pdl_enabled() {
   static int on = 1;
@@ -111,6 +148,24 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
 }  // namespace tllm
 
 // Each shared object exports its own tllm_last_error() and tllm_set_pdl().
+#ifdef TLLM_TRACE
+#define TLLM_DEFINE_TRACE                                                                                   \
+  extern "C" int tllm_trace_dump(void* host, int max_records) {                                              \
+    unsigned int n = 0;                                                                                      \
+    cudaDeviceSynchronize();                                                                                 \
+    cudaMemcpyFromSymbol(&n, ::tllm::g_trace_n, sizeof(n));                                                  \
+    if (n > 8192u) n = 8192u;                                                                                \
+    if ((int)n > max_records) n = (unsigned int)max_records;                                                 \
+    cudaMemcpyFromSymbol(host, ::tllm::g_trace, sizeof(::tllm::TraceRec) * n);                               \
+    const unsigned int zero = 0;                                                                             \
+    cudaMemcpyToSymbol(::tllm::g_trace_n, &zero, sizeof(zero));                                              \
+    return (int)n;                                                                                           \
+  }
+#else
+#define TLLM_DEFINE_TRACE
+#endif
+
 #define TLLM_DEFINE_LAST_ERROR                                                  \
   extern "C" const char* tllm_last_error() { return ::tllm::error_buffer(); }  \
-  extern "C" void tllm_set_pdl(int on) { ::tllm::pdl_enabled() = on ? 1 : 0; }
+  extern "C" void tllm_set_pdl(int on) { ::tllm::pdl_enabled() = on ? 1 : 0; } \
+  TLLM_DEFINE_TRACE

@@ -70,6 +70,23 @@ def _i32(t: Optional[torch.Tensor], name: str):
         raise KernelError(f"{name} must be a contiguous int32 tensor")
 
 
+def trace_dump():
+    """The timeline notes of every loaded library since the last call (needs a TLLM_TRACE=1 build):
+    a list of (t_enter ns, t_ready ns, grid x, y, z, block x, library), sorted by t_enter.  t_ready of a
+    launch is when the kernel before it in the stream had finished."""
+    import struct
+    out = []
+    buf = ctypes.create_string_buffer(8192 * 32)
+    for key, lib in build._loaded.items():
+        if not hasattr(lib, "tllm_trace_dump"):
+            continue
+        n = lib.tllm_trace_dump(buf, 8192)
+        for i in range(n):
+            t0, t1, gx, gy, gz, bx = struct.unpack_from("<QQIIII", buf, i * 32)
+            out.append((t0, t1, gx, gy, gz, bx, key))
+    return sorted(out)
+
+
 # ----------------------------------------------------------------------------- elementwise
 
 

@@ -57,12 +57,17 @@ def build_dir() -> str:
         return d
 
 
+def _extra_flags():
+    """Flags from the environment (builds for measurements): TLLM_TRACE=1 adds the timeline notes."""
+    return ["-DTLLM_TRACE=1"] if os.environ.get("TLLM_TRACE") == "1" else []
+
+
 def _hash(source: str, extra_headers, flags) -> str:
     h = hashlib.sha256()
     for f in [source] + list(HEADERS) + list(EXTRA_HEADERS.get(source[:-3], [])) + list(extra_headers):
         with open(os.path.join(CSRC, f), "rb") as fh:
             h.update(f.encode() + b"\0" + fh.read())
-    h.update(" ".join(ARCH_FLAGS + BASE_FLAGS + list(flags)).encode())
+    h.update(" ".join(ARCH_FLAGS + BASE_FLAGS + list(flags) + _extra_flags()).encode())
     return h.hexdigest()[:16]
 
 
@@ -86,7 +91,8 @@ def compile_library(name: str, extra_headers=(), flags=(), verbose: bool = True)
     if os.path.isfile(out):
         return out
     tmp = f"{out}.{os.getpid()}.tmp"
-    cmd = [nvcc_path()] + ARCH_FLAGS + BASE_FLAGS + list(flags) + ["-I", CSRC, "-o", tmp, os.path.join(CSRC, name + ".cu")]
+    cmd = [nvcc_path()] + ARCH_FLAGS + BASE_FLAGS + list(flags) + _extra_flags() + ["-I", CSRC, "-o", tmp,
+                                                                                       os.path.join(CSRC, name + ".cu")]
     if verbose:
         print(f"[tiny_llm_b200] compiling {name}.cu{' ' + ' '.join(flags) if flags else ''} for sm_100a ...",
               file=sys.stderr, flush=True)
