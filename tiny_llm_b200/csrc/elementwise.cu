@@ -63,11 +63,21 @@ __global__ void rms_norm_vec_kernel(const float* __restrict__ x, const float* __
                                     int hidden, float eps) {
   __shared__ float scratch[33];
   pdl_trigger();
-  pdl_wait();
+  // the weight is a constant of the model (and `rows` comes with the step's tables): both are read
+  // before the wait for the kernel that writes x, so that only x itself is waited for afterwards
   const int r = blockIdx.x;
-  if (r >= n_rows) return;
-  const float4* src = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * hidden);
   const int n4 = hidden / 4;
+  const float4* w4 = reinterpret_cast<const float4*>(w);
+  float4 g[VEC];
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    const int idx = threadIdx.x + i * blockDim.x;
+    g[i] = idx < n4 ? __ldg(w4 + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  const int src_row = r < n_rows ? (rows ? rows[r] : r) : 0;
+  pdl_wait();
+  if (r >= n_rows) return;
+  const float4* src = reinterpret_cast<const float4*>(x + (size_t)src_row * hidden);
   float4 v[VEC];
   float ss = 0.f;
 #pragma unroll
@@ -79,14 +89,11 @@ __global__ void rms_norm_vec_kernel(const float* __restrict__ x, const float* __
   ss = block_sum(ss, scratch);
   const float denom = sqrtf(ss / (float)hidden + eps);
   T* dst = out + (size_t)r * hidden;
-  const float4* w4 = reinterpret_cast<const float4*>(w);
 #pragma unroll
   for (int i = 0; i < VEC; ++i) {
     const int idx = threadIdx.x + i * blockDim.x;
-    if (idx < n4) {
-      const float4 g = w4[idx];
-      store4(dst + 4 * idx, (g.x * v[i].x) / denom, (g.y * v[i].y) / denom, (g.z * v[i].z) / denom, (g.w * v[i].w) / denom);
-    }
+    if (idx < n4)
+      store4(dst + 4 * idx, (g[i].x * v[i].x) / denom, (g[i].y * v[i].y) / denom, (g[i].z * v[i].z) / denom, (g[i].w * v[i].w) / denom);
   }
 }
 
