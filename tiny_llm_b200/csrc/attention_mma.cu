@@ -66,6 +66,9 @@ attention_mma_kernel(const AttnParams p) {
   const int per_split = (n_tiles + p.splits - 1) / p.splits;
   const int t_begin = first_tile + split * per_split;
   const int t_end = min(last_tile + 1, t_begin + per_split);   // exclusive
+  int* page_slots = reinterpret_cast<int*>(v_s + STAGES * BN * LDS);
+  const PageLookup pages = stage_pages(table, page_slots, t_begin * BN, t_end * BN, p.page_size, p.max_blocks, threadIdx.x, WARPS * 32);
+  __syncthreads();
 
   // ---- Q tile: row r -> token r / group, head kvh * group + r % group
   for (int idx = threadIdx.x; idx < BM * CHUNKS; idx += WARPS * 32) {
@@ -81,7 +84,7 @@ attention_mma_kernel(const AttnParams p) {
 #pragma unroll
   for (int st = 0; st < STAGES - 1; ++st) {
     if (t_begin + st < t_end)
-      load_kv_rows(k_s + st * BN * LDS, v_s + st * BN * LDS, table, (t_begin + st) * BN, key_lo, key_hi, kvh, p, threadIdx.x);
+      load_kv_rows(k_s + st * BN * LDS, v_s + st * BN * LDS, pages, (t_begin + st) * BN, key_lo, key_hi, kvh, p, threadIdx.x);
     cp_async_commit();
   }
 
@@ -111,7 +114,7 @@ attention_mma_kernel(const AttnParams p) {
       const int nxt = tix + STAGES - 1;
       if (nxt < t_end) {
         const int ns = (nxt - t_begin) % STAGES;
-        load_kv_rows(k_s + ns * BN * LDS, v_s + ns * BN * LDS, table, nxt * BN, key_lo, key_hi, kvh, p, threadIdx.x);
+        load_kv_rows(k_s + ns * BN * LDS, v_s + ns * BN * LDS, pages, nxt * BN, key_lo, key_hi, kvh, p, threadIdx.x);
       }
       cp_async_commit();
     }
@@ -289,7 +292,7 @@ extern "C" int tllm_attention_mma(const void* q, int q_row_stride, const void* k
     constexpr int ST = 3;
     // the merge buffers (4 x 16 x (HD + 2) floats) reuse the tile stages
     static_assert(4 * 16 * (HD + 2) * 4 <= ST * BN * LDS * 2, "merge buffers must fit the key stages");
-    const int smem = (16 + 2 * ST * BN) * LDS * 2;
+    const int smem = (16 + 2 * ST * BN) * LDS * 2 + TABLE_SLOTS * 4;
     static bool configured = false;
     if (!configured) {
       cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -299,7 +302,7 @@ extern "C" int tllm_attention_mma(const void* q, int q_row_stride, const void* k
     TLLM_LAUNCH("attention_decode", attention_decode_kernel<ST>, dim3((unsigned)n_requests, nkv, splits), 128, smem, s, p);
   } else {
     constexpr int ST = 2;
-    const int smem = (64 + 2 * ST * BN) * LDS * 2;
+    const int smem = (64 + 2 * ST * BN) * LDS * 2 + TABLE_SLOTS * 4;
     static bool configured = false;
     if (!configured) {
       cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<4, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);

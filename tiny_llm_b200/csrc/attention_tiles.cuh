@@ -71,14 +71,41 @@ struct AttnParams {
 // up the page of one row; the copies are then issued so that consecutive lanes fetch consecutive
 // 16-byte pieces of a row (whole 128-byte lines per instruction), the row's address coming from
 // its lane by shuffle.
-__device__ __forceinline__ void load_kv_rows(__nv_bfloat16* k_dst, __nv_bfloat16* v_dst, const int* table, int j0,
+constexpr int TABLE_SLOTS = 512;   // block-table entries of a CTA's keys that are kept in shared memory
+
+// Where a request's pages are: the entries for the keys a CTA walks are copied to shared memory once
+// (they come with the step's tables, so before the wait for the kernel in front), because a lookup in
+// global memory in front of every tile's copies is a round trip to L2 that the whole warp waits for.
+struct PageLookup {
+  const int* table;    // the request's row of the block table
+  const int* staged;   // entries [first, first + count) of it, in shared memory
+  int first, count, max_blocks;
+  __device__ __forceinline__ int operator()(int block) const {
+    if (block >= max_blocks) return -1;
+    const int i = block - first;
+    return i >= 0 && i < count ? staged[i] : table[block];
+  }
+};
+// Copies the entries for keys [j_lo, j_hi) into `slots` (TABLE_SLOTS ints); the caller synchronises the threads.
+__device__ __forceinline__ PageLookup stage_pages(const int* table, int* slots, int j_lo, int j_hi, int page_size,
+                                                  int max_blocks, int tid, int threads) {
+  PageLookup pl;
+  pl.table = table; pl.staged = slots; pl.max_blocks = max_blocks;
+  pl.first = max(0, j_lo) / page_size;
+  const int last = min(max_blocks, (max(0, j_hi) + page_size - 1) / page_size);
+  pl.count = max(0, min(TABLE_SLOTS, last - pl.first));
+  for (int i = tid; i < pl.count; i += threads) slots[i] = table[pl.first + i];
+  return pl;
+}
+
+__device__ __forceinline__ void load_kv_rows(__nv_bfloat16* k_dst, __nv_bfloat16* v_dst, const PageLookup& pages, int j0,
                                              int j_begin, int j_end, int kvh, const AttnParams& p, int tid) {
   const int warp = tid >> 5, lane = tid & 31;
   const int row = warp * 32 + lane;            // 0..63 keys, 64..127 values
   const bool is_v = row >= BN;
   const int j = j0 + (row & (BN - 1));
-  bool ok = j >= j_begin && j <= j_end && j / p.page_size < p.max_blocks;
-  const int page = ok ? table[j / p.page_size] : -1;
+  bool ok = j >= j_begin && j <= j_end;
+  const int page = ok ? pages(j / p.page_size) : -1;
   ok = ok && page >= 0;
   const __nv_bfloat16* src = is_v ? p.vcache : p.kcache;
   if (ok) src += (long long)page * p.page_stride + (long long)kvh * p.head_stride + (long long)(j % p.page_size) * HD;
@@ -94,7 +121,7 @@ __device__ __forceinline__ void load_kv_rows(__nv_bfloat16* k_dst, __nv_bfloat16
 
 // Decoded tokens: at most 16 rows (new tokens x query heads of the group) of one request and
 // key/value head over one slice of its keys, by 128 threads (`tid` in [0, 128)) that share
-// `smem_raw` ((16 + 2 STAGES 64) rows of LDS elements) and meet at `sync()`.  The four warps split
+// `smem_raw` ((16 + 2 STAGES 64) rows of LDS elements, then TABLE_SLOTS ints) and meet at `sync()`.  The four warps split
 // every 64-key tile between them, 16 keys each, keep a running softmax of their own and merge them
 // through shared memory at the end.  With p.splits == 1 the rows are normalised and written to
 // p.out; else the unnormalised partial (o, max, sum) goes to p.part_o / p.part_ml.  The caller
@@ -128,6 +155,9 @@ __device__ __forceinline__ void attention_decode_item(const AttnParams& p, int r
   const int per_split = (n_tiles + p.splits - 1) / p.splits;
   const int t_begin = first_tile + split * per_split;
   const int t_end = min(last_tile + 1, t_begin + per_split);
+  int* page_slots = reinterpret_cast<int*>(v_s + STAGES * BN * LDS);
+  const PageLookup pages = stage_pages(table, page_slots, t_begin * BN, t_end * BN, p.page_size, p.max_blocks, tid, 128);
+  sync();
 
   // the first STAGES - 1 tiles: those that end before the step's first token are older than the step
   bool early[STAGES - 1];
@@ -135,7 +165,7 @@ __device__ __forceinline__ void attention_decode_item(const AttnParams& p, int r
   for (int st = 0; st < STAGES - 1; ++st) {
     early[st] = t_begin + st < t_end && (t_begin + st + 1) * BN <= start;
     if (early[st])
-      load_kv_rows(k_s + st * BN * LDS, v_s + st * BN * LDS, table, (t_begin + st) * BN, key_lo, key_hi, kvh, p, tid);
+      load_kv_rows(k_s + st * BN * LDS, v_s + st * BN * LDS, pages, (t_begin + st) * BN, key_lo, key_hi, kvh, p, tid);
   }
   dep();
   for (int idx = tid; idx < 16 * CHUNKS; idx += 128) {
@@ -149,7 +179,7 @@ __device__ __forceinline__ void attention_decode_item(const AttnParams& p, int r
 #pragma unroll
   for (int st = 0; st < STAGES - 1; ++st) {
     if (!early[st] && t_begin + st < t_end)
-      load_kv_rows(k_s + st * BN * LDS, v_s + st * BN * LDS, table, (t_begin + st) * BN, key_lo, key_hi, kvh, p, tid);
+      load_kv_rows(k_s + st * BN * LDS, v_s + st * BN * LDS, pages, (t_begin + st) * BN, key_lo, key_hi, kvh, p, tid);
     cp_async_commit();
   }
 
@@ -175,11 +205,12 @@ __device__ __forceinline__ void attention_decode_item(const AttnParams& p, int r
       const int nxt = tix + STAGES - 1;
       if (nxt < t_end) {
         const int ns = (nxt - t_begin) % STAGES;
-        load_kv_rows(k_s + ns * BN * LDS, v_s + ns * BN * LDS, table, nxt * BN, key_lo, key_hi, kvh, p, tid);
+        load_kv_rows(k_s + ns * BN * LDS, v_s + ns * BN * LDS, pages, nxt * BN, key_lo, key_hi, kvh, p, tid);
       }
       cp_async_commit();
     }
     if (tix == t_begin) {
+      trace_mark(0);   // the queries and the first tile are in shared memory
 #pragma unroll
       for (int k0 = 0; k0 < HD; k0 += 16) ldmatrix_x4(qf[k0 / 16], q_s + (lane & 15) * LDS + k0 + (lane >> 4) * 8);
     }
@@ -240,6 +271,7 @@ __device__ __forceinline__ void attention_decode_item(const AttnParams& p, int r
     }
   }
   cp_async_wait<0>();
+  trace_mark(1);       // the tiles of this slice are done
   l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
   l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
   l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
@@ -286,6 +318,7 @@ __device__ __forceinline__ void attention_decode_item(const AttnParams& p, int r
       }
     }
   }
+  trace_mark(2);       // merged and written
 }
 
 // Merges the slices of one (token, head) `th` by one warp: out = sum_s 2^(m_s - m) o_s / sum_s 2^(m_s - m) l_s.

@@ -92,6 +92,7 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 struct TraceRec {
   unsigned long long t_enter, t_ready;
   unsigned int gx, gy, gz, bx;
+  unsigned long long t_mark[4];   // optional notes of the kernel itself, see trace_mark()
 };
 __device__ TraceRec g_trace[8192];
 __device__ unsigned int g_trace_n;
@@ -104,6 +105,13 @@ __device__ __forceinline__ unsigned long long trace_now() {
 __device__ __forceinline__ bool trace_here() { return (blockIdx.x | blockIdx.y | blockIdx.z | threadIdx.x) == 0; }
 #endif
 
+// A kernel may note up to four more moments of its first CTA (nothing without -DTLLM_TRACE).
+__device__ __forceinline__ void trace_mark(int i) {
+#ifdef TLLM_TRACE
+  if (trace_here()) g_trace[s_trace_slot].t_mark[i] = trace_now();
+#endif
+}
+
 __device__ __forceinline__ void pdl_trigger() {
 #ifdef TLLM_TRACE
   if (trace_here()) {
@@ -111,6 +119,7 @@ __device__ __forceinline__ void pdl_trigger() {
     s_trace_slot = i;
     g_trace[i].t_enter = trace_now();
     g_trace[i].t_ready = 0;
+    g_trace[i].t_mark[0] = g_trace[i].t_mark[1] = g_trace[i].t_mark[2] = g_trace[i].t_mark[3] = 0;
     g_trace[i].gx = gridDim.x; g_trace[i].gy = gridDim.y; g_trace[i].gz = gridDim.z; g_trace[i].bx = blockDim.x;
   }
 #endif

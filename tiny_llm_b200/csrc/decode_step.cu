@@ -65,8 +65,8 @@ constexpr int MAX_STAGES = 16;
 constexpr int MIN_STAGES = 2;
 constexpr int RED_BYTES = 2 * CONSUMER_WARPS * 32 * 16;   // two buffers of one float4 per consumer thread
 constexpr int ATT_STAGES = 3;
-constexpr int TEAM_BYTES = (16 + 2 * ATT_STAGES * BN) * LDS * 2;
-constexpr int TEAMS = 2 * TEAM_BYTES <= 116 * 1024 ? 2 : 1;
+constexpr int TEAM_BYTES = (16 + 2 * ATT_STAGES * BN) * LDS * 2 + TABLE_SLOTS * 4;
+constexpr int TEAMS = 2 * TEAM_BYTES <= 120 * 1024 ? 2 : 1;
 constexpr unsigned long long WAIT_NS = 2000000000ull;
 constexpr int ERR_STEP_PRODUCER = 4, ERR_STEP_CONSUMER = 5, ERR_STEP_GRID = 6;
 

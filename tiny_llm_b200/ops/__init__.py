@@ -72,18 +72,19 @@ def _i32(t: Optional[torch.Tensor], name: str):
 
 def trace_dump():
     """The timeline notes of every loaded library since the last call (needs a TLLM_TRACE=1 build):
-    a list of (t_enter ns, t_ready ns, grid x, y, z, block x, library), sorted by t_enter.  t_ready of a
-    launch is when the kernel before it in the stream had finished."""
+    a list of (t_enter ns, t_ready ns, grid x, y, z, block x, library, marks), sorted by t_enter.  t_ready
+    of a launch is when the kernel before it in the stream had finished; marks are up to four more
+    moments a kernel noted itself (0: none)."""
     import struct
     out = []
-    buf = ctypes.create_string_buffer(8192 * 32)
+    buf = ctypes.create_string_buffer(8192 * 64)
     for key, lib in build._loaded.items():
         if not hasattr(lib, "tllm_trace_dump"):
             continue
         n = lib.tllm_trace_dump(buf, 8192)
         for i in range(n):
-            t0, t1, gx, gy, gz, bx = struct.unpack_from("<QQIIII", buf, i * 32)
-            out.append((t0, t1, gx, gy, gz, bx, key))
+            t0, t1, gx, gy, gz, bx, m0, m1, m2, m3 = struct.unpack_from("<QQIIIIQQQQ", buf, i * 64)
+            out.append((t0, t1, gx, gy, gz, bx, key, (m0, m1, m2, m3)))
     return sorted(out)
 
 
