@@ -122,17 +122,19 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   pdl_trigger();
-  pdl_wait();
-  // the request's block table, so that the producer's page lookups are not a chain of global loads
+  // The step's tables (request lengths, block table) were written before the step's first kernel: they are
+  // read before the wait for the kernel in front.  The block table goes to shared memory, so that the
+  // producer's page lookups are not a chain of global loads.
   for (int b = threadIdx.x; b < min(p.max_blocks, MAX_TABLE); b += THREADS)
     table_s[b] = p.block_table[(size_t)req * p.max_blocks + b];
-  __syncthreads();
-
   const int tok0 = p.cu_q[req];
   const int q_len = p.cu_q[req + 1] - tok0;
+  const int start = p.q_start[req];
+  __syncthreads();
+  pdl_wait();
+
   const int rows_total = q_len * group;
   const int row0 = tile * BM;
-  const int start = p.q_start[req];
   const int tok_lo = row0 / group;
   const int tok_hi = min(q_len - 1, (row0 + BM - 1) / group);
   const int kv_end = start + q_len;                         // keys that exist once this step's are written
