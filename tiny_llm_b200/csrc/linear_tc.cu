@@ -268,7 +268,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     for (int i = 0; i < n_pre; ++i) {
       mbar_expect_tx(&full_bar[i], L::STAGE_BYTES);
       uint8_t* a_dst = smem + i * L::STAGE_BYTES;
-      if (SWAP) tma_load_2d(a_dst, &map_a, (kb_begin + i) * BK, tile_a * BM, &full_bar[i]);
+      if (SWAP) tma_load_2d_hint(a_dst, &map_a, (kb_begin + i) * BK, tile_a * BM, &full_bar[i], l2_evict_first_policy());
       else tma_load_2d(a_dst + L::A_BYTES, &map_b, (kb_begin + i) * BK, tile_b * BN, &full_bar[i]);
     }
   }
@@ -286,7 +286,10 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           if (!mbar_wait(&empty_bar[s], parity, abort_flag)) { *abort_flag = 1; atomicExch(status, ERR_PRODUCER); break; }
           mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
         }
-        if (!pre || !SWAP) tma_load_2d(a_dst, &map_a, (kb_begin + i) * BK, tile_a * BM, &full_bar[s]);
+        if (!pre || !SWAP) {
+          if (SWAP) tma_load_2d_hint(a_dst, &map_a, (kb_begin + i) * BK, tile_a * BM, &full_bar[s], l2_evict_first_policy());   // weights: read once per step
+          else tma_load_2d(a_dst, &map_a, (kb_begin + i) * BK, tile_a * BM, &full_bar[s]);
+        }
         if (!pre || SWAP) tma_load_2d(a_dst + L::A_BYTES, &map_b, (kb_begin + i) * BK, tile_b * BN, &full_bar[s]);
       }
     } else if (warp == 1 && lane == 0) {
@@ -458,13 +461,14 @@ linear_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   if (warp == 0 && lane == 0) {
     for (int i = 0; i < n_pre; ++i) {
       mbar_expect_tx(&full_bar[i], L::STAGE_BYTES);
-      tma_load_2d(smem + i * L::STAGE_BYTES, &map_a, (kb_begin + i) * BK, tile_a * BM, &full_bar[i]);
+      tma_load_2d_hint(smem + i * L::STAGE_BYTES, &map_a, (kb_begin + i) * BK, tile_a * BM, &full_bar[i], l2_evict_first_policy());
     }
   }
   pdl_wait();
 
   if (warp == 0 && lane == 0) {
     // ---------------- TMA producer
+    const uint64_t once = l2_evict_first_policy();   // the weights are read once per step
     for (int i = 0; i < n_kb; ++i) {
       const int s = i % STAGES;
       uint8_t* a_dst = smem + s * L::STAGE_BYTES;
@@ -473,7 +477,7 @@ linear_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         const uint32_t parity = ((i / STAGES) & 1) ^ 1;
         if (!mbar_wait(&empty_bar[s], parity, abort_flag)) { *abort_flag = 1; atomicExch(status, ERR_PRODUCER); break; }
         mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
-        tma_load_2d(a_dst, &map_a, (kb_begin + i) * BK, tile_a * BM, &full_bar[s]);
+        tma_load_2d_hint(a_dst, &map_a, (kb_begin + i) * BK, tile_a * BM, &full_bar[s], once);
       }
       tma_load_2d(a_dst + L::A_BYTES, &map_b, (kb_begin + i) * BK, tile_b * BN, &full_bar[s]);
     }

@@ -133,6 +133,18 @@ __device__ __forceinline__ uint32_t instr_desc_bf16(int m, int n, bool b_mn_majo
          ((uint32_t)(m >> 4) << 24);
 }
 
+// The same copy with an L2 hint for data that is read once (the weights of a decode step, 2 GB that
+// would otherwise push the step's small, hot tensors -- activations, tables, partial results -- out of L2).
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
+}
+__device__ __forceinline__ void tma_load_2d_hint(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "l"(policy) : "memory");
+}
 // Asks for a tensor map's descriptor ahead of the first copy that uses it
 __device__ __forceinline__ void tma_prefetch_map(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
