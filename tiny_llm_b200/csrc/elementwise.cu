@@ -292,8 +292,10 @@ extern "C" int tllm_rms_norm(const float* x, const float* w, void* out, const in
   if (aligned && hidden <= 4 * 4 * 256) {
     // 128 or 256 threads, up to four 16-byte loads each
     const int n4 = hidden / 4;
-    // few rows (decode): more threads per row, fewer loads per thread in a row
-    const int threads = n_rows <= 64 ? (n4 <= 128 ? 128 : (n4 <= 256 ? 256 : 512)) : (n4 <= 128 * 4 ? 128 : 256);
+    // Few rows (decode): more threads per row, fewer loads per thread in a row.  Only for bfloat16 output:
+    // the 32-bit path promises sums whose order does not depend on what else is in the batch.
+    const bool wide = out_dtype == TLLM_BF16 && n_rows <= 64;
+    const int threads = wide ? (n4 <= 128 ? 128 : (n4 <= 256 ? 256 : 512)) : (n4 <= 128 * 4 ? 128 : 256);
     const int vec = (n4 + threads - 1) / threads;
 #define TLLM_NORM_CASE(V)                                                                                                   \
   if (out_dtype == TLLM_F32)                                                                                               \
