@@ -26,6 +26,18 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool pred
   const int bytes = pred ? 16 : 0;   // 0: the destination is zero-filled
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes) : "memory");
 }
+// The same copy with an L2 policy (keys and values are read once per step: they should not push the
+// step's small, hot tensors out of L2).
+__device__ __forceinline__ uint64_t l2_evict_first() {
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
+}
+__device__ __forceinline__ void cp_async16_hint(void* dst, const void* src, bool pred, uint64_t policy) {
+  const int bytes = pred ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2, %3;" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "l"(policy)
+               : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void ldmatrix_x4(uint32_t* r, const void* p) {
@@ -99,7 +111,8 @@ __device__ __forceinline__ PageLookup stage_pages(const int* table, int* slots, 
 }
 
 __device__ __forceinline__ void load_kv_rows(__nv_bfloat16* k_dst, __nv_bfloat16* v_dst, const PageLookup& pages, int j0,
-                                             int j_begin, int j_end, int kvh, const AttnParams& p, int tid) {
+                                             int j_begin, int j_end, int kvh, const AttnParams& p, int tid,
+                                             bool read_once = false) {
   const int warp = tid >> 5, lane = tid & 31;
   const int row = warp * 32 + lane;            // 0..63 keys, 64..127 values
   const bool is_v = row >= BN;
@@ -110,12 +123,15 @@ __device__ __forceinline__ void load_kv_rows(__nv_bfloat16* k_dst, __nv_bfloat16
   const __nv_bfloat16* src = is_v ? p.vcache : p.kcache;
   if (ok) src += (long long)page * p.page_stride + (long long)kvh * p.head_stride + (long long)(j % p.page_size) * HD;
   __nv_bfloat16* dst = (warp < 2 ? k_dst : v_dst) + (warp & 1) * 32 * LDS;   // this warp's 32 rows
+  const uint64_t once = l2_evict_first();
 #pragma unroll
   for (int idx = lane; idx < 32 * CHUNKS; idx += 32) {
     const int r = idx / CHUNKS, c = idx % CHUNKS;
     const unsigned long long a = __shfl_sync(0xffffffffu, (unsigned long long)src, r);
     const int okr = __shfl_sync(0xffffffffu, (int)ok, r);
-    cp_async16(dst + r * LDS + c * 8, reinterpret_cast<const __nv_bfloat16*>(a) + (okr ? c * 8 : 0), okr != 0);
+    // decoded tokens read every key once per step; the tiles of a prompt portion are shared by its CTAs through L2
+    if (read_once) cp_async16_hint(dst + r * LDS + c * 8, reinterpret_cast<const __nv_bfloat16*>(a) + (okr ? c * 8 : 0), okr != 0, once);
+    else cp_async16(dst + r * LDS + c * 8, reinterpret_cast<const __nv_bfloat16*>(a) + (okr ? c * 8 : 0), okr != 0);
   }
 }
 
@@ -165,7 +181,7 @@ __device__ __forceinline__ void attention_decode_item(const AttnParams& p, int r
   for (int st = 0; st < STAGES - 1; ++st) {
     early[st] = t_begin + st < t_end && (t_begin + st + 1) * BN <= start;
     if (early[st])
-      load_kv_rows(k_s + st * BN * LDS, v_s + st * BN * LDS, pages, (t_begin + st) * BN, key_lo, key_hi, kvh, p, tid);
+      load_kv_rows(k_s + st * BN * LDS, v_s + st * BN * LDS, pages, (t_begin + st) * BN, key_lo, key_hi, kvh, p, tid, true);
   }
   dep();
   for (int idx = tid; idx < 16 * CHUNKS; idx += 128) {
@@ -179,7 +195,7 @@ __device__ __forceinline__ void attention_decode_item(const AttnParams& p, int r
 #pragma unroll
   for (int st = 0; st < STAGES - 1; ++st) {
     if (!early[st] && t_begin + st < t_end)
-      load_kv_rows(k_s + st * BN * LDS, v_s + st * BN * LDS, pages, (t_begin + st) * BN, key_lo, key_hi, kvh, p, tid);
+      load_kv_rows(k_s + st * BN * LDS, v_s + st * BN * LDS, pages, (t_begin + st) * BN, key_lo, key_hi, kvh, p, tid, true);
     cp_async_commit();
   }
 
@@ -205,7 +221,7 @@ __device__ __forceinline__ void attention_decode_item(const AttnParams& p, int r
       const int nxt = tix + STAGES - 1;
       if (nxt < t_end) {
         const int ns = (nxt - t_begin) % STAGES;
-        load_kv_rows(k_s + ns * BN * LDS, v_s + ns * BN * LDS, pages, nxt * BN, key_lo, key_hi, kvh, p, tid);
+        load_kv_rows(k_s + ns * BN * LDS, v_s + ns * BN * LDS, pages, nxt * BN, key_lo, key_hi, kvh, p, tid, true);
       }
       cp_async_commit();
     }

@@ -222,15 +222,12 @@ def _swap_splits(n: int, k: int, atomic_ok: bool) -> int:
     return max(1, min(want, k_blocks // 4))
 
 
-_cluster_limit = int(os.environ.get("TLLM_CLUSTER_MAX", "8"))
-
-
 def _cluster_slices(n: int, k: int, limit: int = 8) -> int:
     """Slices of K per weight tile for the cluster kernel: 1, 2, 4 or 8, enough CTAs for every SM, at
     least four 64-wide blocks per slice."""
     s = _swap_splits(n, k, True)
     p = 1
-    while p * 2 <= min(s, limit, _cluster_limit):
+    while p * 2 <= min(s, limit):
         p *= 2
     return p
 
@@ -466,8 +463,6 @@ def decode_step_library(head_dim: int):
     timed_cta = os.environ.get("TLLM_STEP_TIMING")   # a switch for measurements: 1 + the CTA whose phases are timed
     if timed_cta:
         flags += (f"-DTLLM_STEP_TIMING={int(timed_cta)}",)
-    if os.environ.get("TLLM_STEP_KC"):
-        flags += (f"-DTLLM_STEP_KC={int(os.environ['TLLM_STEP_KC'])}",)
     lib = build.load_library("decode_step", flags=flags)
     if lib.tllm_decode_step_layer_bytes() != ctypes.sizeof(DecodeLayer) or \
             lib.tllm_decode_step_params_bytes() != ctypes.sizeof(DecodeParams):
