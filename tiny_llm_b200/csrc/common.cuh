@@ -112,6 +112,13 @@ __device__ __forceinline__ void trace_mark(int i) {
 #endif
 }
 
+// ... and a number of its own in the last of the four slots (which product this launch was).
+__device__ __forceinline__ void trace_tag(unsigned long long v) {
+#ifdef TLLM_TRACE
+  if (trace_here()) g_trace[s_trace_slot].t_mark[3] = v;
+#endif
+}
+
 __device__ __forceinline__ void pdl_trigger() {
 #ifdef TLLM_TRACE
   if (trace_here()) {

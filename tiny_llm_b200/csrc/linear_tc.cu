@@ -273,6 +273,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
   }
   pdl_wait();
+  trace_tag(((unsigned long long)rows_a << 40) | ((unsigned long long)rows_b << 20) | (unsigned long long)k_blocks);   // which product (timeline builds only)
 
   if (n_kb > 0) {
     if (warp == 0 && lane == 0) {
@@ -465,6 +466,7 @@ linear_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     }
   }
   pdl_wait();
+  trace_tag(((unsigned long long)rows_a << 40) | ((unsigned long long)rows_b << 20) | (unsigned long long)k_blocks);   // which product (timeline builds only)
 
   if (warp == 0 && lane == 0) {
     // ---------------- TMA producer
@@ -694,6 +696,7 @@ linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     }
   }
   pdl_wait();
+  trace_tag(((unsigned long long)rows_a << 40) | ((unsigned long long)rows_b << 20) | (unsigned long long)k_blocks);   // which product (timeline builds only)
 
   if (warp == 0 && lane == 0) {
     // ---------------- TMA producer
