@@ -206,12 +206,14 @@ __device__ __forceinline__ void store_tile_normal(uint32_t taddr, int row, int t
           if (full && vec_ok) {
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
-              float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
               if (EPI == EPI_ADD_F32) {
-                const float4 p = *reinterpret_cast<const float4*>(dst + j);
-                o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
+                // the add happens in L2 (a 16-byte reduction, nothing comes back): a load, an add and a store
+                // per chunk would make the epilogue a chain of round trips; this thread is the element's only writer
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + j), "f"(v[j]), "f"(v[j + 1]), "f"(v[j + 2]),
+                             "f"(v[j + 3]) : "memory");
+              } else {
+                *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
               }
-              *reinterpret_cast<float4*>(dst + j) = o;
             }
           } else {
 #pragma unroll
