@@ -131,7 +131,8 @@ def test_linear_with_k_slices_reduced_in_a_cluster(ops, m, n, k, monkeypatch):
 
 
 @pytest.mark.parametrize("m,nq,nkv,hd,k,page", [(7, 6, 3, 32, 1024, 8), (1, 32, 4, 64, 2048, 16), (33, 2, 2, 128, 512, 4),
-                                              (5, 5, 1, 16, 80, 8), (300, 6, 3, 64, 1024, 16), (257, 3, 1, 128, 328, 8)])
+                                              (5, 5, 1, 16, 80, 8), (300, 6, 3, 64, 1024, 16), (257, 3, 1, 128, 328, 8),
+                                              (2048, 32, 4, 64, 136, 16)])   # 160 tiles: the last round runs as strips
 def test_qkv_projection_with_rotation_and_cache_write_in_its_epilogue(ops, m, nq, nkv, hd, k, page):
     torch.manual_seed(13)
     n_pages, max_pos = -(-m // page) + 6, 91

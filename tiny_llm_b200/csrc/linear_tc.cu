@@ -66,6 +66,9 @@ struct ClusterArgs {
   const int* slot_mapping;         // [tokens] or null: the rows hold queries only
   long long page_stride, head_stride;
   int nq, nkv, hd, page_size;
+  // persistent kernel: the tiles of the last, incomplete round are cut into strips of `tail_width` columns so
+  // that they spread over all SMs (0: no cutting); tiles [0, tail_from) are whole
+  int tail_from, tail_width;
 };
 
 // Epilogue of one 128 x BN tile of C in the NORMAL orientation: this thread owns row `row` of the
@@ -75,7 +78,7 @@ struct ClusterArgs {
 // bfloat16 (the projection's output is a bfloat16 tensor of the model), rotated in 32-bit and
 // written: queries to the row of `out`, keys and values to the token's slot of the cache.
 template <int BN>
-__device__ __forceinline__ void store_tile_rope_kv(uint32_t taddr, int m, int tile_b, int rows_a, int rows_b,
+__device__ __forceinline__ void store_tile_rope_kv(uint32_t taddr, int m, int n_first, int width, int rows_a, int rows_b,
                                                    void* __restrict__ out, int ldo, const ClusterArgs& ca) {
   const int hd = ca.hd, half = hd / 2;   // 64 or 128: half = 32 or 64
   const bool row_ok = m < rows_a;
@@ -101,8 +104,8 @@ __device__ __forceinline__ void store_tile_rope_kv(uint32_t taddr, int m, int ti
       }
     }
 #pragma unroll 1
-    for (int h0 = 0; h0 < BN; h0 += hd) {
-      const int n0 = tile_b * BN + h0;          // first column of this head
+    for (int h0 = 0; h0 < width; h0 += hd) {
+      const int n0 = n_first + h0;              // first column of this head
       const int head = n0 / hd;
       float lo[32], hi[32];
       tmem_ld32(taddr + h0 + sub, lo);          // warp-wide: every lane reads, whatever it stores
@@ -654,8 +657,8 @@ struct PersistentSmem {
 template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                            void* __restrict__ out, int rows_a, int rows_b, int k_blocks, int ldo,
-                            const ClusterArgs ca, int* __restrict__ status) {
+                            const __grid_constant__ CUtensorMap map_b_strip, void* __restrict__ out, int rows_a, int rows_b,
+                            int k_blocks, int ldo, const ClusterArgs ca, int* __restrict__ status) {
   static_assert(2 * BN <= 512, "two accumulators must fit tensor memory");
   using L = PersistentSmem<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
@@ -672,6 +675,15 @@ linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
   const int tiles_m = (rows_a + BM - 1) / BM, tiles_n = (rows_b + BN - 1) / BN;
   const int n_tiles = tiles_m * tiles_n;
   constexpr uint32_t TMEM_COLS = 2 * BN;
+  // Work items: the whole tiles [0, tail_from), then the tiles of the last, incomplete round cut into strips
+  // of tail_width columns (160 tiles on 148 SMs: 148 whole tiles, then 12 x 4 strips for 48 of the SMs,
+  // instead of 12 whole tiles for 12 of them).  Item i -> (row tile, first column, width).
+  const int whole = ca.tail_width > 0 ? ca.tail_from : n_tiles;
+  const int strips = ca.tail_width > 0 ? BN / ca.tail_width : 1;
+  const int n_items = whole + (n_tiles - whole) * strips;
+  auto item_tile = [&](int i) { return i < whole ? i : whole + (i - whole) / strips; };
+  auto item_col = [&](int i) { return (item_tile(i) / tiles_m) * BN + (i < whole ? 0 : ((i - whole) % strips) * ca.tail_width); };
+  auto item_width = [&](int i) { return i < whole ? BN : ca.tail_width; };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -689,7 +701,7 @@ linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
   // before this grid waits for its predecessors.
   pdl_trigger();
   const int first_tile = blockIdx.x;
-  const int n_pre = first_tile < n_tiles ? min(k_blocks, STAGES) : 0;
+  const int n_pre = first_tile < whole ? min(k_blocks, STAGES) : 0;   // (a CTA's first item is a whole tile, or it has none worth the trouble)
   if (warp == 0 && lane == 0) {
     const int tn = first_tile / tiles_m;
     for (int i = 0; i < n_pre; ++i) {
@@ -704,26 +716,26 @@ linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     // ---------------- TMA producer
     int it = 0;   // k-blocks issued so far, over all tiles: stage = it % STAGES
     bool ok = true;
-    for (int t = first_tile; t < n_tiles && ok; t += gridDim.x) {
-      const int tm = t % tiles_m, tn = t / tiles_m;
+    for (int t = first_tile; t < n_items && ok; t += gridDim.x) {
+      const int tm = item_tile(t) % tiles_m, col = item_col(t), width = item_width(t);
       for (int kb = 0; kb < k_blocks; ++kb, ++it) {
         const int s = it % STAGES;
         uint8_t* a_dst = smem + s * L::STAGE_BYTES;
         const bool pre = it < n_pre;
         if (!pre) {
           if (!mbar_wait(&empty_bar[s], ((it / STAGES) & 1) ^ 1, abort_flag)) { *abort_flag = 1; atomicExch(status, ERR_PRODUCER); ok = false; break; }
-          mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
-          tma_load_2d(a_dst + L::A_BYTES, &map_b, kb * BK, tn * BN, &full_bar[s]);
+          mbar_expect_tx(&full_bar[s], (uint32_t)(L::A_BYTES + width * BK * 2));
+          tma_load_2d(a_dst + L::A_BYTES, width == BN ? &map_b : &map_b_strip, kb * BK, col, &full_bar[s]);
         }
         tma_load_2d(a_dst, &map_a, kb * BK, tm * BM, &full_bar[s]);
       }
     }
   } else if (warp == 1 && lane == 0) {
     // ---------------- MMA issuer
-    const uint32_t idesc = instr_desc_bf16(BM, BN);
     int it = 0, local = 0;
     bool ok = true;
-    for (int t = first_tile; t < n_tiles && ok; t += gridDim.x, ++local) {
+    for (int t = first_tile; t < n_items && ok; t += gridDim.x, ++local) {
+      const uint32_t idesc = instr_desc_bf16(BM, item_width(t));
       const int buf = local & 1;
       if (!mbar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1, abort_flag)) { *abort_flag = 1; atomicExch(status, ERR_MMA); break; }
       tc_fence_after();
@@ -747,7 +759,7 @@ linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     const int quad = warp & 3;
     const int row = quad * 32 + lane;
     int local = 0;
-    for (int t = first_tile; t < n_tiles; t += gridDim.x, ++local) {
+    for (int t = first_tile; t < n_items; t += gridDim.x, ++local) {
       const int buf = local & 1;
       bool ok = mbar_wait(&acc_full[buf], (local >> 1) & 1, abort_flag);
       if (!ok) { *abort_flag = 1; atomicExch(status, ERR_EPILOGUE); }
@@ -755,8 +767,9 @@ linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       if (!ok) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quad * 32) << 16);
-      if (EPI == EPI_ROPE_KV) store_tile_rope_kv<BN>(taddr, (t % tiles_m) * BM + row, t / tiles_m, rows_a, rows_b, out, ldo, ca);
-      else store_tile_normal<BN, EPI>(taddr, row, t % tiles_m, t / tiles_m, rows_a, rows_b, out, ldo);
+      if (EPI == EPI_ROPE_KV)
+        store_tile_rope_kv<BN>(taddr, (item_tile(t) % tiles_m) * BM + row, item_col(t), item_width(t), rows_a, rows_b, out, ldo, ca);
+      else store_tile_normal<BN, EPI>(taddr, row, t % tiles_m, t / tiles_m, rows_a, rows_b, out, ldo);   // (no strips for these)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buf]);   // four arrivals free the accumulator
@@ -813,7 +826,7 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int r
 
 template <int EPI>
 static int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int m, int n, int k, int ldo,
-                             int* status, cudaStream_t s, const ClusterArgs& ca = ClusterArgs()) {
+                             int* status, cudaStream_t s, const ClusterArgs& ca = ClusterArgs(), const void* w_ptr = nullptr) {
   constexpr int BN = 256, STAGES = 4;
   using L = PersistentSmem<BN, STAGES>;
   auto kern = linear_tc_persistent_kernel<BN, STAGES, EPI>;
@@ -829,7 +842,21 @@ static int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, void*
   }
   const int tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
   const int grid = tiles < sm_count ? tiles : sm_count;
-  TLLM_LAUNCH("linear_tc_persistent", kern, grid, THREADS, L::TOTAL, s, ma, mb, out, m, n, (k + BK - 1) / BK, ldo, ca, status);
+  ClusterArgs args = ca;
+  args.tail_from = tiles;
+  args.tail_width = 0;
+  const CUtensorMap* strip_map = &mb;
+  CUtensorMap ms;
+  if (EPI == EPI_ROPE_KV && tiles > sm_count && tiles % sm_count != 0) {
+    // the last round is incomplete: cut its tiles into strips of whole heads if those then fit one round
+    const int width = ca.hd <= 64 ? 64 : ca.hd, left = tiles % sm_count;
+    if (BN % width == 0 && left * (BN / width) <= sm_count && make_map(&ms, w_ptr, n, k, k, width)) {
+      args.tail_from = tiles - left;
+      args.tail_width = width;
+      strip_map = &ms;
+    }
+  }
+  TLLM_LAUNCH("linear_tc_persistent", kern, grid, THREADS, L::TOTAL, s, ma, mb, *strip_map, out, m, n, (k + BK - 1) / BK, ldo, args, status);
   return TLLM_OK;
 }
 
@@ -969,7 +996,7 @@ extern "C" int tllm_linear_tc_cluster(const void* a, const void* w, void* out, i
     TLLM_REQUIRE(hd == 64 || hd == 128, "linear_tc_cluster: the Q/K/V epilogue for more than 128 tokens takes head size 64 or 128 (got %d)", hd);
     if (!make_map(&ma, a, m, k, lda, BM) || !make_map(&mb, w, n, k, k, 256))
       TLLM_FAIL(TLLM_ERR_CUDA, "linear_tc_cluster: cuTensorMapEncodeTiled failed");
-    return launch_persistent<EPI_ROPE_KV>(ma, mb, out, m, n, k, ldo, status, s, ca);
+    return launch_persistent<EPI_ROPE_KV>(ma, mb, out, m, n, k, ldo, status, s, ca, w);
   }
   const int bn = m <= 16 ? 16 : (m <= 32 ? 32 : (m <= 64 ? 64 : 128));
   if (!make_map(&ma, w, n, k, k, BM) || !make_map(&mb, a, m, k, lda, bn))
