@@ -230,6 +230,7 @@ def reference_arm():
 
 
 def main():
+    global PAGE
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
@@ -241,7 +242,9 @@ def main():
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="measure one part only (for profiler captures of a small case)")
     ap.add_argument("--batch", type=int, default=BATCH, help="requests of the decode step (default 8)")
+    ap.add_argument("--page-size", type=int, default=PAGE, help="tokens per page of the cache")
     args = ap.parse_args()
+    PAGE = args.page_size
     if args.impl == "reference":
         return reference_arm()
     if args.gpus != 1:

@@ -4,10 +4,10 @@
 // A CTA serves 128 rows of one (request, key/value head); a row is a (new token, query head of the
 // group) pair, so the heads of a group share every key/value tile.  Keys are walked in tiles of 64:
 //
-//   warp 0 (one thread): TMA.  The query tile comes as one 3-D box (head size x heads of the group x
+//   warp 0: TMA.  The query tile comes as one 3-D box (head size x heads of the group x
 //     tokens) of the step's Q/K/V rows; a key tile and a value tile come page by page (one 2-D box of
 //     page_size rows each, looked up in the request's block table, which sits in shared memory) into a
-//     ring of four stages.
+//     ring of four stages; every copy of a tile is issued by a lane of its own.
 //   warp 1 (one thread): tcgen05.mma.  S = Q K^T (M 128, N 64, K = head size; both operands
 //     K-major in 128-byte-swizzled shared memory) into one of two S buffers in tensor memory, one
 //     tile ahead of the softmax; then O += P V (M 128, N = head
@@ -57,6 +57,7 @@ constexpr int MAX_TABLE = 1024;                    // block-table entries kept i
 constexpr int OFF_TABLE = OFF_BAR + 160;
 constexpr int SMEM_TOTAL = OFF_TABLE + MAX_TABLE * 4 + 1024;   // + alignment slack
 constexpr uint32_t TMEM_COLS = 256;                // S of even tiles: columns [0, 64); of odd tiles: [64, 128); O: [128, 128 + HD)
+constexpr float RESCALE_STEP = 8.f;
 constexpr int ERR_ATT_PRODUCER = 7, ERR_ATT_MMA = 8, ERR_ATT_SOFTMAX = 9;
 
 struct TcAttnParams {
@@ -78,6 +79,20 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
 }
+
+// Optional phase timing of the softmax (-DTLLM_ATT_TIMING=1, a build for measurements): lane 0 of the first
+// softmax warp of CTA 0 adds up clock64() differences per phase of its loop over the key tiles.
+#ifdef TLLM_ATT_TIMING
+__device__ unsigned long long g_att_cycles[16];   // [8..15]: the MMA thread of the same CTA
+#define ATT_T(k)                                                  \
+  if (timed) {                                                    \
+    const long long t_now_ = clock64();                           \
+    att_acc[k] += (unsigned long long)(t_now_ - att_prev);        \
+    att_prev = t_now_;                                            \
+  }
+#else
+#define ATT_T(k)
+#endif
 
 __global__ void __launch_bounds__(THREADS, 2)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -140,40 +155,56 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   const int kv_end = start + q_len;                         // keys that exist once this step's are written
   const int n_tiles = row0 < rows_total ? (start + tok_hi) / BNK + 1 : 0;
 
-  if (warp == 0 && lane == 0) {
-    // ---------------- TMA producer
+  if (warp == 0) {
+    // ---------------- TMA producer.  A tile of 64 keys is up to eight pages, each a copy for K and one for V:
+    // lane 2 g fetches the keys of the tile's page g, lane 2 g + 1 its values, so that the copies of a tile
+    // are issued side by side (one thread issuing them all was the slowest part of the whole kernel).
     const int* table = p.block_table + (size_t)req * p.max_blocks;
     const int pages_per_tile = BNK / p.page_size;
     const uint32_t page_bytes = (uint32_t)p.page_size * HD * 2u;
-    if (n_tiles > 0) {
+    const int g = lane >> 1;
+    const bool is_v = lane & 1;
+    if (lane == 0 && n_tiles > 0) {
       mbar_expect_tx(q_full, Q_BYTES);
       tma_load_3d(smem, &map_q, 0, kvh * group, tok0 + tok_lo, q_full);
     }
+#ifdef TLLM_ATT_TIMING
+    const bool timed = blockIdx.x == 0 && lane == 0;
+    unsigned long long att_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    long long att_prev = clock64();
+#endif
     for (int i = 0; i < n_tiles; ++i) {
       const int s = i % KV_STAGES;
+      ATT_T(5)   // producer: issuing
       if (i >= KV_STAGES) {
-        const uint32_t parity = ((i / KV_STAGES) & 1) ^ 1;
-        if (!mbar_wait(&kv_empty[s], parity, abort_flag)) { *abort_flag = 1; atomicExch(p.status, ERR_ATT_PRODUCER); break; }
+        bool ok = true;
+        if (lane == 0) ok = mbar_wait(&kv_empty[s], ((i / KV_STAGES) & 1) ^ 1, abort_flag);
+        if (!__shfl_sync(0xffffffffu, (int)ok, 0)) {
+          if (lane == 0) { *abort_flag = 1; atomicExch(p.status, ERR_ATT_PRODUCER); }
+          break;
+        }
       }
-      // pages of keys [i * 64, i * 64 + 64) that hold at least one existing key
-      int pages[BNK / 8];
-      int n_valid = 0;
-      for (int g = 0; g < pages_per_tile; ++g) {
-        const int blk = i * pages_per_tile + g;
-        int page = -1;
-        if (blk < p.max_blocks && blk * p.page_size < kv_end) page = blk < MAX_TABLE ? table_s[blk] : table[blk];
-        pages[g] = page;
-        n_valid += page >= 0 ? 1 : 0;
+      ATT_T(4)   // producer: waited for a free stage
+      // this lane's page of keys [i * 64, i * 64 + 64), if it holds at least one existing key
+      int page = -1;
+      const int blk = i * pages_per_tile + g;
+      if (g < pages_per_tile && blk < p.max_blocks && blk * p.page_size < kv_end) page = blk < MAX_TABLE ? table_s[blk] : table[blk];
+      const int n_valid = __popc(__ballot_sync(0xffffffffu, page >= 0 && !is_v));
+      if (lane == 0) {
+        mbar_expect_tx(&k_full[s], (uint32_t)n_valid * page_bytes);
+        mbar_expect_tx(&v_full[s], (uint32_t)n_valid * page_bytes);
       }
-      mbar_expect_tx(&k_full[s], (uint32_t)n_valid * page_bytes);
-      mbar_expect_tx(&v_full[s], (uint32_t)n_valid * page_bytes);
-      for (int g = 0; g < pages_per_tile; ++g) {
-        if (pages[g] < 0) continue;
-        const int row = (pages[g] * p.nkv + kvh) * p.page_size;
-        tma_load_2d(smem + OFF_K + s * K_BYTES + g * page_bytes, &map_k, 0, row, &k_full[s]);
-        tma_load_2d(smem + OFF_V + s * V_BYTES + g * page_bytes, &map_v, 0, row, &v_full[s]);
+      __syncwarp();
+      if (page >= 0) {
+        const int row = (page * p.nkv + kvh) * p.page_size;
+        if (is_v) tma_load_2d(smem + OFF_V + s * V_BYTES + g * page_bytes, &map_v, 0, row, &v_full[s]);
+        else tma_load_2d(smem + OFF_K + s * K_BYTES + g * page_bytes, &map_k, 0, row, &k_full[s]);
       }
     }
+#ifdef TLLM_ATT_TIMING
+    if (timed)
+      for (int k = 4; k < 6; ++k) atomicAdd(&g_att_cycles[8 + k], att_acc[k]);
+#endif
   } else if (warp == 1 && lane == 0) {
     // ---------------- MMA issuer
     const uint32_t idesc_qk = instr_desc_bf16(BM, BNK);
@@ -181,11 +212,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const uint32_t q_addr = smem_u32(smem), p_addr = smem_u32(smem + OFF_P);
     const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * BNK;
     bool ok = n_tiles == 0 || mbar_wait(q_full, 0, abort_flag);
+#ifdef TLLM_ATT_TIMING
+    const bool timed = blockIdx.x == 0;
+    unsigned long long att_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    long long att_prev = clock64();
+#endif
     // S = Q K^T of tile t into the S buffer of its parity; it runs one tile ahead of O += P V
     auto issue_qk = [&](int t) -> bool {
       const int s = t % KV_STAGES;
+      ATT_T(3)
       if (!mbar_wait(&k_full[s], (t / KV_STAGES) & 1, abort_flag)) return false;
       tc_fence_after();
+      ATT_T(0)   // waited for K
       const uint32_t k_addr = smem_u32(smem + OFF_K + s * K_BYTES);
 #pragma unroll
       for (int k = 0; k < HD / UMMA_K; ++k)
@@ -199,9 +237,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const int s = i % KV_STAGES;
       // the other S buffer is free: the softmax of tile i - 1 has read it (its P was waited for below)
       if (i + 1 < n_tiles && !issue_qk(i + 1)) { ok = false; break; }
+      ATT_T(3)   // issuing
       if (!mbar_wait(p_full, i & 1, abort_flag)) { ok = false; break; }
+      ATT_T(1)   // waited for P
       if (!mbar_wait(&v_full[s], (i / KV_STAGES) & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
+      ATT_T(2)   // waited for V
       const uint32_t v_addr = smem_u32(smem + OFF_V + s * V_BYTES);
 #pragma unroll
       for (int kk = 0; kk < BNK / UMMA_K; ++kk)   // 16 keys per step: 32 bytes along a row of P, two 8-row groups of V
@@ -210,6 +251,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       umma_commit(&kv_empty[s]);
       umma_commit(pv_done);
     }
+#ifdef TLLM_ATT_TIMING
+    if (timed)
+      for (int k = 0; k < 8; ++k) atomicAdd(&g_att_cycles[8 + k], att_acc[k]);
+#endif
     if (!ok && !*abort_flag) { *abort_flag = 1; atomicExch(p.status, ERR_ATT_MMA); }
   } else if (warp >= 2) {
     // ---------------- softmax: this thread owns row `row` of the tile (tensor-memory lane)
@@ -224,12 +269,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const float c = p.scale_log2;
     float m_run = -CUDART_INF_F, l_run = 0.f;
     bool ok = true;
+#ifdef TLLM_ATT_TIMING
+    const bool timed = blockIdx.x == 0 && warp == 2 && lane == 0;
+    unsigned long long att_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    long long att_prev = clock64();
+#endif
     for (int i = 0; i < n_tiles; ++i) {
       const int s = i % KV_STAGES;
       ok = mbar_wait(&s_full[i & 1], (i >> 1) & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
+      ATT_T(0)   // waited for S
       const uint32_t t_s = t_s0 + (i & 1) * BNK;
       float sc[BNK];
       {
@@ -240,6 +291,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
         for (int j = 0; j < BNK; ++j) sc[j] = __uint_as_float(raw[j]);
       }
+      ATT_T(1)   // S in registers
       const int j0 = i * BNK;
       if (!live || j0 + BNK - 1 > pos) {   // the tile touches this row's causal edge (or the row does not exist)
 #pragma unroll
@@ -254,7 +306,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         mx4[2] = fmaxf(mx4[2], sc[j + 2]); mx4[3] = fmaxf(mx4[3], sc[j + 3]);
       }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      const float mn = fmaxf(m_run, mx * c);
+      // The running maximum only has to bound the exponents: it follows the true one when that has moved by
+      // more than RESCALE_STEP (in log2 units), so P stays below 2^RESCALE_STEP and O is rescaled rarely.
+      // The result is the same quotient sum(p v) / sum(p): p carries the same factor above and below.
+      const float mn = mx * c > m_run + RESCALE_STEP ? mx * c : m_run;
       const float ms = mn == -CUDART_INF_F ? 0.f : mn;
       const float corr = ex2(m_run - ms);   // 0 while nothing was seen
       m_run = mn;
@@ -268,12 +323,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         }
       }
       l_run = l_run * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+      ATT_T(2)   // maximum, exponentials, sum
       if (i > 0) {   // the product before this one has read P and finished O
         ok = mbar_wait(pv_done, (i - 1) & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
       }
+      ATT_T(3)   // waited for the product before
       // P as bfloat16, 16-byte chunk j of the row stored at chunk position j ^ (row % 8): the 128-byte swizzle
 #pragma unroll
       for (int ch = 0; ch < BNK / 8; ++ch) {
@@ -284,7 +341,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         v.w = pack_bf16(sc[ch * 8 + 6], sc[ch * 8 + 7]);
         *reinterpret_cast<uint4*>(p_row + ((ch ^ (row & 7)) << 4)) = v;
       }
+      ATT_T(4)   // P stored
       if (i > 0 && !__all_sync(0xffffffffu, corr == 1.f)) {   // the maximum of some row of this warp moved
+#ifdef TLLM_ATT_TIMING
+        if (timed) att_acc[7] += 1;
+#endif
 #pragma unroll
         for (int h = 0; h < HD; h += 32) {
           float o[32];
@@ -294,6 +355,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           tmem_st32(t_o + h, o);
         }
       }
+      ATT_T(5)   // O rescaled
       if (j0 + BNK > kv_end) {   // value rows past the last key hold whatever the page held: zero them
         ok = mbar_wait(&v_full[s], (i / KV_STAGES) & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
@@ -307,7 +369,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P (and V) were written by ordinary stores
       tc_fence_before();
       mbar_arrive(p_full);
+      ATT_T(6)   // fences, arrival
     }
+#ifdef TLLM_ATT_TIMING
+    if (timed)
+      for (int k = 0; k < 8; ++k) atomicAdd(&g_att_cycles[k], att_acc[k]);
+#endif
     if (ok && n_tiles > 0) {
       ok = mbar_wait(pv_done, (n_tiles - 1) & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
@@ -396,6 +463,17 @@ static bool make_map_q(CUtensorMap* map, const void* ptr, int tokens, int nq, in
 using namespace tllm;
 
 extern "C" int tllm_attention_tc_head_dim() { return HD; }
+
+#ifdef TLLM_ATT_TIMING
+// Cycles per phase of the timed softmax lane since the last call: waited for S, S to registers, maximum +
+// exponentials + sum, waited for the product before, P stored, O rescaled, fences + arrival; [7] counts the rescales.
+extern "C" int tllm_attention_tc_timing(unsigned long long* host) {
+  cudaDeviceSynchronize();
+  if (cudaMemcpyFromSymbol(host, ::tllm::g_att_cycles, 16 * sizeof(unsigned long long)) != cudaSuccess) return 1;
+  const unsigned long long zero[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+  return cudaMemcpyToSymbol(::tllm::g_att_cycles, zero, sizeof(zero)) != cudaSuccess;
+}
+#endif
 
 // 1 if the kernel takes these sizes (the caller then need not try and fail).
 extern "C" int tllm_attention_tc_fits(int nq, int nkv, int hd, int page_size, int window) {

@@ -57,9 +57,12 @@ def build_dir() -> str:
         return d
 
 
-def _extra_flags():
-    """Flags from the environment (builds for measurements): TLLM_TRACE=1 adds the timeline notes."""
-    return ["-DTLLM_TRACE=1"] if os.environ.get("TLLM_TRACE") == "1" else []
+def _extra_flags(source: str):
+    """Flags from the environment (builds for measurements): TLLM_TRACE=1 adds the timeline notes to every
+    source; TLLM_NVCC_FLAGS_<SOURCE> gives one source further flags (for instance
+    TLLM_NVCC_FLAGS_ATTENTION_TC=-DTLLM_ATT_TIMING=1 for attention_tc.cu)."""
+    flags = ["-DTLLM_TRACE=1"] if os.environ.get("TLLM_TRACE") == "1" else []
+    return flags + os.environ.get("TLLM_NVCC_FLAGS_" + source[:-3].upper(), "").split()
 
 
 def _hash(source: str, extra_headers, flags) -> str:
@@ -67,7 +70,7 @@ def _hash(source: str, extra_headers, flags) -> str:
     for f in [source] + list(HEADERS) + list(EXTRA_HEADERS.get(source[:-3], [])) + list(extra_headers):
         with open(os.path.join(CSRC, f), "rb") as fh:
             h.update(f.encode() + b"\0" + fh.read())
-    h.update(" ".join(ARCH_FLAGS + BASE_FLAGS + list(flags) + _extra_flags()).encode())
+    h.update(" ".join(ARCH_FLAGS + BASE_FLAGS + list(flags) + _extra_flags(source)).encode())
     return h.hexdigest()[:16]
 
 
@@ -91,7 +94,7 @@ def compile_library(name: str, extra_headers=(), flags=(), verbose: bool = True)
     if os.path.isfile(out):
         return out
     tmp = f"{out}.{os.getpid()}.tmp"
-    cmd = [nvcc_path()] + ARCH_FLAGS + BASE_FLAGS + list(flags) + _extra_flags() + ["-I", CSRC, "-o", tmp,
+    cmd = [nvcc_path()] + ARCH_FLAGS + BASE_FLAGS + list(flags) + _extra_flags(name + ".cu") + ["-I", CSRC, "-o", tmp,
                                                                                        os.path.join(CSRC, name + ".cu")]
     if verbose:
         print(f"[tiny_llm_b200] compiling {name}.cu{' ' + ' '.join(flags) if flags else ''} for sm_100a ...",
