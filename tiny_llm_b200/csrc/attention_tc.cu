@@ -8,16 +8,16 @@
 //     tokens) of the step's Q/K/V rows; a key tile and a value tile come page by page (one 2-D box of
 //     page_size rows each, looked up in the request's block table, which sits in shared memory) into a
 //     ring of four stages; every copy of a tile is issued by a lane of its own.
-//   warp 1 (one thread): tcgen05.mma.  S = Q K^T (M 128, N 64, K = head size; both operands
-//     K-major in 128-byte-swizzled shared memory) into one of two S buffers in tensor memory, one
-//     tile ahead of the softmax; then O += P V (M 128, N = head
-//     size, K 64) with P from shared memory and V taken as it lies in the cache (rows = keys: the
-//     MN-major form of the B operand).  tcgen05.commit hands each result over on an mbarrier.
+//   warps 1 and 6 (one thread each): tcgen05.mma.  Warp 1: S = Q K^T (M 128, N 64, K = head size; both
+//     operands K-major in 128-byte-swizzled shared memory) into one of two S buffers in tensor memory, up
+//     to two tiles ahead of the softmax; warp 6: O += P V (M 128, N = head
+//     size, K 64) with P from tensor memory (the A operand) and V taken as it lies in the cache (rows =
+//     keys: the MN-major form of the B operand).  tcgen05.commit hands each result over on an mbarrier.
 //   warps 2-5: softmax.  A thread owns one row: it reads its 64 scores from tensor memory, applies
 //     the causal rule (key j is visible to the token at position p iff j <= p), keeps the running
-//     maximum and sum in 32-bit with the scale folded into exp2, writes P as bfloat16 into shared
-//     memory in the swizzled layout the MMA expects, and rescales its row of O in tensor memory when
-//     the maximum moved.  Rows of a value tile beyond the request's last key are zeroed first (a
+//     maximum and sum in 32-bit with the scale folded into exp2, writes P as bfloat16 pairs into one
+//     of two P buffers in tensor memory, and rescales its row of O in tensor memory when the maximum
+//     moved far.  Rows of a value tile beyond the request's last key are zeroed first (a
 //     page may hold anything there, and 0 x NaN would spoil the product).
 //
 // Two such CTAs share an SM, so one CTA's softmax overlaps the other's MMAs.  Every wait is
@@ -48,15 +48,17 @@ static_assert(HD == 64, "a row of keys must be one 128-byte swizzle row");
 constexpr int BM = 128;          // rows per CTA = MMA M
 constexpr int BNK = 64;          // keys per tile
 constexpr int KV_STAGES = 4;
-constexpr int THREADS = 192;     // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-5: softmax
+constexpr int THREADS = 224;     // warp 0: TMA, warp 1: S = Q K^T + tensor memory, warps 2-5: softmax, warp 6: O += P V
 constexpr int UMMA_K = 16;
-constexpr int Q_BYTES = BM * HD * 2, K_BYTES = BNK * HD * 2, V_BYTES = BNK * HD * 2, P_BYTES = BM * BNK * 2;
-constexpr int OFF_K = Q_BYTES, OFF_V = OFF_K + KV_STAGES * K_BYTES, OFF_P = OFF_V + KV_STAGES * V_BYTES;
-constexpr int OFF_BAR = OFF_P + P_BYTES;
+constexpr int Q_BYTES = BM * HD * 2, K_BYTES = BNK * HD * 2, V_BYTES = BNK * HD * 2;
+constexpr int OFF_K = Q_BYTES, OFF_V = OFF_K + KV_STAGES * K_BYTES;
+constexpr int OFF_BAR = OFF_V + KV_STAGES * V_BYTES;
 constexpr int MAX_TABLE = 1024;                    // block-table entries kept in shared memory (longer tables are read from global)
 constexpr int OFF_TABLE = OFF_BAR + 160;
 constexpr int SMEM_TOTAL = OFF_TABLE + MAX_TABLE * 4 + 1024;   // + alignment slack
-constexpr uint32_t TMEM_COLS = 256;                // S of even tiles: columns [0, 64); of odd tiles: [64, 128); O: [128, 128 + HD)
+constexpr uint32_t TMEM_COLS = 256;                // S of even tiles: columns [0, 64); of odd tiles: [64, 128); O: [128, 192);
+constexpr uint32_t TMEM_O = 2 * BNK, TMEM_P = TMEM_O + HD;   // P (bfloat16 pairs) of even tiles: [192, 224); of odd tiles: [224, 256)
+static_assert(TMEM_P + BNK <= TMEM_COLS, "S, O and P share 256 columns of tensor memory");
 constexpr float RESCALE_STEP = 8.f;
 constexpr int ERR_ATT_PRODUCER = 7, ERR_ATT_MMA = 8, ERR_ATT_SOFTMAX = 9;
 
@@ -105,9 +107,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   uint64_t* v_full = k_full + KV_STAGES;         // [KV_STAGES]
   uint64_t* kv_empty = v_full + KV_STAGES;       // [KV_STAGES]
   uint64_t* s_full = kv_empty + KV_STAGES;       // [2]: S of an even / odd tile is in tensor memory
-  uint64_t* p_full = s_full + 2;                 // P of this tile is in shared memory, O rescaled (128 arrivals)
-  uint64_t* pv_done = p_full + 1;                // O holds this tile too; P and the stage are free
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
+  uint64_t* p_full = s_full + 2;                 // [2]: P of an even / odd tile is in tensor memory (its S has been read), O rescaled (one arrival per softmax warp)
+  uint64_t* o_done = p_full + 2;                 // [2]: O holds an even / odd tile too, and its P buffer is free
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   int* table_s = reinterpret_cast<int*>(smem + OFF_TABLE);
 
@@ -126,8 +128,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&kv_empty[s], 1); }
     mbar_init(&s_full[0], 1);
     mbar_init(&s_full[1], 1);
-    mbar_init(p_full, 128);
-    mbar_init(pv_done, 1);
+    mbar_init(&p_full[0], 4);
+    mbar_init(&p_full[1], 4);
+    mbar_init(&o_done[0], 1);
+    mbar_init(&o_done[1], 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -205,66 +209,95 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     if (timed)
       for (int k = 4; k < 6; ++k) atomicAdd(&g_att_cycles[8 + k], att_acc[k]);
 #endif
-  } else if (warp == 1 && lane == 0) {
-    // ---------------- MMA issuer
+  } else if (warp == 1) {
+    // ---------------- S = Q K^T of tile t into the S buffer of its parity, as soon as its keys are there and
+    // the softmax of tile t - 2 has read that buffer: up to two tiles ahead of the softmax.  The whole warp
+    // walks the loop and waits; one elected lane issues (operands computed by the converged warp are warp-wide
+    // values: a loop walked by a single lane took nearly twice as long per tile).
     const uint32_t idesc_qk = instr_desc_bf16(BM, BNK);
-    const uint32_t idesc_pv = instr_desc_bf16(BM, HD, true);   // V as it lies: rows = keys (MN-major B)
-    const uint32_t q_addr = smem_u32(smem), p_addr = smem_u32(smem + OFF_P);
-    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * BNK;
+    const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
+    const uint32_t q_lo = smem_desc_sw128_lo(smem_u32(smem)), k_lo = smem_desc_sw128_lo(smem_u32(smem + OFF_K));
     bool ok = n_tiles == 0 || mbar_wait(q_full, 0, abort_flag);
+    ok = __all_sync(0xffffffffu, ok);
 #ifdef TLLM_ATT_TIMING
-    const bool timed = blockIdx.x == 0;
+    const bool timed = blockIdx.x == 0 && lane == 0;
     unsigned long long att_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     long long att_prev = clock64();
 #endif
-    // S = Q K^T of tile t into the S buffer of its parity; it runs one tile ahead of O += P V
-    auto issue_qk = [&](int t) -> bool {
+    for (int t = 0; t < n_tiles && ok; ++t) {
       const int s = t % KV_STAGES;
-      ATT_T(3)
-      if (!mbar_wait(&k_full[s], (t / KV_STAGES) & 1, abort_flag)) return false;
+      ATT_T(3)   // issuing
+      if (t >= 2)   // tile t - 2: its S has been read, and its product has read the P buffer that the softmax of tile t will write
+        ok = mbar_wait(&p_full[t & 1], ((t >> 1) - 1) & 1, abort_flag) && mbar_wait(&o_done[t & 1], ((t >> 1) - 1) & 1, abort_flag);
+      ATT_T(1)   // waited for the S buffer
+      ok = ok && mbar_wait(&k_full[s], (t / KV_STAGES) & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
       tc_fence_after();
       ATT_T(0)   // waited for K
-      const uint32_t k_addr = smem_u32(smem + OFF_K + s * K_BYTES);
+      const uint32_t d = tmem_u + (t & 1) * BNK, kt_lo = k_lo + s * (K_BYTES >> 4);   // descriptors count in 16-byte units
+      if (elect_one()) {
 #pragma unroll
-      for (int k = 0; k < HD / UMMA_K; ++k)
-        umma_bf16(tmem_s + (t & 1) * BNK, smem_desc_sw128(q_addr + k * UMMA_K * 2), smem_desc_sw128(k_addr + k * UMMA_K * 2),
-                  idesc_qk, k > 0 ? 1u : 0u);
-      umma_commit(&s_full[t & 1]);
-      return true;
-    };
-    if (ok && n_tiles > 0) ok = issue_qk(0);
-    for (int i = 0; i < n_tiles && ok; ++i) {
-      const int s = i % KV_STAGES;
-      // the other S buffer is free: the softmax of tile i - 1 has read it (its P was waited for below)
-      if (i + 1 < n_tiles && !issue_qk(i + 1)) { ok = false; break; }
-      ATT_T(3)   // issuing
-      if (!mbar_wait(p_full, i & 1, abort_flag)) { ok = false; break; }
-      ATT_T(1)   // waited for P
-      if (!mbar_wait(&v_full[s], (i / KV_STAGES) & 1, abort_flag)) { ok = false; break; }
-      tc_fence_after();
-      ATT_T(2)   // waited for V
-      const uint32_t v_addr = smem_u32(smem + OFF_V + s * V_BYTES);
-#pragma unroll
-      for (int kk = 0; kk < BNK / UMMA_K; ++kk)   // 16 keys per step: 32 bytes along a row of P, two 8-row groups of V
-        umma_bf16(tmem_o, smem_desc_sw128(p_addr + kk * UMMA_K * 2), smem_desc_sw128(v_addr + kk * UMMA_K * HD * 2), idesc_pv,
-                  (i > 0 || kk > 0) ? 1u : 0u);
-      umma_commit(&kv_empty[s]);
-      umma_commit(pv_done);
+        for (int k = 0; k < HD / UMMA_K; ++k)
+          umma_bf16_lo(d, q_lo + (k * UMMA_K * 2 >> 4), kt_lo + (k * UMMA_K * 2 >> 4), idesc_qk, k > 0 ? 1u : 0u);
+        umma_commit(&s_full[t & 1]);
+      }
+      __syncwarp();
     }
 #ifdef TLLM_ATT_TIMING
     if (timed)
-      for (int k = 0; k < 8; ++k) atomicAdd(&g_att_cycles[8 + k], att_acc[k]);
+      for (int k = 0; k < 4; ++k) atomicAdd(&g_att_cycles[8 + k], att_acc[k]);
 #endif
-    if (!ok && !*abort_flag) { *abort_flag = 1; atomicExch(p.status, ERR_ATT_MMA); }
-  } else if (warp >= 2) {
+    if (!ok && lane == 0 && !*abort_flag) { *abort_flag = 1; atomicExch(p.status, ERR_ATT_MMA); }
+  } else if (warp == 6) {
+    // ---------------- O += P V of tile i, when the softmax has written P (the same way: warp-wide loop, one lane issues)
+    const uint32_t idesc_pv = instr_desc_bf16(BM, HD, true);   // V as it lies: rows = keys (MN-major B)
+    const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
+    const uint32_t v_lo = smem_desc_sw128_lo(smem_u32(smem + OFF_V));
+    const uint32_t tmem_o = tmem_u + TMEM_O;
+    bool ok = true;
+#ifdef TLLM_ATT_TIMING
+    const bool timed = blockIdx.x == 0 && lane == 0;
+    unsigned long long att_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    long long att_prev = clock64();
+#endif
+    for (int i = 0; i < n_tiles; ++i) {
+      const int s = i % KV_STAGES;
+      ATT_T(7)   // issuing
+      ok = mbar_wait(&p_full[i & 1], (i >> 1) & 1, abort_flag);
+      ATT_T(6)   // waited for P
+      ok = ok && mbar_wait(&v_full[s], (i / KV_STAGES) & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      ATT_T(2)   // waited for V
+      const uint32_t a = tmem_u + TMEM_P + (i & 1) * (BNK / 2), vt_lo = v_lo + s * (V_BYTES >> 4);
+      const uint32_t acc0 = i > 0 ? 1u : 0u;
+      if (elect_one()) {
+#pragma unroll
+        for (int kk = 0; kk < BNK / UMMA_K; ++kk)   // 16 keys per step: eight columns of P pairs, two 8-row groups of V
+          umma_bf16_ts_lo(tmem_o, a + kk * (UMMA_K / 2), vt_lo + (kk * UMMA_K * HD * 2 >> 4), idesc_pv, kk > 0 ? 1u : acc0);
+        umma_commit(&kv_empty[s]);
+        umma_commit(&o_done[i & 1]);
+      }
+      __syncwarp();
+    }
+#ifdef TLLM_ATT_TIMING
+    if (timed) {
+      atomicAdd(&g_att_cycles[8 + 2], att_acc[2]);
+      atomicAdd(&g_att_cycles[8 + 6], att_acc[6]);
+      atomicAdd(&g_att_cycles[8 + 7], att_acc[7]);
+    }
+#endif
+    if (!ok && lane == 0 && !*abort_flag) { *abort_flag = 1; atomicExch(p.status, ERR_ATT_MMA); }
+  } else if (warp >= 2 && warp < 6) {
     // ---------------- softmax: this thread owns row `row` of the tile (tensor-memory lane)
     const int quad = warp & 3;
     const int row = quad * 32 + lane;
     const int grow = row0 + row;
     const bool live = grow < rows_total;
     const int pos = start + grow / group;
-    const uint32_t t_s0 = tmem_base + ((uint32_t)(quad * 32) << 16), t_o = t_s0 + 2 * BNK;
-    uint8_t* p_row = smem + OFF_P + row * 128;
+    const uint32_t t_s0 = tmem_base + ((uint32_t)(quad * 32) << 16), t_o = t_s0 + TMEM_O, t_p0 = t_s0 + TMEM_P;
     const int soft_tid = (warp - 2) * 32 + lane;   // 0..127 among the softmax threads
     const float c = p.scale_log2;
     float m_run = -CUDART_INF_F, l_run = 0.f;
@@ -276,9 +309,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #endif
     for (int i = 0; i < n_tiles; ++i) {
       const int s = i % KV_STAGES;
-      ok = mbar_wait(&s_full[i & 1], (i >> 1) & 1, abort_flag);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+      ok = mbar_wait(&s_full[i & 1], (i >> 1) & 1, abort_flag);   // (a wait that gave up is seen at this tile's vote below)
       tc_fence_after();
       ATT_T(0)   // waited for S
       const uint32_t t_s = t_s0 + (i & 1) * BNK;
@@ -324,28 +355,25 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       l_run = l_run * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
       ATT_T(2)   // maximum, exponentials, sum
-      if (i > 0) {   // the product before this one has read P and finished O
-        ok = mbar_wait(pv_done, (i - 1) & 1, abort_flag);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        tc_fence_after();
-      }
-      ATT_T(3)   // waited for the product before
-      // P as bfloat16, 16-byte chunk j of the row stored at chunk position j ^ (row % 8): the 128-byte swizzle
+      // P as bfloat16 pairs in the P buffer of this tile's parity: the A operand of O += P V, taken from tensor
+      // memory.  The product of tile i - 2 has read that buffer: S of this tile was issued after it had finished.
+      {
+        uint32_t pk[BNK / 2];
 #pragma unroll
-      for (int ch = 0; ch < BNK / 8; ++ch) {
-        uint4 v;
-        v.x = pack_bf16(sc[ch * 8 + 0], sc[ch * 8 + 1]);
-        v.y = pack_bf16(sc[ch * 8 + 2], sc[ch * 8 + 3]);
-        v.z = pack_bf16(sc[ch * 8 + 4], sc[ch * 8 + 5]);
-        v.w = pack_bf16(sc[ch * 8 + 6], sc[ch * 8 + 7]);
-        *reinterpret_cast<uint4*>(p_row + ((ch ^ (row & 7)) << 4)) = v;
+        for (int j = 0; j < BNK / 2; ++j) pk[j] = pack_bf16(sc[2 * j], sc[2 * j + 1]);
+        tmem_st32_raw(t_p0 + (i & 1) * (BNK / 2), pk);
       }
-      ATT_T(4)   // P stored
-      if (i > 0 && !__all_sync(0xffffffffu, corr == 1.f)) {   // the maximum of some row of this warp moved
+      ATT_T(3)   // P on its way to tensor memory
+      if (!__all_sync(0xffffffffu, ok && (i == 0 || corr == 1.f))) {   // the maximum of some row of this warp moved far
+        ok = __all_sync(0xffffffffu, ok);                               // (or a wait gave up)
+        if (!ok) break;
 #ifdef TLLM_ATT_TIMING
         if (timed) att_acc[7] += 1;
 #endif
+        ok = mbar_wait(&o_done[(i - 1) & 1], ((i - 1) >> 1) & 1, abort_flag);   // the product before this one has finished O
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
 #pragma unroll
         for (int h = 0; h < HD; h += 32) {
           float o[32];
@@ -355,6 +383,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           tmem_st32(t_o + h, o);
         }
       }
+      tmem_st_wait();
       ATT_T(5)   // O rescaled
       if (j0 + BNK > kv_end) {   // value rows past the last key hold whatever the page held: zero them
         ok = mbar_wait(&v_full[s], (i / KV_STAGES) & 1, abort_flag);
@@ -365,10 +394,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
           for (int ch = 0; ch < 8; ++ch) vrow[ch] = make_uint4(0u, 0u, 0u, 0u);
         }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // V was written by ordinary stores
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P (and V) were written by ordinary stores
       tc_fence_before();
-      mbar_arrive(p_full);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[i & 1]);
       ATT_T(6)   // fences, arrival
     }
 #ifdef TLLM_ATT_TIMING
@@ -376,7 +406,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       for (int k = 0; k < 8; ++k) atomicAdd(&g_att_cycles[k], att_acc[k]);
 #endif
     if (ok && n_tiles > 0) {
-      ok = mbar_wait(pv_done, (n_tiles - 1) & 1, abort_flag);
+      ok = mbar_wait(&o_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (!ok) {
