@@ -298,25 +298,31 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
         if (!pre || SWAP) tma_load_2d(a_dst + L::A_BYTES, &map_b, (kb_begin + i) * BK, tile_b * BN, &full_bar[s]);
       }
-    } else if (warp == 1 && lane == 0) {
-      // ---------------- MMA issuer
+    } else if (warp == 1) {
+      // ---------------- MMA issuer: the whole warp walks the loop and waits, one elected lane issues (a loop
+      // walked by one lane alone spends about twice as long between two stages)
       const uint32_t idesc = instr_desc_bf16(BM, BN);
+      const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
+      const uint32_t lo0 = smem_desc_sw128_lo(smem_u32(smem));
       bool ok = true;
-      for (int i = 0; i < n_kb && ok; ++i) {
+      for (int i = 0; i < n_kb; ++i) {
         const int s = i % STAGES;
         const uint32_t parity = (i / STAGES) & 1;
-        if (!mbar_wait(&full_bar[s], parity, abort_flag)) { *abort_flag = 1; atomicExch(status, ERR_MMA); ok = false; break; }
+        ok = __all_sync(0xffffffffu, mbar_wait(&full_bar[s], parity, abort_flag));
+        if (!ok) break;
         tc_fence_after();
-        const uint32_t a_addr = smem_u32(smem + s * L::STAGE_BYTES);
-        const uint32_t b_addr = a_addr + L::A_BYTES;
+        const uint32_t a_lo = lo0 + s * (L::STAGE_BYTES >> 4), b_lo = a_lo + (L::A_BYTES >> 4);   // descriptors count in 16-byte units
+        if (elect_one()) {
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k) {
-          umma_bf16(tmem_base, smem_desc_sw128(a_addr + k * UMMA_K * 2), smem_desc_sw128(b_addr + k * UMMA_K * 2),
-                    idesc, (i > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_bf16_lo(tmem_u, a_lo + (k * UMMA_K * 2 >> 4), b_lo + (k * UMMA_K * 2 >> 4), idesc, (i > 0 || k > 0) ? 1u : 0u);
+          umma_commit(&empty_bar[s]);   // the stage is free once these MMAs have read it
         }
-        umma_commit(&empty_bar[s]);   // the stage is free once these MMAs have read it
+        __syncwarp();
       }
-      umma_commit(acc_bar);           // arrives when every MMA issued so far has completed
+      if (!ok && lane == 0) { *abort_flag = 1; atomicExch(status, ERR_MMA); }
+      if (elect_one()) umma_commit(acc_bar);   // arrives when every MMA issued so far has completed
+      __syncwarp();
     } else if (warp >= 2) {
       // ---------------- epilogue: warp w reads tensor-memory lanes [32 (w % 4), +32)
       const int quad = warp & 3;
@@ -488,24 +494,30 @@ linear_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       }
       tma_load_2d(a_dst + L::A_BYTES, &map_b, (kb_begin + i) * BK, tile_b * BN, &full_bar[s]);
     }
-  } else if (warp == 1 && lane == 0) {
-    // ---------------- MMA issuer
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (warp-wide loop, one elected lane issues)
     const uint32_t idesc = instr_desc_bf16(BM, BN);
+    const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
+    const uint32_t lo0 = smem_desc_sw128_lo(smem_u32(smem));
+    bool ok = true;
     for (int i = 0; i < n_kb; ++i) {
       const int s = i % STAGES;
       const uint32_t parity = (i / STAGES) & 1;
-      if (!mbar_wait(&full_bar[s], parity, abort_flag)) { *abort_flag = 1; atomicExch(status, ERR_MMA); break; }
+      ok = __all_sync(0xffffffffu, mbar_wait(&full_bar[s], parity, abort_flag));
+      if (!ok) break;
       tc_fence_after();
-      const uint32_t a_addr = smem_u32(smem + s * L::STAGE_BYTES);
-      const uint32_t b_addr = a_addr + L::A_BYTES;
+      const uint32_t a_lo = lo0 + s * (L::STAGE_BYTES >> 4), b_lo = a_lo + (L::A_BYTES >> 4);
+      if (elect_one()) {
 #pragma unroll
-      for (int k = 0; k < BK / UMMA_K; ++k) {
-        umma_bf16(tmem_base, smem_desc_sw128(a_addr + k * UMMA_K * 2), smem_desc_sw128(b_addr + k * UMMA_K * 2),
-                  idesc, (i > 0 || k > 0) ? 1u : 0u);
+        for (int k = 0; k < BK / UMMA_K; ++k)
+          umma_bf16_lo(tmem_u, a_lo + (k * UMMA_K * 2 >> 4), b_lo + (k * UMMA_K * 2 >> 4), idesc, (i > 0 || k > 0) ? 1u : 0u);
+        umma_commit(&empty_bar[s]);
       }
-      umma_commit(&empty_bar[s]);
+      __syncwarp();
     }
-    umma_commit(acc_bar);
+    if (!ok && lane == 0) { *abort_flag = 1; atomicExch(status, ERR_MMA); }
+    if (elect_one()) umma_commit(acc_bar);
+    __syncwarp();
   } else if (warp >= 2) {
     // ---------------- park the accumulators: warp w reads tensor-memory lanes [32 (w % 4), +32)
     const int quad = warp & 3;
@@ -730,30 +742,38 @@ linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         tma_load_2d(a_dst, &map_a, kb * BK, tm * BM, &full_bar[s]);
       }
     }
-  } else if (warp == 1 && lane == 0) {
-    // ---------------- MMA issuer
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (warp-wide loop, one elected lane issues)
+    const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
+    const uint32_t lo0 = smem_desc_sw128_lo(smem_u32(smem));
     int it = 0, local = 0;
     bool ok = true;
     for (int t = first_tile; t < n_items && ok; t += gridDim.x, ++local) {
       const uint32_t idesc = instr_desc_bf16(BM, item_width(t));
       const int buf = local & 1;
-      if (!mbar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1, abort_flag)) { *abort_flag = 1; atomicExch(status, ERR_MMA); break; }
+      ok = __all_sync(0xffffffffu, mbar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1, abort_flag));
+      if (!ok) break;
       tc_fence_after();
-      const uint32_t d_tmem = tmem_base + buf * BN;
+      const uint32_t d_tmem = tmem_u + buf * BN;
       for (int kb = 0; kb < k_blocks; ++kb, ++it) {
         const int s = it % STAGES;
-        if (!mbar_wait(&full_bar[s], (it / STAGES) & 1, abort_flag)) { *abort_flag = 1; atomicExch(status, ERR_MMA); ok = false; break; }
+        ok = __all_sync(0xffffffffu, mbar_wait(&full_bar[s], (it / STAGES) & 1, abort_flag));
+        if (!ok) break;
         tc_fence_after();
-        const uint32_t a_addr = smem_u32(smem + s * L::STAGE_BYTES);
-        const uint32_t b_addr = a_addr + L::A_BYTES;
+        const uint32_t a_lo = lo0 + s * (L::STAGE_BYTES >> 4), b_lo = a_lo + (L::A_BYTES >> 4);
+        if (elect_one()) {
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k)
-          umma_bf16(d_tmem, smem_desc_sw128(a_addr + k * UMMA_K * 2), smem_desc_sw128(b_addr + k * UMMA_K * 2), idesc,
-                    (kb > 0 || k > 0) ? 1u : 0u);
-        umma_commit(&empty_bar[s]);
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_bf16_lo(d_tmem, a_lo + (k * UMMA_K * 2 >> 4), b_lo + (k * UMMA_K * 2 >> 4), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit(&empty_bar[s]);
+        }
+        __syncwarp();
       }
-      umma_commit(&acc_full[buf]);   // arrives when this tile's MMAs have completed
+      if (!ok) break;
+      if (elect_one()) umma_commit(&acc_full[buf]);   // arrives when this tile's MMAs have completed
+      __syncwarp();
     }
+    if (!ok && lane == 0) { *abort_flag = 1; atomicExch(status, ERR_MMA); }
   } else if (warp >= 2) {
     // ---------------- epilogue: warp w reads tensor-memory lanes [32 (w % 4), +32)
     const int quad = warp & 3;
