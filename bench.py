@@ -283,8 +283,15 @@ def main():
                 rec["cycles_per_step"] = {n: round(v / (steps + warmup)) for n, v in zip(names, cycles)}
             print(json.dumps(rec))
         else:
-            print(json.dumps({"only": "prefill", "layers": args.layers, "tokens": 2048,
-                              "ms": round(timed_prefill(runner, 2048, repeats=2), 3)}))
+            ops.attention_tc_timing()   # (a build with cycle counters: start from zero)
+            rec = {"only": "prefill", "layers": args.layers, "tokens": 2048,
+                   "ms": round(timed_prefill(runner, 2048, repeats=2), 3)}
+            cycles = ops.attention_tc_timing()
+            if cycles is not None:
+                # cycles per key tile in the roles of the attention kernel's first CTA, which walks 2048 / 64 tiles
+                tiles = (2048 // 64) * args.layers * 4
+                rec["attention_cycles_per_tile"] = {n: round(v / tiles, 1) for n, v in cycles.items()}
+            print(json.dumps(rec))
         return 0
 
     sampler = ClockSampler().start()

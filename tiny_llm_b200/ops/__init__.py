@@ -478,6 +478,21 @@ def decode_step_timing(head_dim: int):
     return list(out)
 
 
+def attention_tc_timing() -> Optional[dict]:
+    """Cycles that the roles of the prompt-attention kernel's first CTA spent per phase since the last call, or
+    None if the kernel was not built with TLLM_NVCC_FLAGS_ATTENTION_TC=-DTLLM_ATT_TIMING=1."""
+    lib = build.load_library("attention_tc", flags=("-DTLLM_HEAD_DIM=64",))
+    if not hasattr(lib, "tllm_attention_tc_timing"):
+        return None
+    out = (ctypes.c_ulonglong * 16)()
+    lib.tllm_attention_tc_timing(out)
+    names = ["softmax: wait S", "softmax: S to registers", "softmax: max, exp2, sum", "softmax: P to tensor memory",
+             "(unused)", "softmax: vote, store wait", "softmax: fence, arrive", "rescales of O",
+             "qk: wait K", "qk: wait S buffer", "pv: wait V", "qk: issue", "tma: wait free stage", "tma: issue",
+             "pv: wait P", "pv: issue"]
+    return {n: int(v) for n, v in zip(names, out) if n != "(unused)"}
+
+
 def decode_step_refusal(head_dim: int, params: DecodeParams) -> Optional[str]:
     """None if the fused kernel takes these sizes, else the reason it does not."""
     lib = decode_step_library(head_dim)
