@@ -1,5 +1,5 @@
 """A decode step as ONE kernel, where the model allows it.  An option (TLLM_FUSED_DECODE=1), off by
-default: at the TinyLlama shape it measures 1.39 ms per step of eight requests against 0.85 ms for
+default: at the TinyLlama shape it measures 1.39 ms per step of eight requests against 0.82 ms for
 the part-by-part path under a CUDA graph (its grid barriers and activation reloads cost what the
 kernel boundaries cost there), so it is kept as a second, tested way to run the step, not the first.
 
