@@ -222,7 +222,7 @@ def timed_e2e(pipe, batch, context, steps, warmup):
 
 def reference_arm():
     """The reference is a Bazel + Rust + CUDA >= 13 C++ project without a Python package: the one
-    allowed offline install (pip install --no-index ... /root/reference) has nothing to build."""
+    allowed offline install (pip install --no-index ... of the reference checkout) has nothing to build."""
     print(json.dumps({"impl": "reference", "unavailable":
                       "zscey/tiny-llm is a Bazel/Rust/CUDA-13 C++ project with no setup.py or pyproject.toml; "
                       "pip cannot install it offline and no Bazel or Rust toolchain exists here"}))

@@ -108,7 +108,7 @@ def check_attention_block(ref_root):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "..", "reference")
     block, table, scale = check_attention_block(ref_root)
     result = {
         "rms_norm_b2l107d241": check_rms_norm(ref_root),

@@ -10,7 +10,7 @@ import torch
 import plain_llama as pl
 from conftest import TINY_A, TINY_B
 
-REF = os.environ.get("TINY_LLM_REFERENCE", "/root/reference")
+REF = os.environ.get("TINY_LLM_REFERENCE", os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "reference"))   # a tiny-llm checkout, if one lies beside the repository
 
 
 def test_committed_golden_differences_are_small():
