@@ -277,6 +277,11 @@ def test_paged_attention_on_tcgen05(ops, nq, nkv, page):
     qkv[last, :hd] *= 6.0
     ks[0][5, 0] = (qkv[last, :hd] / qkv[last, :hd].float().norm() * 8.0).to(DT[dtype])
     k_cache[int(table[0, 5 // page]), 0, 5 % page] = ks[0][5, 0]
+    # ... and the query before it with key 450, eight tiles into the keys: the running maximum of that row jumps
+    # far after O already holds seven tiles (the kernel rescales O only on such jumps)
+    qkv[last - 1, :hd] *= 6.0
+    ks[0][450, 0] = (qkv[last - 1, :hd] / qkv[last - 1, :hd].float().norm() * 8.0).to(DT[dtype])
+    k_cache[int(table[0, 450 // page]), 0, 450 % page] = ks[0][450, 0]
     pos = torch.cat([torch.arange(l - n, l, dtype=torch.int32) for l, n in zip(lens, q_lens)])
     cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
     starts = torch.tensor([l - n for l, n in zip(lens, q_lens)], dtype=torch.int32)
@@ -303,6 +308,8 @@ def test_paged_attention_on_tcgen05(ops, nq, nkv, page):
         cur += n
     p = torch.softmax((qkv[last, :hd].float() * scale) @ ks[0][:lens[0], 0].float().t(), 0)
     assert float(p[5]) > 0.9
+    p = torch.softmax((qkv[last - 1, :hd].float() * scale) @ ks[0][:lens[0] - 1, 0].float().t(), 0)
+    assert float(p[450]) > 0.9
 
 
 def test_attention_refuses_sizes_it_is_not_built_for(ops):
