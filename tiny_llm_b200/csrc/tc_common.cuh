@@ -68,22 +68,6 @@ __device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
 }
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// The same product with the A operand in tensor memory: row m of A in lane m, its K elements (16-bit) packed
-// in pairs along the columns from a_tmem on (element 2 c in the low half of column c).
-__device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -130,17 +114,11 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, stored with the
-// 128-byte swizzle: 8-row groups are 1024 bytes apart (stride byte offset), descriptor version 1.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((addr & 0x3FFFF) >> 4);    // start address, 16-byte units
-  d |= (uint64_t)1 << 16;                    // leading byte offset (unused with a swizzle, K-major)
-  d |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset
-  d |= (uint64_t)1 << 46;                    // descriptor version of sm_100
-  d |= (uint64_t)2 << 61;                    // SWIZZLE_128B
-  return d;
-}
+// Shared-memory matrix descriptor (64 bits) of a K-major tile whose rows are 128 bytes, stored with the
+// 128-byte swizzle: bits 0-13 start address in 16-byte units, 16-29 leading byte offset (unused with a swizzle,
+// K-major: 1), 32-45 stride byte offset in 16-byte units (8-row groups are 1024 bytes apart), 46 the descriptor
+// version of sm_100, 61-63 the swizzle (2: 128 bytes).
+//
 // The issuing thread's time between two products is a chain of dependent instructions, and with small tiles it,
 // not the tensor pipe, sets the pace (about 60 cycles per product when nothing else is computed, twice that with
 // a 64-bit descriptor built per product).  All descriptors of one kernel share their upper word; the lower one
@@ -156,6 +134,8 @@ __device__ __forceinline__ void umma_bf16_lo(uint32_t d_tmem, uint32_t a_lo, uin
       "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t}"
       ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(SMEM_DESC_SW128_HI) : "memory");
 }
+// ... with the A operand in tensor memory: row m of A in lane m, its K elements (16-bit) packed in pairs along
+// the columns from a_tmem on (element 2 c in the low half of column c).
 __device__ __forceinline__ void umma_bf16_ts_lo(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
