@@ -271,16 +271,9 @@ def main():
         if args.only == "decode":
             ms, launched = timed_decode(runner, args.batch, start_len, steps, warmup, out)
             rec = {"only": "decode", "batch": args.batch, "layers": args.layers, "ms_per_step": round(ms, 4),
-                   "gpu_launches": launched, "fused_decode_step": runner._fused is not None}
+                   "gpu_launches": launched}
             if TRACE:
                 rec["timeline"] = timeline_summary(timed_decode.timeline)
-            if runner._fused is not None and os.environ.get("TLLM_STEP_TIMING"):
-                # device cycles one CTA of the fused decode step spent per kind of phase, per step
-                names = ["norm_load", "qkv", "grid_barriers", "attention", "combine", "plain_load", "o_proj", "gate_up",
-                         "down", "lm_head", "producer_waits_for_free_stage", "producer_total", "consumer_waits_for_weights",
-                         "reduce_and_epilogue"]
-                cycles = ops.decode_step_timing(cfg.head_dim)
-                rec["cycles_per_step"] = {n: round(v / (steps + warmup)) for n, v in zip(names, cycles)}
             print(json.dumps(rec))
         else:
             ops.attention_tc_timing()   # (a build with cycle counters: start from zero)
@@ -346,6 +339,7 @@ def main():
         "points": points, "clocks": clocks,
         "libraries": sorted(os.path.basename(p) for p in ops.build.loaded_libraries().values()),
     }
+    ops.check_status()   # no kernel of the timed runs gave up a bounded wait
     print(json.dumps(line))
     return 0
 

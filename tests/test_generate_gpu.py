@@ -119,3 +119,28 @@ def test_command_line(model_dirs):
     assert outs[0] == " ".join(map(str, pipe.apply([[9, 8, 7]], max_new_tokens=5, do_sample=False)[0]))
     bad = subprocess.run([sys.executable, "-m", "tiny_llm_b200"], capture_output=True, text=True, cwd=ROOT)
     assert bad.returncode == 1 and "model_path" in bad.stderr
+
+
+def test_command_line_random_weights_and_a_batch_of_prompts(model_dirs, tmp_path):
+    """--random_weights --config --seed makes the model that write_random_model makes; with
+    --prompt_per_line the lines of a block run as one batch through the scheduler (portions of
+    --chunk tokens under --max_tokens_per_step), with the tokens each prompt gives alone."""
+    import json
+    from conftest import TINY_A
+    from tiny_llm_b200 import Pipeline
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(TINY_A))
+    cmd = [sys.executable, "-m", "tiny_llm_b200", "--random_weights", f"--config={cfg_path}", "--seed=0",
+           "--max_new_tokens=6", "--nodo_sample", "--dtype=float32", "--prompt_per_line", "--max_requests=3",
+           "--max_tokens_per_step=8", "--chunk=5", "--num_pages=12", "--page_size=16"]
+    lines = ["9 8 7 6 5 4 3 10 11 12 13 14", "3, 4", "5 6 7 8 9 10 11"]
+    res = subprocess.run(cmd, input="\n".join(lines) + "\n\n", capture_output=True, text=True, cwd=ROOT, timeout=300)
+    assert res.returncode == 0, res.stderr
+    outs = [l for l in res.stdout.splitlines() if l and l[0].isdigit()]
+    assert len(outs) == 3
+    pipe = Pipeline(model_dirs["A"], dtype="float32", max_tokens=512, max_requests=2)   # seed 0: the same weights
+    for line, out in zip(lines, outs):
+        prompt = [int(t) for t in line.replace(",", " ").split()]
+        assert out == " ".join(map(str, pipe.apply([prompt], max_new_tokens=6, do_sample=False)[0]))
+    bad = subprocess.run([sys.executable, "-m", "tiny_llm_b200", "--random_weights"], capture_output=True, text=True, cwd=ROOT)
+    assert bad.returncode == 1 and "--config" in bad.stderr

@@ -127,3 +127,23 @@ def test_random_load_always_drains(seed):
         steps += 1
         assert steps < 2000
     assert len(done) == 12 and cache.groups[0].pool.num_used == 0 and cache.slots.num_free == 3
+
+
+def test_a_windowed_group_admits_by_its_window_and_shrinks_the_first_portion():
+    """A pool that holds a window and a little more: a long prompt is admitted with a first portion
+    that fits, runs to its end with pages coming back behind the window, and a request whose window
+    can never fit is refused on arrival instead of waiting for ever."""
+    cache = CacheManager([KVNeed(1, 16, window=8)], max_tokens=20, page_size=4, max_slots=2)
+    s = Scheduler(cache, 64, max_tokens_per_step=32, max_requests_per_step=2, chunk=32)
+    s.add(req("w", 40, new=3))
+    steps = 0
+    while s.has_work():
+        plan, _ = run_step(s, cache)
+        assert plan, "the scheduler planned nothing although a request waits and nothing runs"
+        cache.check()
+        steps += 1
+        assert steps < 100
+    assert cache.groups[0].pool.num_used == 0
+    small = CacheManager([KVNeed(1, 16, window=16)], max_tokens=8, page_size=4, max_slots=2)
+    with pytest.raises(RequestRefused):
+        Scheduler(small, 64, chunk=8).add(req("x", 30))

@@ -119,3 +119,55 @@ def test_gate_up_interleave():
     wu = -torch.arange(12.).view(6, 2)
     f = interleave_gate_up(wg, wu, 2)
     assert torch.equal(f[0:2], wg[0:2]) and torch.equal(f[2:4], wu[0:2]) and torch.equal(f[8:10], wg[4:6])
+
+
+def test_sharded_checkpoint_alias_of_the_output_matrix_and_harmless_extras(tmp_path):
+    """A folder as large checkpoints are published: shards + index, no lm_head.weight (the embedding
+    table stands in), and the rotary frequencies that older files carry."""
+    from tiny_llm_b200.weights import ShardedSafetensors
+    cfg = LlamaConfig.from_dict(TINY_A)
+    spec = cfg.model_spec()
+    specs = DecoderModel(spec).weight_specs()
+    state = random_state(specs, 0, 0.02, torch.float32)
+    whole = load_state(specs, state, torch.float32, "cpu")
+    del state["lm_head.weight"]
+    state["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.ones(8)
+    names = sorted(state)
+    shards = {"model-00001-of-00002.safetensors": names[: len(names) // 2],
+              "model-00002-of-00002.safetensors": names[len(names) // 2:]}
+    for fname, part in shards.items():
+        save_safetensors(str(tmp_path / fname), {n: state[n] for n in part})
+    index = {"metadata": {"total_size": 0}, "weight_map": {n: f for f, part in shards.items() for n in part}}
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps(index))
+    got = load_state(specs, str(tmp_path), torch.float32, "cpu", ignore=spec.ignored_weights)
+    assert got["lm_head.weight"] is got["model.embed_tokens.weight"]          # one tensor, not a copy
+    for n in specs:
+        if n != "lm_head.weight":
+            assert torch.equal(got[n], whole[n]), n
+    # without the allow-list the extra tensor is an error, as every unknown tensor is
+    with pytest.raises(WeightError, match=r"unexpected \(1\): model.layers.0.self_attn.rotary_emb.inv_freq"):
+        load_state(specs, str(tmp_path), torch.float32, "cpu")
+    # an index that names a tensor its shard does not hold, or a shard that is not there
+    other = [f for f, part in shards.items() if "model.norm.weight" not in part][0]
+    index["weight_map"]["model.norm.weight"] = other
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps(index))
+    with pytest.raises(WeightError, match="is not in"):
+        ShardedSafetensors(str(tmp_path))
+    index["weight_map"]["model.norm.weight"] = "model-00003-of-00002.safetensors"
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps(index))
+    with pytest.raises(WeightError, match="no such weights file"):
+        ShardedSafetensors(str(tmp_path))
+
+
+def test_a_tied_model_tolerates_a_stored_output_matrix_and_an_untied_one_without_embedding_still_fails():
+    cfg = LlamaConfig.from_dict(TINY_B)          # tied
+    spec = cfg.model_spec()
+    specs = DecoderModel(spec).weight_specs()
+    state = random_state(specs, 1, 0.02, torch.float32)
+    state["lm_head.weight"] = state["model.embed_tokens.weight"].clone()
+    assert "lm_head.weight" not in load_state(specs, state, torch.float32, "cpu", ignore=spec.ignored_weights)
+    untied = DecoderModel(LlamaConfig.from_dict(TINY_A).model_spec()).weight_specs()
+    st = random_state(untied, 0, 0.02, torch.float32)
+    del st["lm_head.weight"], st["model.embed_tokens.weight"]
+    with pytest.raises(WeightError, match=r"missing \(2\): lm_head.weight, model.embed_tokens.weight"):
+        load_state(untied, st, torch.float32, "cpu")

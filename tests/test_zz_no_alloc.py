@@ -45,7 +45,7 @@ def test_noalloc_entry_point_matches_the_regular_one_twice_in_a_row():
         want = torch.full((n,), -1, dtype=torch.int32, device=DEV)
         work = torch.empty(n * v, device=DEV)
         rc = lib.tllm_sample(ptr(logits), ptr(work), n, v, ptr(temps), ptr(top_k), ptr(top_p), ptr(seeds),
-                             ptr(counters), ptr(want), stream)
+                             ptr(counters), ptr(want), ctypes.c_void_p(0), stream)
         assert rc == 0, lib.tllm_last_error().decode()
         got = torch.full((n,), -2, dtype=torch.int32, device=DEV)
         before = torch.cuda.memory_allocated()

@@ -135,7 +135,10 @@ class LlamaConfig:
             max_positions=self.max_position_embeddings, layers=layers,
             order=[LayerCall(i) for i in range(self.num_hidden_layers)], final_norm=norm,
             tie_word_embeddings=self.tie_word_embeddings, eos_token_ids=self.eos_token_ids,
-            initializer_range=self.initializer_range)
+            initializer_range=self.initializer_range,
+            # older checkpoints store the rotary frequencies (the table here is made from rope_theta);
+            # a tied model may still store its output matrix, which is the embedding table again
+            ignored_weights=("*.rotary_emb.inv_freq",) + (("lm_head.weight",) if self.tie_word_embeddings else ()))
 
 
 register_architecture(LlamaConfig.architecture, LlamaConfig)

@@ -39,7 +39,8 @@ def config_from_dict(d: dict):
 
 
 def load_config(model_dir: str):
-    path = os.path.join(model_dir, "config.json")
+    """The configuration of a model folder (its config.json), or of a config.json given by its own path."""
+    path = model_dir if os.path.isfile(model_dir) else os.path.join(model_dir, "config.json")
     if not os.path.isfile(path):
         raise ConfigError(f"no config.json in {model_dir}")
     with open(path) as f:

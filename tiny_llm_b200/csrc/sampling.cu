@@ -173,10 +173,19 @@ __device__ __forceinline__ int block_argmax(const float* __restrict__ row, int v
   return (int)(0xffffffffu - (unsigned)(sc.u[32] & 0xffffffffull));
 }
 
-__global__ void __launch_bounds__(ST) argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int v) {
+// `status` (may be null): the device word in which the step's kernels record a bounded wait that
+// expired.  Block 0 copies it behind the chosen ids (out[gridDim.x]), so that it reaches the host in
+// the copy that carries the ids and a step whose kernel gave up is never mistaken for a result.
+__device__ __forceinline__ void forward_status(const int* status, int* out) {
+  if (status != nullptr && blockIdx.x == 0 && threadIdx.x == 0) out[gridDim.x] = *status;
+}
+
+__global__ void __launch_bounds__(ST)
+argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int v, const int* __restrict__ status) {
   __shared__ BlockScratch sc;
   pdl_trigger();
   pdl_wait();
+  forward_status(status, out);
   const int b = blockIdx.x;
   const int r = block_argmax(logits + (size_t)b * v, v, sc);
   if (threadIdx.x == 0) out[b] = r;
@@ -194,11 +203,13 @@ __global__ void __launch_bounds__(ST)
 sample_kernel(const float* __restrict__ logits, float* __restrict__ work, int v,
               const float* __restrict__ temperature, const int* __restrict__ top_k,
               const float* __restrict__ top_p, const unsigned long long* __restrict__ seeds,
-              const unsigned long long* __restrict__ counters, int* __restrict__ out) {
+              const unsigned long long* __restrict__ counters, int* __restrict__ out,
+              const int* __restrict__ status) {
   __shared__ BlockScratch sc;
   __shared__ int s_choice, s_last;
   pdl_trigger();
   pdl_wait();
+  forward_status(status, out);
   const int b = blockIdx.x;
   const float* row = logits + (size_t)b * v;
   const float temp = temperature[b];
@@ -304,18 +315,20 @@ sample_kernel(const float* __restrict__ logits, float* __restrict__ work, int v,
 
 using namespace tllm;
 
-extern "C" int tllm_argmax(const float* logits, int* out, int n, int v, void* stream) {
+// status (both entry points): null, or the device status word of the step's kernels; out then has
+// room for n + 1 ints and out[n] receives the word.
+extern "C" int tllm_argmax(const float* logits, int* out, int n, int v, const int* status, void* stream) {
   TLLM_REQUIRE(n > 0 && v > 0, "argmax: empty input (%d rows of %d)", n, v);
-  TLLM_LAUNCH("argmax", argmax_kernel, n, ST, 0, (cudaStream_t)stream, logits, out, v);
+  TLLM_LAUNCH("argmax", argmax_kernel, n, ST, 0, (cudaStream_t)stream, logits, out, v, status);
   return TLLM_OK;
 }
 
 extern "C" int tllm_sample(const float* logits, float* work, int n, int v, const float* temperature, const int* top_k,
                            const float* top_p, const unsigned long long* seeds, const unsigned long long* counters,
-                           int* out, void* stream) {
+                           int* out, const int* status, void* stream) {
   TLLM_REQUIRE(n > 0 && v > 0, "sample: empty input (%d rows of %d)", n, v);
   TLLM_REQUIRE(work != nullptr, "sample: needs n*V floats of scratch");
-  TLLM_LAUNCH("sample", sample_kernel, n, ST, 0, (cudaStream_t)stream, logits, work, v, temperature, top_k, top_p, seeds, counters, out);
+  TLLM_LAUNCH("sample", sample_kernel, n, ST, 0, (cudaStream_t)stream, logits, work, v, temperature, top_k, top_p, seeds, counters, out, status);
   return TLLM_OK;
 }
 
@@ -327,9 +340,12 @@ extern "C" int tllm_sample(const float* logits, float* work, int n, int v, const
 
 static __device__ __align__(256) float g_noalloc_scratch[TLLM_SAMPLE_NOALLOC_MAX_FLOATS];
 
+#include <mutex>
+
 namespace {
 constexpr int kMaxDevices = 64;
 float* g_noalloc_ptr[kMaxDevices] = {};   // device address of the array, per device ordinal
+std::mutex g_noalloc_setup;               // two host threads may make their first call at once
 }  // namespace
 
 extern "C" int tllm_sample_noalloc(const float* logits, int n, int v, const float* temperature, const int* top_k,
@@ -343,15 +359,20 @@ extern "C" int tllm_sample_noalloc(const float* logits, int n, int v, const floa
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) TLLM_FAIL(TLLM_ERR_CUDA, "sample_noalloc: cudaGetDevice: %s", cudaGetErrorString(e));
   TLLM_REQUIRE(dev >= 0 && dev < kMaxDevices, "sample_noalloc: device ordinal %d is out of range", dev);
-  if (g_noalloc_ptr[dev] == nullptr) {
-    // set-up, once per device, with that device current: must happen outside of stream capture
-    float* p = nullptr;
-    e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
-    if (e != cudaSuccess || p == nullptr)
-      TLLM_FAIL(TLLM_ERR_CUDA, "sample_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
-    g_noalloc_ptr[dev] = p;
+  float* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> hold(g_noalloc_setup);
+    if (g_noalloc_ptr[dev] == nullptr) {
+      // set-up, once per device, with that device current: must happen outside of stream capture
+      float* p = nullptr;
+      e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+      if (e != cudaSuccess || p == nullptr)
+        TLLM_FAIL(TLLM_ERR_CUDA, "sample_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+      g_noalloc_ptr[dev] = p;
+    }
+    scratch = g_noalloc_ptr[dev];
   }
-  TLLM_LAUNCH("sample_noalloc", sample_kernel, n, ST, 0, (cudaStream_t)stream, logits, g_noalloc_ptr[dev], v,
-              temperature, top_k, top_p, seeds, counters, out);
+  TLLM_LAUNCH("sample_noalloc", sample_kernel, n, ST, 0, (cudaStream_t)stream, logits, scratch, v,
+              temperature, top_k, top_p, seeds, counters, out, (const int*)nullptr);
   return TLLM_OK;
 }

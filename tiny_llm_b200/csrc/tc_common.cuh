@@ -10,7 +10,10 @@
 
 namespace tllm {
 
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // a wait gives up after two seconds
+#ifndef TLLM_WAIT_LIMIT_NS
+#define TLLM_WAIT_LIMIT_NS 2000000000ull   // a wait gives up after two seconds (tests build with a few ms)
+#endif
+constexpr unsigned long long WAIT_LIMIT_NS = TLLM_WAIT_LIMIT_NS;
 
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }

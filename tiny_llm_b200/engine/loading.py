@@ -29,7 +29,7 @@ def load_model(model_dir: str, dtype, device="cuda:0"):
     dtype = parse_dtype(dtype)
     config = load_config(model_dir)
     model = DecoderModel(config.model_spec())
-    model.load(load_state(model.weight_specs(), model_dir, dtype, device))
+    model.load(load_state(model.weight_specs(), model_dir, dtype, device, ignore=model.spec.ignored_weights))
     return config, model
 
 

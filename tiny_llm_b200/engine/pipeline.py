@@ -58,6 +58,18 @@ class Pipeline:
         """A pipeline around a model that is already loaded on the device (kwargs as the constructor's)."""
         return cls((config, model), **kwargs)
 
+    @classmethod
+    def from_parts(cls, runner, scheduler: Scheduler, sampler) -> "Pipeline":
+        """A pipeline around a given step function, scheduler and sampler (anything with `step`,
+        `cache`; `launch`, `collect`): what the host-side tests of the chaining logic use."""
+        self = object.__new__(cls)
+        self.runner, self.scheduler, self.sampler = runner, scheduler, sampler
+        self._ids = itertools.count()
+        self.requests = {}
+        self._pending = None
+        self.counters = {"steps": 0, "chained": 0}
+        return self
+
     # ---- request by request
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None, rid: Hashable = None):
         rid = next(self._ids) if rid is None else rid
@@ -81,6 +93,13 @@ class Pipeline:
         if not plan:
             if self._pending is not None:
                 ended += self._resolve_pending()
+            elif not ended and not self.scheduler.running and self.scheduler.waiting:
+                # nothing runs, nothing was read back, and still the oldest waiting request was not
+                # admitted: the next call would find the same, so say so instead of spinning
+                req = self.scheduler.waiting[0]
+                raise RuntimeError(f"request {req.rid!r} cannot be admitted although nothing else is running "
+                                   f"(free slots {self.runner.cache.slots.num_free}, free pages "
+                                   f"{[g.pool.num_free for g in self.runner.cache.groups]})")
             return self._forget(ended)
         entries = []
         sampling: List[Scheduled] = []
@@ -144,10 +163,15 @@ class Pipeline:
             if idx >= len(req.generated):
                 continue   # the request ended before this id was sampled: a step too many
             req.generated[idx] = tok
-            if req.state == RUNNING and self.scheduler.ends_sequence(req, tok):
+            if self.scheduler.ends_sequence(req, tok):
+                # whatever the request ran after this id is dropped, also when the chained step that
+                # followed has already ended it by length or at the model's last position
                 del req.generated[idx + 1:]
-                self.scheduler.finish(req, "eos")
-                ended.append(req)
+                if req.state == RUNNING:
+                    self.scheduler.finish(req, "eos")
+                    ended.append(req)
+                else:
+                    req.finish_reason = "eos"
         return ended
 
     def _resolve_pending(self) -> List[Request]:

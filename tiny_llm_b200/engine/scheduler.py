@@ -96,8 +96,12 @@ class Scheduler:
             raise RequestRefused(f"request {request.rid!r}: prompt of {n} tokens + max_new_tokens "
                                  f"{request.params.max_new_tokens} exceeds the model's {self.max_positions} positions")
         for g in self.cache.groups:
-            if g.need.window is None and g.pages_for(total) > g.pool.num_pages:
-                raise RequestRefused(f"request {request.rid!r}: {total} tokens need {g.pages_for(total)} pages, "
+            # the fewest tokens the request must be able to hold pages for: all of them, or, in a group
+            # with a window, the window and the token being written, rounded out to whole pages at both
+            # ends (pages behind the window come back only after the step that passed them)
+            most = total if g.need.window is None else min(total, g.need.window + 2 * g.page_size)
+            if g.pages_for(most) > g.pool.num_pages:
+                raise RequestRefused(f"request {request.rid!r}: {most} tokens need {g.pages_for(most)} pages, "
                                      f"the pool has {g.pool.num_pages}")
         request.state = WAITING
         self.waiting.append(request)
@@ -151,8 +155,12 @@ class Scheduler:
             if self.cache.add_request(req.rid) is None:
                 break
             if not self.cache.reserve(req.rid, n):
-                self.cache.free_request(req.rid)
-                break
+                if not self.running and not plan:
+                    # nothing else holds pages: a smaller first portion fits (add() made sure of that)
+                    n = self._largest_portion_that_fits(req, n)
+                if n == 0 or not self.cache.reserve(req.rid, n):
+                    self.cache.free_request(req.rid)
+                    break
             self.waiting.popleft()
             req.state = RUNNING
             self.running.append(req)

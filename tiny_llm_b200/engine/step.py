@@ -144,10 +144,6 @@ class ModelRunner:
         self._graph_seen = set()
         self._table_rows = {}
         self.graph_replays = 0
-        # small decode-only steps run as one kernel where every part of the model can take part in it
-        self._fused = None
-        self._fused_tried = False
-        self.fused_steps = 0
 
     # ---- metadata
     def _region(self, buf, name, n=None):
@@ -381,17 +377,6 @@ class ModelRunner:
             bucket *= 2
         return (batch.num_requests, bucket)
 
-    def _forward_decode(self, batch: StepBatch):
-        """A step that only decodes: the fused kernel if the model and the batch fit it, else the parts."""
-        if not self._fused_tried:
-            from .fused_decode import FusedDecode
-            self._fused_tried = True
-            self._fused = FusedDecode.build(self)
-        if self._fused is not None and self._fused.takes(batch):
-            self.fused_steps += 1
-            return self._fused.run(batch)
-        return self.model.forward(StepContext(self, batch))
-
     def _run(self, entries, batch: StepBatch):
         key = self._graph_key(entries, batch)
         if key is None:
@@ -402,12 +387,12 @@ class ModelRunner:
             if key not in self._graph_seen:
                 # first time: run eagerly (this also sizes the workspace and configures the kernels)
                 self._graph_seen.add(key)
-                return self._forward_decode(batch)
+                return self.model.forward(StepContext(self, batch))
             graph = torch.cuda.CUDAGraph()
             torch.cuda.synchronize(self.device)
             before = ops.launches
             with torch.cuda.graph(graph):
-                logits = self._forward_decode(batch)
+                logits = self.model.forward(StepContext(self, batch))
             kernels = ops.launches - before
             ops.launches = before
             # the graph's launches point into these buffers: keep them alive even if the workspace grows

@@ -171,7 +171,18 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, cos: Optional[torc
 
 EPI_BF16, EPI_F32, EPI_ADD_F32, EPI_SWIGLU, EPI_ATOMIC_F32 = 0, 1, 2, 3, 4
 EPI_CL_ADD_F32, EPI_CL_ROPE_KV, EPI_CL_SWIGLU, EPI_CL_BF16 = 5, 6, 7, 8   # K slices reduced inside a thread-block cluster
-SM_COUNT = 148
+_sm_count = {}
+
+
+def sm_count(device=None) -> int:
+    """Streaming multiprocessors of the device (cudaDevAttrMultiProcessorCount), read once per device:
+    the slice counts below are sized to fill them."""
+    index = torch.cuda.current_device() if device is None else (torch.device(device).index or 0)
+    if index not in _sm_count:
+        _sm_count[index] = torch.cuda.get_device_properties(index).multi_processor_count
+    return _sm_count[index]
+
+
 force_generic = False   # tests set this to compare the tensor-core kernels with the SIMT ones
 split_k = os.environ.get("TLLM_SPLIT_K", "1") != "0"   # slices of K at decode (a switch for measurements)
 # which products of few rows reduce their K slices inside a thread-block cluster instead of with float32
@@ -191,16 +202,27 @@ def status_word(device) -> torch.Tensor:
     return _status[key]
 
 
+_STATUS_CODES = ("1 = TMA producer, 2 = MMA issuer, 3 = epilogue of a matrix product; 7 = TMA producer, "
+                 "8 = MMA issuer, 9 = softmax of the tensor-core attention")
+
+
+def raise_status(device, code: int) -> None:
+    """Clears the device's status word and raises for the code that was read from it."""
+    key = torch.device(device).index or 0
+    if key in _status:
+        _status[key].zero_()
+    raise KernelError(f"a kernel on device {key} gave up waiting (code {code}: {_STATUS_CODES}); "
+                      f"the step's output is not valid and was dropped")
+
+
 def check_status() -> None:
-    """Reads the status words (a device synchronisation) and raises if a kernel gave up a wait."""
+    """Reads the status words (a device synchronisation) and raises if a kernel gave up a wait.
+    The generation path does not call this: there the word travels with the sampled ids
+    (`argmax` / `sample` with `status`)."""
     for key, t in _status.items():
         code = int(t.item())
         if code:
-            t.zero_()
-            raise KernelError(f"a kernel on device {key} gave up waiting (code {code}: 1 = TMA producer, "
-                              f"2 = MMA issuer, 3 = epilogue of a matrix product; 4 = weight producer, "
-                              f"5 = consumer, 6 = grid barrier of the fused decode step; 7 = TMA producer, 8 = MMA issuer, "
-                              f"9 = softmax of the tensor-core attention); its output is not valid")
+            raise_status(f"cuda:{key}", code)
 
 
 def _tc_ok(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
@@ -218,7 +240,7 @@ def _swap_splits(n: int, k: int, atomic_ok: bool) -> int:
         return 1
     row_tiles = -(-n // 128)
     k_blocks = -(-k // 64)
-    want = -(-SM_COUNT // row_tiles)
+    want = -(-sm_count() // row_tiles)
     return max(1, min(want, k_blocks // 4))
 
 
@@ -377,9 +399,10 @@ def _attention_splits(num_requests: int, max_q_len: int, group: int, num_kv_head
         per_slice = -(-tiles // pick)
         return -(-tiles // per_slice)
     ctas = num_requests * (-(-max_q_len * group // 64)) * num_kv_heads
-    if ctas >= SM_COUNT:
+    sms = sm_count()
+    if ctas >= sms:
         return 1
-    return max(1, min(-(-2 * SM_COUNT // ctas), max_kv_len // 256))
+    return max(1, min(-(-2 * sms // ctas), max_kv_len // 256))
 
 
 def paged_attention(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, k_cache: torch.Tensor,
@@ -435,49 +458,6 @@ def paged_attention(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_d
         ctypes.c_float(scale), int(window or 0), _code(qkv.dtype), _stream()))
 
 
-# ----------------------------------------------------------------------------- fused decode step
-
-
-class DecodeLayer(ctypes.Structure):
-    """One run-order entry of the fused decode step; the layout of `DecodeLayer` in csrc/decode_step.cu."""
-    _fields_ = [(n, ctypes.c_void_p) for n in ("w_qkv", "w_o", "w_gate_up", "w_down", "norm1", "norm2", "cos", "sin",
-                                               "kcache", "vcache", "block_table", "slot_mapping")] + \
-               [("eps1", ctypes.c_float), ("eps2", ctypes.c_float), ("scale_log2", ctypes.c_float),
-                ("window", ctypes.c_int)]
-
-
-class DecodeParams(ctypes.Structure):
-    """The layout of `DecodeParams` in csrc/decode_step.cu."""
-    _fields_ = [(n, ctypes.c_void_p) for n in ("layers", "tokens", "positions", "cu_q", "embed", "final_norm", "lm_head",
-                                               "resid", "q_buf", "attn_out", "ffn_act", "logits", "part_o", "part_ml",
-                                               "ssq_part", "sync_words", "status")] + \
-               [(n, ctypes.c_int) for n in ("n_layers", "m", "hidden", "nq", "nkv", "inter", "gu_block", "vocab",
-                                            "page_size", "max_blocks", "splits", "stages", "act_ld")] + \
-               [("final_eps", ctypes.c_float)]
-
-
-def decode_step_library(head_dim: int):
-    if head_dim % 16 or not 16 <= head_dim <= 256:
-        raise KernelError(f"decode_step: head size {head_dim} is not a multiple of 16 up to 256")
-    flags = (f"-DTLLM_HEAD_DIM={head_dim}",)
-    timed_cta = os.environ.get("TLLM_STEP_TIMING")   # a switch for measurements: 1 + the CTA whose phases are timed
-    if timed_cta:
-        flags += (f"-DTLLM_STEP_TIMING={int(timed_cta)}",)
-    lib = build.load_library("decode_step", flags=flags)
-    if lib.tllm_decode_step_layer_bytes() != ctypes.sizeof(DecodeLayer) or \
-            lib.tllm_decode_step_params_bytes() != ctypes.sizeof(DecodeParams):
-        raise KernelError("decode_step: the Python and CUDA sides disagree about the parameter layout")
-    return lib
-
-
-def decode_step_timing(head_dim: int):
-    """Cycles per phase kind that the timed CTA spent since the last call (needs TLLM_STEP_TIMING):
-    norm load, qkv, grid barriers, attention, combine, plain load, o, gate/up, down, lm head."""
-    out = (ctypes.c_ulonglong * 16)()
-    decode_step_library(head_dim).tllm_decode_step_timing(out)
-    return list(out)
-
-
 def attention_tc_timing() -> Optional[dict]:
     """Cycles that the roles of the prompt-attention kernel's first CTA spent per phase since the last call, or
     None if the kernel was not built with TLLM_NVCC_FLAGS_ATTENTION_TC=-DTLLM_ATT_TIMING=1."""
@@ -493,51 +473,41 @@ def attention_tc_timing() -> Optional[dict]:
     return {n: int(v) for n, v in zip(names, out) if n != "(unused)"}
 
 
-def decode_step_refusal(head_dim: int, params: DecodeParams) -> Optional[str]:
-    """None if the fused kernel takes these sizes, else the reason it does not."""
-    lib = decode_step_library(head_dim)
-    if lib.tllm_decode_step(ctypes.byref(params), 0, None) != 0:
-        return lib.tllm_last_error().decode()
-    return None
-
-
-def decode_step(head_dim: int, params: DecodeParams) -> None:
-    """One whole decode step (every layer, final norm, LM head) of at most eight one-token requests
-    as one persistent kernel on the current stream."""
-    lib = decode_step_library(head_dim)
-    _check(lib, lib.tllm_decode_step(ctypes.byref(params), 1, _stream()))
-
-
 # ----------------------------------------------------------------------------- sampling
 
 
-def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
-    _need_cuda(logits, out)
+def argmax(logits: torch.Tensor, out: torch.Tensor, status: Optional[torch.Tensor] = None) -> None:
+    """out[i] = first maximum of row i.  `status`: the device's status word; `out` then holds n + 1
+    ints and out[n] receives the word, so that it travels to the host with the ids."""
+    _need_cuda(logits, out, status)
     _i32(out, "out")
+    _i32(status, "status")
     n, v = logits.shape
-    if logits.dtype != torch.float32 or not logits.is_contiguous() or out.numel() != n:
-        raise KernelError("argmax: logits must be contiguous float32 [n, V] and out int32 [n]")
+    if logits.dtype != torch.float32 or not logits.is_contiguous() or out.numel() != n + (status is not None):
+        raise KernelError("argmax: logits must be contiguous float32 [n, V] and out int32 [n] (n + 1 with a status word)")
     lib = build.load_library("sampling")
-    _check(lib, lib.tllm_argmax(_ptr(logits), _ptr(out), n, v, _stream()))
+    _check(lib, lib.tllm_argmax(_ptr(logits), _ptr(out), n, v, _ptr(status), _stream()))
 
 
 def sample(logits: torch.Tensor, work: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
-           top_p: torch.Tensor, seeds: torch.Tensor, counters: torch.Tensor, out: torch.Tensor) -> None:
+           top_p: torch.Tensor, seeds: torch.Tensor, counters: torch.Tensor, out: torch.Tensor,
+           status: Optional[torch.Tensor] = None) -> None:
     """Temperature -> top-k -> top-p -> multinomial per row; rows with temperature <= 0 are greedy.
     `work` is float32 scratch of at least n*V elements; seeds and counters are int64 (read as
-    unsigned 64-bit)."""
-    _need_cuda(logits, work, temperature, top_k, top_p, seeds, counters, out)
+    unsigned 64-bit).  `status` as for argmax."""
+    _need_cuda(logits, work, temperature, top_k, top_p, seeds, counters, out, status)
     _i32(top_k, "top_k")
     _i32(out, "out")
+    _i32(status, "status")
     n, v = logits.shape
     if logits.dtype != torch.float32 or not logits.is_contiguous() or work.dtype != torch.float32 or \
             work.numel() < n * v or temperature.dtype != torch.float32 or top_p.dtype != torch.float32 or \
-            seeds.dtype != torch.int64 or counters.dtype != torch.int64 or \
-            any(x.numel() != n for x in (temperature, top_k, top_p, seeds, counters, out)):
+            seeds.dtype != torch.int64 or counters.dtype != torch.int64 or out.numel() != n + (status is not None) or \
+            any(x.numel() != n for x in (temperature, top_k, top_p, seeds, counters)):
         raise KernelError("sample: shapes or dtypes do not fit")
     lib = build.load_library("sampling")
     _check(lib, lib.tllm_sample(_ptr(logits), _ptr(work), n, v, _ptr(temperature), _ptr(top_k), _ptr(top_p),
-                                _ptr(seeds), _ptr(counters), _ptr(out), _stream()))
+                                _ptr(seeds), _ptr(counters), _ptr(out), _ptr(status), _stream()))
 
 
 ALL_LIBRARIES = ("elementwise", "linear_generic", "linear_tc", "attention_generic", "sampling")
@@ -549,8 +519,7 @@ ATTENTION_HEAD_DIMS = (16, 32, 48, 64, 128)   # head sizes `build_all` compiles 
 def build_all(verbose: bool = True):
     """Compiles every library (what `__graft_entry__.build()` calls); returns their paths."""
     paths = [build.compile_library(n, verbose=verbose) for n in ALL_LIBRARIES]
-    for name in ("attention_mma", "decode_step"):
-        paths += [build.compile_library(name, flags=(f"-DTLLM_HEAD_DIM={hd}",), verbose=verbose)
-                  for hd in ATTENTION_HEAD_DIMS]
+    paths += [build.compile_library("attention_mma", flags=(f"-DTLLM_HEAD_DIM={hd}",), verbose=verbose)
+              for hd in ATTENTION_HEAD_DIMS]
     paths.append(build.compile_library("attention_tc", flags=("-DTLLM_HEAD_DIM=64",), verbose=verbose))
     return paths

@@ -23,7 +23,7 @@ ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-shared", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 HEADERS = ["common.cuh"]
 EXTRA_HEADERS = {"sampling": ["sampling_noalloc.h"], "attention_mma": ["attention_tiles.cuh"],
-                 "decode_step": ["attention_tiles.cuh"], "linear_tc": ["tc_common.cuh"],
+                 "linear_tc": ["tc_common.cuh"],
                  "attention_tc": ["tc_common.cuh"]}   # per-source headers that enter the hash
 
 _loaded: Dict[str, ctypes.CDLL] = {}

@@ -61,16 +61,6 @@ class GQAttention:
         self.w_o = weights[prefix + "o_proj.weight"]
         self.position.prepare(self.w_o.device)
 
-    def fused_decode(self):
-        """What the fused decode step needs to run this part inside its own kernel; None when it cannot
-        (a call that reads another's cache, a position encoding the kernel does not rotate itself)."""
-        pos = self.position
-        if self.shares_cache or not getattr(pos, "fused", False) or pos.rot_dim not in (0, self.head_dim):
-            return None
-        return {"kind": "gqa_attention", "w_qkv": self.w_qkv, "w_o": self.w_o, "hidden_size": self.hidden_size,
-                "num_heads": self.num_heads, "num_kv_heads": self.num_kv_heads, "head_dim": self.head_dim,
-                "window": self.window, "scale": self.scale, "cos": pos.cos, "sin": pos.sin}
-
     def forward(self, ctx, h, resid, cache) -> None:
         t = h.shape[0]
         qkv = ctx.workspace.get("qkv", (t, self.qkv_dim), ctx.dtype)

@@ -51,11 +51,6 @@ class SwiGLU:
                                             weights[prefix + "up_proj.weight"], self.block)
         self.w_down = weights[prefix + "down_proj.weight"]
 
-    def fused_decode(self):
-        """What the fused decode step needs to run this part inside its own kernel."""
-        return {"kind": "swiglu", "w_gate_up": self.w_gate_up, "w_down": self.w_down, "block": self.block,
-                "hidden_size": self.hidden_size, "intermediate_size": self.intermediate_size}
-
     def forward(self, ctx, h, resid) -> None:
         t = h.shape[0]
         act = ctx.workspace.get("ffn_act", (t, self.intermediate_size), ctx.dtype)

@@ -21,10 +21,6 @@ class RMSNorm:
     def load(self, prefix: str, weights) -> None:
         self.weight = weights[prefix + ".weight"]
 
-    def fused_decode(self):
-        """What the fused decode step needs to run this part inside its own kernel."""
-        return {"kind": "rms_norm", "weight": self.weight, "eps": self.eps, "size": self.size}
-
     def forward(self, ctx, x, rows=None):
         n = x.shape[0] if rows is None else rows.shape[0]
         out = ctx.workspace.get("norm_out", (n, self.size), ctx.dtype)

@@ -43,8 +43,10 @@ class Sampler:
         self._host = [torch.zeros(self._words, dtype=torch.int32, pin_memory=pin) for _ in range(self.RING)]
         self._host_free = [None] * self.RING      # event: the copy that last read this block has run
         self._dev = torch.zeros(self._words, dtype=torch.int32, device=self.device)
-        self._out = torch.zeros(self.max_rows, dtype=torch.int32, device=self.device)
-        self._out_host = [torch.zeros(self.max_rows, dtype=torch.int32, pin_memory=pin) for _ in range(self.RING)]
+        # the chosen ids, and behind them the status word of the step's kernels (see collect)
+        self._out = torch.zeros(self.max_rows + 1, dtype=torch.int32, device=self.device)
+        self._out_host = [torch.zeros(self.max_rows + 1, dtype=torch.int32, pin_memory=pin) for _ in range(self.RING)]
+        self._status = ops.status_word(self.device) if pin else None
         self._next = 0
         self._work = None
 
@@ -61,9 +63,9 @@ class Sampler:
             raise ValueError(f"{n} rows exceed the sampler's {self.max_rows}")
         slot = self._next
         self._next = (slot + 1) % self.RING
-        out = self._out[:n]
+        out = self._out[:n + 1]
         if all(not p.do_sample for p in params):
-            ops.argmax(logits, out)
+            ops.argmax(logits, out, self._status)
         else:
             if self._host_free[slot] is not None:
                 self._host_free[slot].synchronize()
@@ -82,19 +84,25 @@ class Sampler:
             if self._work is None or self._work.numel() < n * self.vocab_size:
                 self._work = torch.empty(max(n, 8) * self.vocab_size, dtype=torch.float32, device=self.device)
             dt, dpp, dk, ds, dc = self._views(self._dev, n)
-            ops.sample(logits, self._work, dt, dk, dpp, ds, dc, out)
-        self._out_host[slot][:n].copy_(out, non_blocking=True)
+            ops.sample(logits, self._work, dt, dk, dpp, ds, dc, out, self._status)
+        self._out_host[slot][:n + 1].copy_(out, non_blocking=True)
         event = None
         if self.device.type == "cuda":
             event = torch.cuda.Event()
             event.record()
-        return SampleTicket(n, slot, event, out)
+        return SampleTicket(n, slot, event, out[:n])
 
     def collect(self, ticket: SampleTicket) -> List[int]:
-        """Waits for a launched call's ids and returns them."""
+        """Waits for a launched call's ids and returns them.  The status word of the step's kernels
+        came with them in the same copy: if a kernel gave up one of its bounded waits, the ids were
+        drawn from logits that are not valid, and this raises instead of returning them (the
+        reference throws on every failed CUDA call, tiny_llm/common/cuda_checks.hpp:8-20)."""
         if ticket.event is not None:
             ticket.event.synchronize()
-        return self._out_host[ticket.slot][:ticket.n].tolist()
+        row = self._out_host[ticket.slot][:ticket.n + 1].tolist()
+        if row[ticket.n]:
+            ops.raise_status(self.device, row[ticket.n])
+        return row[:ticket.n]
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], counters: Sequence[int]) -> List[int]:
         """launch + collect."""

@@ -5,9 +5,11 @@ and stops at the first failure (tiny_llm/runtime/cuda/cuda_runtime.cpp:353-361,
 tiny_llm/weight_managers/safetensors/weight_manager.cpp:87-93)."""
 from __future__ import annotations
 
+import fnmatch
+import json
 import os
 from dataclasses import dataclass
-from typing import Dict, Mapping, Tuple, Union
+from typing import Dict, Mapping, Optional, Sequence, Tuple, Union
 
 import torch
 
@@ -23,9 +25,12 @@ AS_STORED = "as_stored"  # a tensor that is stored in 32-bit stays 32-bit; 16-bi
 
 @dataclass(frozen=True)
 class WeightSpec:
+    """`alias_of`: the tensor to stand in when `name` is not stored (an output matrix that a
+    checkpoint leaves out because it equals the embedding table); both names then share one tensor."""
     name: str
     shape: Tuple[int, ...]
     keep: str = COMPUTE
+    alias_of: Optional[str] = None
 
 
 def _convert(t: torch.Tensor, spec: WeightSpec, dtype: torch.dtype) -> torch.Tensor:
@@ -61,19 +66,75 @@ class _DictSource:
         pass
 
 
+INDEX_NAME = "model.safetensors.index.json"
+
+
+class ShardedSafetensors:
+    """A checkpoint cut into several safetensors files with an index {"weight_map": {tensor name: file}}
+    beside them (the layout large checkpoints are published in; the reference reads one file only,
+    tiny_llm/pipeline/pipeline.cpp:67-68).  Shards are opened when a tensor of theirs is first asked for."""
+
+    def __init__(self, folder: str):
+        self.folder = folder
+        path = os.path.join(folder, INDEX_NAME)
+        try:
+            with open(path) as f:
+                index = json.load(f)
+            self._file_of: Dict[str, str] = dict(index["weight_map"])
+        except (OSError, ValueError, KeyError, TypeError) as e:
+            raise WeightError(f"{path}: not a readable shard index ({e})") from None
+        self._shards: Dict[str, SafetensorsFile] = {}
+        for name, fname in self._file_of.items():    # every shard is opened once here: the check needs all shapes
+            shard = self._shard(fname)
+            if name not in shard:
+                raise WeightError(f"{path}: tensor {name!r} is not in {fname} as the index says")
+
+    def _shard(self, fname: str) -> SafetensorsFile:
+        if fname not in self._shards:
+            if os.path.basename(fname) != fname:
+                raise WeightError(f"{self.folder}: the shard index names a file outside the folder: {fname!r}")
+            self._shards[fname] = SafetensorsFile(os.path.join(self.folder, fname))
+        return self._shards[fname]
+
+    def keys(self):
+        return self._file_of.keys()
+
+    def __contains__(self, k):
+        return k in self._file_of
+
+    def shape(self, k):
+        return self._shard(self._file_of[k]).shape(k)
+
+    def dtype(self, k):
+        return self._shard(self._file_of[k]).dtype(k)
+
+    def get(self, k):
+        return self._shard(self._file_of[k]).get(k)
+
+    def close(self):
+        for s in self._shards.values():
+            s.close()
+
+
 def open_source(source: Union[str, Mapping[str, torch.Tensor]]):
-    """A model folder (its model.safetensors), a .safetensors file, or a dict of tensors."""
+    """A model folder (its model.safetensors, or its shards by model.safetensors.index.json), a
+    .safetensors file, or a dict of tensors."""
     if isinstance(source, (str, os.PathLike)):
         path = os.fspath(source)
         if os.path.isdir(path):
-            path = os.path.join(path, "model.safetensors")
+            single = os.path.join(path, "model.safetensors")
+            if not os.path.isfile(single) and os.path.isfile(os.path.join(path, INDEX_NAME)):
+                return ShardedSafetensors(path)
+            path = single
         return SafetensorsFile(path)
     return _DictSource(source)
 
 
-def check_against(specs: Mapping[str, WeightSpec], src) -> None:
-    missing = sorted(n for n in specs if n not in src)
-    unexpected = sorted(n for n in src.keys() if n not in specs)
+def check_against(specs: Mapping[str, WeightSpec], src, ignore: Sequence[str] = ()) -> None:
+    """`ignore`: name patterns (fnmatch) of stored tensors that the model has no use for and that are
+    known to be harmless; every other tensor the model does not want is an error."""
+    missing = sorted(n for n, s in specs.items() if n not in src and not (s.alias_of and s.alias_of in src))
+    unexpected = sorted(n for n in src.keys() if n not in specs and not any(fnmatch.fnmatchcase(n, p) for p in ignore))
     wrong = []
     for n, s in specs.items():
         if n not in src:
@@ -95,14 +156,23 @@ def check_against(specs: Mapping[str, WeightSpec], src) -> None:
         raise WeightError("\n".join(lines))
 
 
-def load_state(specs: Mapping[str, WeightSpec], source, dtype: torch.dtype, device) -> Dict[str, torch.Tensor]:
-    """Checks the whole set, then converts and moves tensor by tensor."""
+def load_state(specs: Mapping[str, WeightSpec], source, dtype: torch.dtype, device,
+               ignore: Sequence[str] = ()) -> Dict[str, torch.Tensor]:
+    """Checks the whole set, then converts and moves tensor by tensor.  A tensor that is not stored
+    but has an `alias_of` that is shares that tensor (no second copy on the device)."""
     src = open_source(source)
     try:
-        check_against(specs, src)
+        check_against(specs, src, ignore)
         out = {}
         for n, s in specs.items():
-            out[n] = _convert(src.get(n), s, dtype).to(device).contiguous()
+            if n in src:
+                out[n] = _convert(src.get(n), s, dtype).to(device).contiguous()
+        for n, s in specs.items():
+            if n not in out:
+                other = specs.get(s.alias_of)
+                if other is None or tuple(other.shape) != tuple(s.shape) or other.keep != s.keep:
+                    raise WeightError(f"{n} is not stored and its stand-in {s.alias_of} has another shape or kind")
+                out[n] = out[s.alias_of]
         return out
     finally:
         src.close()
