@@ -156,10 +156,12 @@ def attention_block(h, w: Dict[str, torch.Tensor], prefix: str, cfg: dict, cos, 
 
 
 def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], quant: Quant = no_quant,
-            dtype=torch.float32) -> torch.Tensor:
+            dtype=torch.float32, rows: Optional[List[int]] = None) -> torch.Tensor:
     """Logits [T, V] of one whole sequence starting at position 0: embedding, then per layer
     norm -> attention -> residual -> norm -> SwiGLU -> residual, final norm, LM head
-    (tiny_llm/parser/llama_parser.cpp:164-276).  The residual stream is never rounded."""
+    (tiny_llm/parser/llama_parser.cpp:164-276).  The residual stream is never rounded.
+    `rows`: the positions whose logits are wanted ([len(rows), V]; the reference itself takes the
+    last row only, tiny_llm/ops/cuda/gemm_q1_helper.cu:99-124); None: all."""
     w = {k: v.to(dtype) for k, v in w.items()}
     toks = torch.tensor(tokens, dtype=torch.long)
     t = toks.numel()
@@ -176,6 +178,8 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], quant: Qua
         h = quant(rms_norm(x, w[p + "post_attention_layernorm.weight"], eps))
         x = x + swiglu_mlp(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
                            w[p + "mlp.down_proj.weight"], quant)
+    if rows is not None:
+        x = x[torch.tensor(rows, dtype=torch.long)]
     x = quant(rms_norm(x, w["model.norm.weight"], eps))
     head = w["lm_head.weight"] if "lm_head.weight" in w else w["model.embed_tokens.weight"]
     return linear(x, head)

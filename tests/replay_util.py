@@ -208,5 +208,15 @@ def compare(got, ref, prefix, dtype, what, ref32=None):
                                  f"{int(bad[0])} of {r.shape[0]} (max |diff| {float(diff.max()):.3e}, tolerance {tol:.3e}; "
                                  f"wrong positions: {bad.tolist()[:20]})")
         worst = max(worst, float(diff.max()) / tol)
-    print(f"[margin] {what} {dtype}: worst |diff| / tolerance = {worst:.3f}")
+    record_margin(what, dtype, worst)
     return worst
+
+
+def record_margin(what, dtype, worst, tolerance_kind="|diff| / tolerance"):
+    """Prints how much of its tolerance a comparison used and, when TLLM_MARGIN_FILE names a file,
+    appends the figure there as a JSON line, so that a run leaves a record of its margins."""
+    print(f"[margin] {what} {dtype}: worst {tolerance_kind} = {worst:.3g}")
+    path = os.environ.get("TLLM_MARGIN_FILE")
+    if path:
+        with open(path, "a") as f:
+            f.write(json.dumps({"what": what, "dtype": dtype, "kind": tolerance_kind, "worst": float(f"{worst:.4g}")}) + "\n")

@@ -312,6 +312,106 @@ def test_paged_attention_on_tcgen05(ops, nq, nkv, page):
     assert float(p[450]) > 0.9
 
 
+LENS8 = [2048, 2047, 1000, 700, 65, 1, 1999, 513]
+
+
+def _lens64():
+    g = torch.Generator().manual_seed(64)
+    return [2048, 2047, 1, 64, 65] + torch.randint(1, 2049, (59,), generator=g).tolist()
+
+
+@pytest.mark.parametrize("bucket", [False, True])
+@pytest.mark.parametrize("hd,nq,nkv,q_len,lens,window,page", [
+    (64, 32, 4, 1, [2048], None, 16),          # batch 1 at the longest context: the most key slices
+    (64, 32, 4, 1, LENS8, None, 16),           # the benchmark's shape, contexts from 1 to 2,048 in one batch
+    (64, 8, 1, 2, LENS8, 37, 16),              # two tokens x a group of eight = 16 rows, a window
+    (128, 8, 8, 1, LENS8, None, 16),           # one query head per key/value head, head size 128
+    (128, 32, 8, 1, [2048, 1000, 2047], None, 32),
+    (128, 4, 1, 4, LENS8, None, 8),            # four tokens x a group of four
+    (64, 4, 2, 1, _lens64(), None, 16),        # batch 64
+    (128, 2, 1, 1, _lens64(), 500, 16),
+], ids=["b1", "b8", "b8-q2-window", "b8-mha-hd128", "b3-hd128-page32", "b8-q4-hd128", "b64", "b64-hd128-window"])
+def test_decode_attention_over_long_contexts(ops, hd, nq, nkv, q_len, lens, window, page, bucket):
+    """Every request brings q_len tokens (q_len x group <= 16), so the decode kernel and the merge of its key
+    slices run, with the slice count the engine itself picks for these sizes; `bucket` hands the kernel
+    the power-of-two bucket of the longest context, as a replayed graph does, so that short requests
+    have empty slices.  Unwritten slots of the pages are NaN; one key far back carries a query."""
+    from tiny_llm_b200.engine import Workspace
+    dtype = "bfloat16"
+    n_req = len(lens)
+    lens = [max(l, q_len) for l in lens]
+    group = nq // nkv
+    assert q_len * group <= 16
+    table, k_cache, v_cache, ks, vs = paged_setup(dtype, n_req, lens, nkv, hd, page, seed=hd + nq + n_req)
+    g = torch.Generator().manual_seed(11)
+    t = n_req * q_len
+    qkv = torch.randn(t, (nq + 2 * nkv) * hd, generator=g).to(DT[dtype])
+    far = 3 if lens[0] > 3 else 0
+    if window is None:   # request 0's last query, first head, and its key 3 are scaled so that this score stands out
+        row = q_len - 1
+        qkv[row, :hd] *= 6.0
+        ks[0][far, 0] = (qkv[row, :hd] / qkv[row, :hd].float().norm() * 8.0).to(DT[dtype])
+        k_cache[int(table[0, far // page]), 0, far % page] = ks[0][far, 0]
+    tok_req = torch.arange(n_req, dtype=torch.int32).repeat_interleave(q_len)
+    pos = torch.cat([torch.arange(l - q_len, l, dtype=torch.int32) for l in lens])
+    cu = torch.arange(0, t + 1, q_len, dtype=torch.int32)
+    starts = torch.tensor([l - q_len for l in lens], dtype=torch.int32)
+    max_kv = max(lens)
+    if bucket:
+        max_kv = 256
+        while max_kv < max(lens):
+            max_kv *= 2
+        max_kv *= 2 if max_kv == max(lens) else 1     # a bucket that is strictly larger than every context
+    batch = types.SimpleNamespace(token_request=tok_req.to(DEV), positions=pos.to(DEV), cu_q=cu.to(DEV),
+                                  q_start=starts.to(DEV), num_requests=n_req, max_q_len=q_len, max_kv_len=max_kv)
+    splits = ops._attention_splits(n_req, q_len, group, nkv, max_kv)
+    assert splits > 1 or max(lens) < 128
+    out = torch.full((t, nq * hd), float("nan"), dtype=DT[dtype], device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    ops.paged_attention(qkv.to(DEV), nq, nkv, hd, k_cache.to(DEV), v_cache.to(DEV), table.to(DEV), batch, out,
+                        scale, window, Workspace(DEV))
+    out = out.float().cpu()
+    assert not torch.isnan(out).any()
+    for r, l in enumerate(lens):
+        q = qkv[r * q_len: (r + 1) * q_len, : nq * hd].float().view(q_len, nq, hd)
+        ref = pl.attention(q, ks[r].float(), vs[r].float(), pos[r * q_len: (r + 1) * q_len], window=window,
+                           quant=pl.bf16_quant).reshape(q_len, nq * hd)
+        d = float((out[r * q_len: (r + 1) * q_len] - ref).abs().max())
+        assert d <= tol(dtype, max(1.0, float(ref.abs().max()))), (r, l, d, splits)
+    if window is None:
+        p = torch.softmax((qkv[q_len - 1, :hd].float() * scale) @ ks[0][:lens[0], 0].float().t(), 0)
+        assert float(p[far]) > 0.9
+
+
+def test_products_at_the_sizes_of_a_2048_token_prompt(ops):
+    """The persistent 128 x 256 kernel over several rounds of tiles at the TinyLlama layer sizes: gate/up
+    with SiLU * up in its epilogue (2,048 x 11,264 x 2,048) and the down projection adding into the
+    32-bit residual (2,048 x 2,048 x 5,632), each against a 64-bit product on the host."""
+    from tiny_llm_b200.engine import Workspace
+    from tiny_llm_b200.parts import interleave_gate_up
+    g = torch.Generator().manual_seed(21)
+    m, h, inter = 2048, 2048, 5632
+    a = torch.randn(m, h, generator=g).to(torch.bfloat16)
+    wg = (torch.randn(inter, h, generator=g) / math.sqrt(h)).to(torch.bfloat16)
+    wu = (torch.randn(inter, h, generator=g) / math.sqrt(h)).to(torch.bfloat16)
+    act = torch.full((m, inter), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.linear_swiglu(a.to(DEV), interleave_gate_up(wg, wu, 128).to(DEV), act, 128, Workspace(DEV))
+    ops.check_status()
+    ref = pl.silu(pl.linear(a.float(), wg.float())) * pl.linear(a.float(), wu.float())
+    d = (act.float().cpu() - ref).abs()
+    assert float(d.max()) <= tol("bfloat16", max(1.0, float(ref.abs().max()))), float(d.max())
+    # down projection: adds into a residual that already holds values
+    wd = (torch.randn(h, inter, generator=g) / math.sqrt(inter)).to(torch.bfloat16)
+    z = pl.bf16_quant(ref).to(torch.bfloat16)
+    resid0 = torch.randn(m, h, generator=g)
+    resid = resid0.to(DEV)
+    ops.linear(z.to(DEV), wd.to(DEV), resid, accumulate=True)
+    ops.check_status()
+    ref2 = (resid0.double() + pl.linear(z.double(), wd.double())).float()
+    d2 = (resid.cpu() - ref2).abs()
+    assert float(d2.max()) <= 5e-4 * max(1.0, float(ref2.abs().max())), float(d2.max())   # 32-bit sums of exact bfloat16 products
+
+
 def test_attention_refuses_sizes_it_is_not_built_for(ops):
     from tiny_llm_b200.ops import KernelError
     z = torch.zeros(2, dtype=torch.int32, device=DEV)
