@@ -10,13 +10,19 @@ A 2,048-token prompt runs whole, in portions of 512/300/2/..., and with its last
 (contexts 2,016 to 2,047: decode attention over many key slices, replayed CUDA graphs); at the
 TinyLlama shape eight requests live at contexts above 1,000 with portions of newcomers beside their
 decoded tokens and so few pages that they are used again.  Logits are compared at chosen places (the
-first tokens, page and portion edges, the last 32) with the plain implementation: 32-bit within 1e-4
-and bit for bit equal between the cuts, bfloat16 within the rounding yardstick of replay_util.
+first tokens, page and portion edges, the last 32) with the plain implementation.  bfloat16 is held to
+the rounding yardstick of replay_util.  The 32-bit path is compared with the plain implementation run in
+64-bit and held to 1e-4, or to four times the error that the plain implementation's own 32-bit run has
+against its 64-bit run where that is larger: with attention as peaked as here the 32-bit plain run is
+itself up to 1.4e-4 away from the 64-bit one, and the engine, which sums every product in ascending k
+where the CPU library sums in blocks, was measured at 2.2 to 2.5 times the plain run's error at three
+degrees of sharpening.  Between the cuts the 32-bit logits are equal bit for bit.
 
 The query and key projections are scaled up so that attention is peaked: a wrong or missing key then
 moves the logits far beyond rounding (with N(0, 0.02) alone attention over 2,000 keys is nearly flat
-and a wrong page could hide); one test puts a wrong page into the cache on purpose and checks that the
-comparison sees it."""
+and a wrong page could hide); one test puts a wrong page into the cache on purpose (another page's keys
+and values in every layer, as a wrong block-table entry would give) and checks that both comparisons
+see it."""
 import pytest
 import torch
 
@@ -64,12 +70,18 @@ def shape(request):
     specs, state = make_state(cfg, seed)
     toks = ru.make_requests(cfg.vocab_size, [PROMPT], seed)["r0"]
     pcfg = cfg.to_dict()
+    ref64 = pl.forward(pcfg, state, toks, rows=WANT, dtype=torch.float64).float()
     ref32 = pl.forward(pcfg, state, toks, rows=WANT)
     wq = {k: (v if v.dim() == 1 else v.to(torch.bfloat16).float()) for k, v in state.items()}
     ref16 = pl.forward(pcfg, wq, toks, quant=pl.bf16_quant, rows=WANT)
     del wq
     return dict(name=f"{request.param} ({cfg.num_hidden_layers} of {layers_of_model} layers)", cfg=cfg, specs=specs,
-                state=state, toks=toks, ref32=ref32, ref16=ref16)
+                state=state, toks=toks, ref64=ref64, ref32=ref32, ref16=ref16, tol32=tolerance32(ref32, ref64))
+
+
+def tolerance32(ref32, ref64):
+    """1e-4, or four times the plain implementation's own 32-bit error where that is larger."""
+    return max(1e-4, 4.0 * float((ref32 - ref64).abs().max()))
 
 
 def build_runner(cfg, specs, state, dtype, max_tokens, max_requests=8, max_step=2048):
@@ -115,12 +127,13 @@ def test_float32_at_real_sizes_matches_plain_and_cuts_agree_bitwise(shape):
     ops.check_status()
     worst = 0.0
     for how, g in got.items():
-        assert g.shape == shape["ref32"].shape
+        assert g.shape == shape["ref64"].shape
         assert not torch.isnan(g).any(), how
-        d = float((g - shape["ref32"]).abs().max())
-        assert d <= 1e-4, (shape["name"], how, d)
+        d = float((g - shape["ref64"]).abs().max())
+        assert d <= shape["tol32"], (shape["name"], how, d, shape["tol32"])
         worst = max(worst, d)
-    ru.record_margin(f"{shape['name']} whole/portions/tail", "float32", worst, "|diff| (limit 1e-4)")
+    ru.record_margin(f"{shape['name']} whole/portions/tail (limit {shape['tol32']:.2e}, plain 32-bit run itself "
+                     f"{float((shape['ref32'] - shape['ref64']).abs().max()):.2e})", "float32", worst, "|diff| to the 64-bit plain run")
     assert torch.equal(got["portions"], got["whole"]) and torch.equal(got["tail"], got["whole"])
 
 
@@ -134,28 +147,34 @@ def test_bfloat16_at_real_sizes_within_the_rounding_yardstick(shape):
         ru.compare({"x" + "r": g}, {"r": shape["ref16"]}, "x", "bfloat16", f"{shape['name']} {how}", {"r": shape["ref32"]})
 
 
-def test_a_wrong_page_in_the_cache_is_seen_by_the_bfloat16_yardstick(shape):
-    """After the prompt, one page of keys of one layer is overwritten with another page's keys; the
-    logits of the tokens decoded after that must fall outside the tolerance.  (If they did not, the
-    comparison above could not tell a wrong page from rounding.)"""
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_wrong_page_in_the_cache_is_seen_by_the_comparison(shape, dtype):
+    """After the prompt, one page of the request (keys 1,120 to 1,135 of 2,016) is overwritten in every
+    layer with another of its pages, keys and values, which is what a wrong block-table entry gives; the
+    logits of the 32 tokens decoded after that must fall outside the tolerance.  (If they did not, the
+    comparisons above could not tell a wrong page from rounding.)"""
+    from tiny_llm_b200.engine import StepEntry
     cfg, toks = shape["cfg"], shape["toks"]
-    runner = build_runner(cfg, shape["specs"], shape["state"], "bfloat16", max_tokens=PROMPT + 64)
+    runner = build_runner(cfg, shape["specs"], shape["state"], dtype, max_tokens=PROMPT + 64)
     head = PROMPT - TAIL
     runner.cache.add_request("x")
-    from tiny_llm_b200.engine import StepEntry
     runner.step([StepEntry("x", toks[:head], [])])
     table = runner.cache.block_table(0, "x")
     kv = runner.cache.groups[0].kv
-    layer = cfg.num_hidden_layers - 1
-    kv[layer, 0, table[70]] = kv[layer, 0, table[20]]          # keys 1,120..1,135 become keys 320..335
-    rows = []
-    for i in range(head, PROMPT):
-        rows.append(runner.step([StepEntry("x", [toks[i]], [0])]).cpu().clone())
+    kv[:, :, table[70]] = kv[:, :, table[20]]
+    rows = [runner.step([StepEntry("x", [toks[i]], [0])]).cpu().clone() for i in range(head, PROMPT)]
     runner.cache.free_request("x")
     got = torch.cat(rows)
     tail_rows = [WANT.index(p) for p in range(head, PROMPT)]
-    with pytest.raises(AssertionError, match="differs from the plain implementation"):
-        ru.compare({"xr": got}, {"r": shape["ref16"][tail_rows]}, "x", "bfloat16", "wrong page", {"r": shape["ref32"][tail_rows]})
+    if dtype == "float32":
+        d = float((got - shape["ref64"][tail_rows]).abs().max())
+        ru.record_margin(f"{shape['name']} with a wrong page", dtype, d / shape["tol32"], "|diff| / tolerance (must exceed 1)")
+        assert d > shape["tol32"], (d, shape["tol32"])
+    else:
+        r16, r32 = shape["ref16"][tail_rows], shape["ref32"][tail_rows]
+        ratio = float((got - r16).abs().max()) / float((r16 - r32).abs().max())
+        ru.record_margin(f"{shape['name']} with a wrong page", dtype, ratio, "|diff| / tolerance (must exceed 1)")
+        assert ratio > 1.0, ratio
 
 
 # ----------------------------------------------------------------------------- eight live requests
@@ -203,14 +222,15 @@ def crowd():
     pcfg = cfg.to_dict()
     wq = {k: (v if v.dim() == 1 else v.to(torch.bfloat16).float()) for k, v in state.items()}
     rows = list(range(CROWD_ROW0, 1216))
+    ref64 = {k: pl.forward(pcfg, state, t, rows=rows, dtype=torch.float64).float() for k, t in seqs.items()}
     ref32 = {k: pl.forward(pcfg, state, t, rows=rows) for k, t in seqs.items()}
     ref16 = {k: pl.forward(pcfg, wq, t, quant=pl.bf16_quant, rows=rows) for k, t in seqs.items()}
-    return cfg, specs, state, reqs, lengths, ref32, ref16
+    return cfg, specs, state, reqs, lengths, ref64, ref32, ref16
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_eight_live_requests_beyond_1000_tokens_with_pages_used_again(crowd, dtype):
-    cfg, specs, state, reqs, lengths, ref32, ref16 = crowd
+    cfg, specs, state, reqs, lengths, ref64, ref32, ref16 = crowd
     decode = 40
     steps = mixed_trace(reqs, decode=decode)
     need = ru.tokens_needed(steps)
@@ -230,9 +250,11 @@ def test_eight_live_requests_beyond_1000_tokens_with_pages_used_again(crowd, dty
         g = got[rid]
         assert g.shape == r32.shape and not torch.isnan(g).any(), rid
         if dtype == "float32":
-            d = float((g - r32).abs().max())
-            assert d <= 1e-4, (rid, d)
-            worst = max(worst, d)
+            r64 = ref64[f"r{i % 4}"][rows]
+            tol = tolerance32(r32, r64)
+            d = float((g - r64).abs().max())
+            assert d <= tol, (rid, d, tol)
+            worst = max(worst, d / tol)
         else:
             r16 = ref16[f"r{i % 4}"][rows]
             tol = float((r16 - r32).abs().max())
@@ -240,4 +262,4 @@ def test_eight_live_requests_beyond_1000_tokens_with_pages_used_again(crowd, dty
             assert d <= tol, (rid, d, tol)
             worst = max(worst, d / tol)
     ru.record_margin("tinyllama (4 of 22 layers) eight live requests, pages used again", dtype, worst,
-                     "|diff| (limit 1e-4)" if dtype == "float32" else "|diff| / tolerance")
+                     "|diff| / tolerance")
