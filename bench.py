@@ -6,8 +6,11 @@
 A step is one decode step of a batch of 8 requests at a context of 2,048 tokens (the last timed step
 writes position 2047).  `value` is decoded tokens per second with the device clock around K steps
 that are enqueued back to back; `e2e` is the same through the Python entry point with host tokens in
-and out every step.  The line also carries a 2,048-token prefill, decoding at batch 1 and 64, the
-HBM roofline of the decode step, and the clocks seen while timing."""
+and out every step.  Every figure is the median of REPEATS timed regions of K steps each inside the
+one run.  The line also carries a 2,048-token prefill, decoding at batch 1 and 64, the stated workload
+of the model's benchmark (512-token prompts + 256 generated tokens through the entry point, admission and
+prompts included), the same points at the Llama-2-7B and Llama-3-8B layer sizes (all 32 layers), the HBM
+roofline of every decode point, and the clocks seen while timing."""
 import argparse
 import json
 import os
@@ -24,9 +27,15 @@ TINYLLAMA = dict(architectures=["LlamaForCausalLM"], model_type="llama", num_hid
                  num_attention_heads=32, num_key_value_heads=4, intermediate_size=5632, vocab_size=32000,
                  rope_theta=10000.0, rms_norm_eps=1e-5, max_position_embeddings=2048, tie_word_embeddings=False,
                  hidden_act="silu", initializer_range=0.02, torch_dtype="bfloat16")
+LLAMA2_7B = dict(TINYLLAMA, num_hidden_layers=32, hidden_size=4096, num_attention_heads=32, num_key_value_heads=32,
+                 intermediate_size=11008, vocab_size=32000, rope_theta=10000.0, max_position_embeddings=4096)
+LLAMA3_8B = dict(TINYLLAMA, num_hidden_layers=32, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8,
+                 intermediate_size=14336, vocab_size=128256, rope_theta=500000.0, max_position_embeddings=8192)
+OTHER_SHAPES = {"llama2_7b": (LLAMA2_7B, 3), "llama3_8b": (LLAMA3_8B, 4)}   # configuration, seed of its weights
 CONTEXT = 2048
 BATCH = 8
 PAGE = 16
+REPEATS = 5
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
@@ -84,15 +93,15 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(self.rows)}
 
 
-def build_model(layers, dtype, device):
+def build_model(layers, dtype, device, shape=TINYLLAMA, seed=2):
     import torch
     from tiny_llm_b200.config import LlamaConfig
     from tiny_llm_b200.parts import DecoderModel
     from tiny_llm_b200.weights import load_state, random_state
-    cfg = LlamaConfig.from_dict(dict(TINYLLAMA, num_hidden_layers=layers))
+    cfg = LlamaConfig.from_dict(dict(shape, num_hidden_layers=layers))
     model = DecoderModel(cfg.model_spec())
     specs = model.weight_specs()
-    state = random_state(specs, 2, cfg.initializer_range, dtype, device=device)   # seed 2, N(0, 0.02)
+    state = random_state(specs, seed, cfg.initializer_range, dtype, device=device)   # N(0, 0.02)
     model.load(load_state(specs, state, dtype, device))
     return cfg, model
 
@@ -127,9 +136,10 @@ def timeline_summary(records):
     return dict(sorted(out.items(), key=lambda kv: -kv[1]["total_us"]))
 
 
-def timed_decode(runner, batch, start_len, steps, warmup, sampler_out):
-    """Prefills `batch` requests to start_len tokens, then runs warmup + steps decode steps enqueued
-    back to back; returns (ms per step over the timed steps, kernels launched in them)."""
+def timed_decode(runner, batch, start_len, steps, warmup, sampler_out, repeats=1):
+    """Prefills `batch` requests to start_len tokens, then runs warmup + repeats x steps decode steps enqueued
+    back to back, each run of `steps` between two events; returns (median ms per step over the runs,
+    kernels launched in one run, mean context of the timed steps)."""
     import torch
     from tiny_llm_b200 import ops
     from tiny_llm_b200.engine import StepEntry
@@ -141,7 +151,7 @@ def timed_decode(runner, batch, start_len, steps, warmup, sampler_out):
         toks = torch.randint(0, vocab, (start_len,), generator=g).tolist()
         for lo in range(0, start_len, 1024):
             runner.step([StepEntry(rid, toks[lo: lo + 1024], [])])
-    feed = torch.randint(0, vocab, (warmup + steps, batch), generator=g).tolist()
+    feed = torch.randint(0, vocab, (warmup + repeats * steps, batch), generator=g).tolist()
 
     def one(i):
         logits = runner.step([StepEntry(rid, [feed[i][j]], [0]) for j, rid in enumerate(rids)])
@@ -149,24 +159,27 @@ def timed_decode(runner, batch, start_len, steps, warmup, sampler_out):
 
     for i in range(warmup):
         one(i)
-    torch.cuda.synchronize()
-    before = ops.launches
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0.record()
-    for i in range(warmup, warmup + steps):
-        if TRACE and i == warmup + steps - 1:   # the last step alone, between two reads of the timeline notes
-            torch.cuda.synchronize()
-            ops.trace_dump()
-        one(i)
-    t1.record()
-    torch.cuda.synchronize()
+    times, launched = [], 0
+    for rep in range(repeats):
+        torch.cuda.synchronize()
+        before = ops.launches
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for i in range(warmup + rep * steps, warmup + (rep + 1) * steps):
+            if TRACE and rep == repeats - 1 and i == warmup + repeats * steps - 1:   # the last step alone, between two reads of the timeline notes
+                torch.cuda.synchronize()
+                ops.trace_dump()
+            one(i)
+        t1.record()
+        torch.cuda.synchronize()
+        times.append(t0.elapsed_time(t1) / steps)
+        launched = ops.launches - before
     if TRACE:
         timed_decode.timeline = ops.trace_dump()
-    ms = t0.elapsed_time(t1) / steps
-    launched = ops.launches - before
     for rid in rids:
         runner.cache.free_request(rid)
-    return ms, launched
+    mean_ctx = start_len + warmup + (repeats * steps + 1) / 2.0
+    return statistics.median(times), launched, mean_ctx
 
 
 def timed_prefill(runner, tokens, repeats=5):
@@ -189,17 +202,18 @@ def timed_prefill(runner, tokens, repeats=5):
     return statistics.median(times)
 
 
-def timed_e2e(pipe, batch, context, steps, warmup):
+def timed_e2e(pipe, batch, context, steps, warmup, repeats=1):
     """The same decode through the Python entry point: host tokens in and out every step.  The
     requests are admitted over several steps (the prompt budget), so they get a margin of tokens
     that keeps all of them decoding side by side through warm-up and the timed steps; the last timed
-    step still runs within `margin` tokens of `context`."""
+    step still runs within `margin` tokens of `context`.  Returns the median over `repeats` runs of
+    `steps` steps each of the wall time per step."""
     import torch
     from tiny_llm_b200.sampling import SamplingParams
     g = torch.Generator().manual_seed(3)
     vocab = pipe.model.spec.vocab_size
     margin = 2 * batch + 4
-    new_tokens = steps + warmup + margin
+    new_tokens = repeats * steps + warmup + margin
     params = SamplingParams(max_new_tokens=new_tokens, do_sample=False, ignore_eos=True)
     for _ in range(batch):
         pipe.add_request(torch.randint(0, vocab, (context - new_tokens,), generator=g).tolist(), params)
@@ -207,17 +221,79 @@ def timed_e2e(pipe, batch, context, steps, warmup):
         pipe.step()                                  # prompts in (untimed)
     for _ in range(warmup):
         pipe.step()
-    torch.cuda.synchronize()
-    assert len(pipe.scheduler.running) == batch
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        pipe.step()
-    torch.cuda.synchronize()
-    dt = time.perf_counter() - t0
-    assert len(pipe.scheduler.running) == batch      # nobody ended inside the timed steps
+    times = []
+    for _ in range(repeats):
+        torch.cuda.synchronize()
+        assert len(pipe.scheduler.running) == batch
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            pipe.step()
+        torch.cuda.synchronize()
+        times.append((time.perf_counter() - t0) * 1e3 / steps)
+        assert len(pipe.scheduler.running) == batch      # nobody ended inside the timed steps
     while pipe.has_work():
         pipe.step()
-    return dt * 1e3 / steps
+    return statistics.median(times)
+
+
+def timed_workload(pipe, batch, prompt_len=512, new_tokens=256, repeats=3):
+    """The benchmark's stated workload through the entry point: `batch` requests of a 512-token random
+    prompt each, 256 tokens generated greedily, from the first add_request to the last token on the
+    host (admission, prompts in portions, decoding).  Returns generated tokens per second of wall time,
+    median of `repeats` runs (after one untimed run)."""
+    import torch
+    g = torch.Generator().manual_seed(4)
+    vocab = pipe.model.spec.vocab_size
+    rates = []
+    for rep in range(repeats + 1):
+        prompts = [torch.randint(0, vocab, (prompt_len,), generator=g).tolist() for _ in range(batch)]
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        out = pipe.apply(prompts, max_new_tokens=new_tokens, do_sample=False, ignore_eos=True)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        assert all(len(o) == new_tokens for o in out)
+        if rep:
+            rates.append(batch * new_tokens / dt)
+    return statistics.median(rates)
+
+
+def decode_bytes(model, runner, batch, mean_ctx, itemsize):
+    """Bytes a decode step has to read: every weight once and the cache of the live requests."""
+    kv_per_token = sum(g.bytes_per_token(itemsize) for g in runner.cache.groups)
+    return weight_bytes(model) + batch * mean_ctx * kv_per_token
+
+
+def prefill_flops(c, layers, t):
+    """2 * T * matrix parameters + causal attention + LM head on one row."""
+    per_layer = (c.hidden_size * (c.num_attention_heads + 2 * c.num_key_value_heads) * c.head_dim +
+                 c.num_attention_heads * c.head_dim * c.hidden_size + 3 * c.hidden_size * c.intermediate_size)
+    return 2.0 * t * per_layer * layers + 2.0 * t * t * c.num_attention_heads * c.head_dim * layers + \
+        2.0 * c.hidden_size * c.vocab_size
+
+
+def other_shape_points(name, shape, seed, dtype, device, pk, steps, out, points, fracs):
+    """Decode at batch 16 and 64 and a 2,048-token prefill at another model's layer sizes, all of its layers."""
+    import gc
+
+    import torch
+    from tiny_llm_b200.engine import make_runner
+    cfg, model = build_model(shape["num_hidden_layers"], dtype, device, shape=shape, seed=seed)
+    itemsize = 2 if dtype == torch.bfloat16 else 4
+    runner = make_runner(model, dtype, device, max_tokens=64 * CONTEXT, page_size=PAGE, max_requests=64,
+                         max_tokens_per_step=2048)
+    s = min(steps, 16)
+    for b in (16, 64):
+        ms, _, ctx = timed_decode(runner, b, CONTEXT - (3 * s + 3), s, 3, out, repeats=3)
+        points[f"{name}_decode_b{b}"] = round(b * 1e3 / ms, 1)
+        fracs[f"{name}_decode_b{b}"] = round(decode_bytes(model, runner, b, ctx, itemsize) / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+    ms = timed_prefill(runner, 2048, repeats=3)
+    points[f"{name}_prefill_2048"] = round(2048 * 1e3 / ms, 1)
+    if dtype == torch.bfloat16:
+        fracs[f"{name}_prefill_2048"] = round(prefill_flops(cfg, cfg.num_hidden_layers, 2048) / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)
+    del runner, model
+    gc.collect()
+    torch.cuda.empty_cache()
 
 
 def reference_arm():
@@ -233,7 +309,7 @@ def main():
     global PAGE
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=TINYLLAMA["num_hidden_layers"],
@@ -243,6 +319,8 @@ def main():
                     help="measure one part only (for profiler captures of a small case)")
     ap.add_argument("--batch", type=int, default=BATCH, help="requests of the decode step (default 8)")
     ap.add_argument("--page-size", type=int, default=PAGE, help="tokens per page of the cache")
+    ap.add_argument("--quick", action="store_true",
+                    help="leave out the workload points and the Llama-2-7B / Llama-3-8B layer sizes")
     args = ap.parse_args()
     PAGE = args.page_size
     if args.impl == "reference":
@@ -261,7 +339,10 @@ def main():
     pk = peaks()
     cfg, model = build_model(args.layers, dtype, device)
     itemsize = 2 if dtype == torch.bfloat16 else 4
-    start_len = CONTEXT - (steps + warmup)            # the last timed step writes position CONTEXT - 1
+    start_len = CONTEXT - (REPEATS * steps + warmup)   # the last timed step writes position CONTEXT - 1
+    if start_len < 64:
+        print(f"--steps {steps} x {REPEATS} repeats + --warmup {warmup} do not fit a context of {CONTEXT}")
+        return 2
     runner = make_runner(model, dtype, device, max_tokens=64 * CONTEXT, page_size=PAGE, max_requests=64,
                          max_tokens_per_step=2048)
     out = torch.zeros(64, dtype=torch.int32, device=device)
@@ -269,7 +350,7 @@ def main():
     if args.only != "all":
         # a small, single-purpose run for a profiler capture: one plain line, no record
         if args.only == "decode":
-            ms, launched = timed_decode(runner, args.batch, start_len, steps, warmup, out)
+            ms, launched, _ = timed_decode(runner, args.batch, CONTEXT - (steps + warmup), steps, warmup, out)
             rec = {"only": "decode", "batch": args.batch, "layers": args.layers, "ms_per_step": round(ms, 4),
                    "gpu_launches": launched}
             if TRACE:
@@ -288,36 +369,46 @@ def main():
         return 0
 
     sampler = ClockSampler().start()
-    ms, launched = timed_decode(runner, BATCH, start_len, steps, warmup, out)
+    ms, launched, mean_ctx = timed_decode(runner, BATCH, start_len, steps, warmup, out, repeats=REPEATS)
     clocks = sampler.stop()
+    achieved = decode_bytes(model, runner, BATCH, mean_ctx, itemsize) / (ms * 1e-3) / 1e9
 
-    points = {}
+    points, fracs = {}, {}
     for b, key in ((1, "decode_b1"), (64, "decode_b64")):
         s = min(steps, 32)
-        pms, _ = timed_decode(runner, b, CONTEXT - (s + 3), s, 3, out)
+        pms, _, ctx = timed_decode(runner, b, CONTEXT - (REPEATS * s + 3), s, 3, out, repeats=REPEATS)
         points[key] = round(b * 1e3 / pms, 1)
+        fracs[key] = round(decode_bytes(model, runner, b, ctx, itemsize) / (pms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
     prefill_ms = timed_prefill(runner, 2048)
 
     pipe = Pipeline.from_model(cfg, model, dtype=dtype, device=0, page_size=PAGE, max_tokens=BATCH * CONTEXT,
                                max_requests=BATCH, max_tokens_per_step=2048, chunk=1024)
-    e2e_ms = timed_e2e(pipe, BATCH, CONTEXT, steps, warmup)
+    e2e_ms = timed_e2e(pipe, BATCH, CONTEXT, steps, warmup, repeats=REPEATS)
     h2d = 4 * (3 * BATCH + (BATCH + 1) + 3 * BATCH + BATCH + BATCH + BATCH * pipe.runner.max_blocks)
+    del pipe
 
-    # roofline of the decode step: every weight once + the cache of the live requests
-    kv_per_token = sum(g.bytes_per_token(itemsize) for g in runner.cache.groups)
-    mean_ctx = start_len + warmup + (steps + 1) / 2.0
-    step_bytes = weight_bytes(model) + BATCH * mean_ctx * kv_per_token
-    achieved = step_bytes / (ms * 1e-3) / 1e9
-    # flops of the prefill step: 2 * T * matrix parameters + causal attention + LM head on one row
-    s = model.spec
+    # the stated workload of the model's benchmark: 512-token prompts + 256 generated tokens through the entry
+    # point (generated tokens per second of wall time for the whole call, prompts and admission included)
+    if not args.quick:
+        for b in (1, 8, 64):
+            wl = Pipeline.from_model(cfg, model, dtype=dtype, device=0, page_size=PAGE, max_tokens=b * 768 + 64,
+                                     max_requests=b, max_tokens_per_step=2048, chunk=512)
+            points[f"workload_512p_256g_b{b}"] = round(timed_workload(wl, b), 1)
+            del wl
+
     c = cfg
-    per_layer = (c.hidden_size * (c.num_attention_heads + 2 * c.num_key_value_heads) * c.head_dim +
-                 c.num_attention_heads * c.head_dim * c.hidden_size + 3 * c.hidden_size * c.intermediate_size)
     t = 2048
-    flops = 2.0 * t * per_layer * args.layers + 2.0 * t * t * c.num_attention_heads * c.head_dim * args.layers + \
-        2.0 * c.hidden_size * c.vocab_size
+    flops = prefill_flops(c, args.layers, t)
     peak_flops = pk["bf16_tflops"] * 1e12 if dtype == torch.bfloat16 else None
     value = BATCH * 1e3 / ms
+    if not args.quick:
+        # the other shapes the benchmark names, all of their layers; this model's tensors go first
+        del runner, model
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        for name, (shape, seed) in OTHER_SHAPES.items():
+            other_shape_points(name, shape, seed, dtype, device, pk, steps, out, points, fracs)
     line = {
         "metric": "decode tok/s at batch 8, context 2048 (TinyLlama-1.1B layer sizes)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
@@ -328,15 +419,15 @@ def main():
                    "hidden_size": c.hidden_size, "heads": c.num_attention_heads, "kv_heads": c.num_key_value_heads,
                    "head_dim": c.head_dim, "intermediate_size": c.intermediate_size, "vocab_size": c.vocab_size,
                    "page_size": PAGE, "l2": "inputs larger than L2 (weights read every step)",
-                   "peaks": pk["source"]},
+                   "peaks": pk["source"], "repeats": REPEATS, "other_shapes": "llama2_7b and llama3_8b: 32 of 32 layers"},
         "e2e": {"value": round(BATCH * 1e3 / e2e_ms, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * BATCH},
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * (BATCH + 1)},
         "gpu_launches": launched,
         "prefill": {"value": round(t * 1e3 / prefill_ms, 1), "tokens": t, "ms": round(prefill_ms, 3),
                     "frac": None if peak_flops is None else round(flops / (prefill_ms * 1e-3) / peak_flops, 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
-        "points": points, "clocks": clocks,
+        "points": points, "points_frac": fracs, "clocks": clocks,
         "libraries": sorted(os.path.basename(p) for p in ops.build.loaded_libraries().values()),
     }
     ops.check_status()   # no kernel of the timed runs gave up a bounded wait

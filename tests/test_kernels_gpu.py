@@ -259,12 +259,13 @@ def test_paged_attention(ops, dtype, nq, nkv, hd, page, window):
         assert float(p[3]) > 0.9
 
 
-@pytest.mark.parametrize("nq,nkv,page", [(8, 1, 16), (32, 4, 16), (4, 4, 8), (2, 1, 64), (16, 2, 32)])
-def test_paged_attention_on_tcgen05(ops, nq, nkv, page):
-    """Head size 64 and portions of at least 128 rows: the tcgen05 kernel.  Portions that start in the
-    middle of a sequence, end in the middle of a page, and a one-token request beside them; unwritten
+@pytest.mark.parametrize("hd,nq,nkv,page", [(64, 8, 1, 16), (64, 32, 4, 16), (64, 4, 4, 8), (64, 2, 1, 64), (64, 16, 2, 32),
+                                            (128, 8, 8, 16), (128, 32, 8, 16), (128, 4, 1, 8), (128, 2, 2, 64), (128, 16, 1, 32)])
+def test_paged_attention_on_tcgen05(ops, hd, nq, nkv, page):
+    """Head size 64 or 128 and portions of at least 128 rows: the tcgen05 kernel.  Portions that start in
+    the middle of a sequence, end in the middle of a page, and a one-token request beside them; unwritten
     slots of the pages are NaN."""
-    hd, dtype = 64, "bfloat16"
+    dtype = "bfloat16"
     lens = [700, 300, 129, 64]
     q_lens = [389, 300, 17, 1]
     table, k_cache, v_cache, ks, vs = paged_setup(dtype, 4, lens, nkv, hd, page, seed=nq + page)
@@ -296,7 +297,7 @@ def test_paged_attention_on_tcgen05(ops, nq, nkv, page):
     ops.paged_attention(qkv.to(DEV), nq, nkv, hd, k_cache.to(DEV), v_cache.to(DEV), table.to(DEV), batch, out,
                         scale, None, Workspace(DEV))
     ops.check_status()
-    assert "attention_tc_head_dim64" in set(ops_mod.build.loaded_libraries()) | before
+    assert f"attention_tc_head_dim{hd}" in set(ops_mod.build.loaded_libraries()) | before
     out = out.float().cpu()
     assert not torch.isnan(out).any()
     cur = 0

@@ -1,5 +1,5 @@
 // bfloat16 attention of prompt portions over the paged cache on the 5th-generation tensor cores
-// (tcgen05), for head size 64 (-DTLLM_HEAD_DIM=64).
+// (tcgen05), for head size 64 or 128 (-DTLLM_HEAD_DIM=64 / 128).
 //
 // A CTA serves 128 rows of one (request, key/value head); a row is a (new token, query head of the
 // group) pair, so the heads of a group share every key/value tile.  Keys are walked in tiles of 64:
@@ -23,8 +23,17 @@
 // Two such CTAs share an SM, so one CTA's softmax overlaps the other's MMAs.  Every wait is
 // bounded (two seconds), after which the kernel records a code in the status word and stops.
 //
-// Sizes: head size 64; heads per key/value head a power of two up to 128; page size 8, 16, 32 or
-// 64; no window.  Other cases run on the mma.sync kernels of attention_mma.cu.
+// Head size 128: a row of 128 values is two 128-byte swizzle rows, so every operand lies in shared
+// memory as two panels of 64 columns (Q: 128 rows each, a key or value tile: 64 rows each), fetched by
+// two copies per page, and the ring has two stages so that two CTAs still fit an SM.  S = Q K^T walks
+// both panels (eight steps of K = 16); O += P V is one product of N = 128 per 16 keys whose descriptor
+// names the distance between the two value panels (the leading byte offset of an MN-major operand).
+// Tensor memory: O takes 128 columns, so P of a tile is written over that tile's own S (which the
+// softmax has read into registers by then): S/P of even tiles [0, 64), of odd tiles [64, 128), O
+// [128, 256).
+//
+// Sizes: head size 64 or 128; heads per key/value head a power of two up to 128; page size 8, 16, 32
+// or 64; no window.  Other cases run on the mma.sync kernels of attention_mma.cu.
 //
 // Reference counterpart: tiny_llm/ops/cuda/flash_attention.cu:338-442 (32-bit SIMT, one lane per
 // key, 64-key tiles, chunk-local causal mask).
@@ -36,7 +45,7 @@
 #include "tc_common.cuh"
 
 #ifndef TLLM_HEAD_DIM
-#error "compile with -DTLLM_HEAD_DIM=64"
+#error "compile with -DTLLM_HEAD_DIM=64 or 128"
 #endif
 
 TLLM_DEFINE_LAST_ERROR
@@ -44,10 +53,11 @@ TLLM_DEFINE_LAST_ERROR
 namespace tllm {
 
 constexpr int HD = TLLM_HEAD_DIM;
-static_assert(HD == 64, "a row of keys must be one 128-byte swizzle row");
+static_assert(HD == 64 || HD == 128, "a row of keys is one or two 128-byte swizzle rows");
+constexpr int PANELS = HD / 64;  // panels of 64 columns (one swizzle row wide) per operand
 constexpr int BM = 128;          // rows per CTA = MMA M
 constexpr int BNK = 64;          // keys per tile
-constexpr int KV_STAGES = 4;
+constexpr int KV_STAGES = HD == 64 ? 4 : 2;
 constexpr int THREADS = 224;     // warp 0: TMA, warp 1: S = Q K^T + tensor memory, warps 2-5: softmax, warp 6: O += P V
 constexpr int UMMA_K = 16;
 constexpr int Q_BYTES = BM * HD * 2, K_BYTES = BNK * HD * 2, V_BYTES = BNK * HD * 2;
@@ -56,9 +66,11 @@ constexpr int OFF_BAR = OFF_V + KV_STAGES * V_BYTES;
 constexpr int MAX_TABLE = 1024;                    // block-table entries kept in shared memory (longer tables are read from global)
 constexpr int OFF_TABLE = OFF_BAR + 160;
 constexpr int SMEM_TOTAL = OFF_TABLE + MAX_TABLE * 4 + 1024;   // + alignment slack
-constexpr uint32_t TMEM_COLS = 256;                // S of even tiles: columns [0, 64); of odd tiles: [64, 128); O: [128, 192);
-constexpr uint32_t TMEM_O = 2 * BNK, TMEM_P = TMEM_O + HD;   // P (bfloat16 pairs) of even tiles: [192, 224); of odd tiles: [224, 256)
-static_assert(TMEM_P + BNK <= TMEM_COLS, "S, O and P share 256 columns of tensor memory");
+constexpr int Q_PANEL = BM * 128, KV_PANEL = BNK * 128;   // bytes of one panel of Q / of a key or value tile
+constexpr uint32_t TMEM_COLS = 256;                // S of even tiles: columns [0, 64); of odd tiles: [64, 128); O: [128, 128 + HD);
+// P (bfloat16 pairs): head size 64: even tiles [192, 224), odd tiles [224, 256); head size 128: over the tile's own S
+constexpr uint32_t TMEM_O = 2 * BNK, TMEM_P = HD == 64 ? TMEM_O + HD : 0, TMEM_P_STEP = HD == 64 ? BNK / 2 : BNK;
+static_assert(TMEM_O + HD <= TMEM_COLS && TMEM_P + TMEM_P_STEP + BNK / 2 <= TMEM_COLS, "S, O and P share 256 columns of tensor memory");
 constexpr float RESCALE_STEP = 8.f;
 constexpr int ERR_ATT_PRODUCER = 7, ERR_ATT_MMA = 8, ERR_ATT_SOFTMAX = 9;
 
@@ -165,13 +177,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     // are issued side by side (one thread issuing them all was the slowest part of the whole kernel).
     const int* table = p.block_table + (size_t)req * p.max_blocks;
     const int pages_per_tile = BNK / p.page_size;
-    const uint32_t page_bytes = (uint32_t)p.page_size * HD * 2u;
-    const int g = lane >> 1;
-    const bool is_v = lane & 1;
-    if (lane == 0 && n_tiles > 0) {
-      mbar_expect_tx(q_full, Q_BYTES);
-      tma_load_3d(smem, &map_q, 0, kvh * group, tok0 + tok_lo, q_full);
+    const uint32_t panel_page_bytes = (uint32_t)p.page_size * 128u;          // one page inside one panel
+    const uint32_t page_bytes = panel_page_bytes * PANELS;
+    // lane = (page of the tile, keys or values, panel): 2 * PANELS copies per page, at most eight pages per tile
+    const int g = lane / (2 * PANELS);
+    const bool is_v = (lane / PANELS) & 1;
+    const int panel = lane % PANELS;
+    if (lane < PANELS && n_tiles > 0) {
+      if (lane == 0) mbar_expect_tx(q_full, Q_BYTES);
+      __syncwarp(PANELS == 1 ? 1u : 3u);
+      tma_load_3d(smem + lane * Q_PANEL, &map_q, lane * 64, kvh * group, tok0 + tok_lo, q_full);
     }
+    __syncwarp();
 #ifdef TLLM_ATT_TIMING
     const bool timed = blockIdx.x == 0 && lane == 0;
     unsigned long long att_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -193,7 +210,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       int page = -1;
       const int blk = i * pages_per_tile + g;
       if (g < pages_per_tile && blk < p.max_blocks && blk * p.page_size < kv_end) page = blk < MAX_TABLE ? table_s[blk] : table[blk];
-      const int n_valid = __popc(__ballot_sync(0xffffffffu, page >= 0 && !is_v));
+      const int n_valid = __popc(__ballot_sync(0xffffffffu, page >= 0 && !is_v && panel == 0));
       if (lane == 0) {
         mbar_expect_tx(&k_full[s], (uint32_t)n_valid * page_bytes);
         mbar_expect_tx(&v_full[s], (uint32_t)n_valid * page_bytes);
@@ -201,8 +218,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       __syncwarp();
       if (page >= 0) {
         const int row = (page * p.nkv + kvh) * p.page_size;
-        if (is_v) tma_load_2d(smem + OFF_V + s * V_BYTES + g * page_bytes, &map_v, 0, row, &v_full[s]);
-        else tma_load_2d(smem + OFF_K + s * K_BYTES + g * page_bytes, &map_k, 0, row, &k_full[s]);
+        const uint32_t off = panel * KV_PANEL + g * panel_page_bytes;
+        if (is_v) tma_load_2d(smem + OFF_V + s * V_BYTES + off, &map_v, panel * 64, row, &v_full[s]);
+        else tma_load_2d(smem + OFF_K + s * K_BYTES + off, &map_k, panel * 64, row, &k_full[s]);
       }
     }
 #ifdef TLLM_ATT_TIMING
@@ -238,8 +256,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const uint32_t d = tmem_u + (t & 1) * BNK, kt_lo = k_lo + s * (K_BYTES >> 4);   // descriptors count in 16-byte units
       if (elect_one()) {
 #pragma unroll
-        for (int k = 0; k < HD / UMMA_K; ++k)
-          umma_bf16_lo(d, q_lo + (k * UMMA_K * 2 >> 4), kt_lo + (k * UMMA_K * 2 >> 4), idesc_qk, k > 0 ? 1u : 0u);
+        for (int k = 0; k < HD / UMMA_K; ++k) {   // 16 columns = 32 bytes inside a swizzle row; every fourth step enters the next panel
+          const uint32_t in_panel = (uint32_t)((k & 3) * UMMA_K * 2) >> 4;
+          umma_bf16_lo(d, q_lo + (uint32_t)(k >> 2) * (Q_PANEL >> 4) + in_panel, kt_lo + (uint32_t)(k >> 2) * (KV_PANEL >> 4) + in_panel,
+                       idesc_qk, k > 0 ? 1u : 0u);
+        }
         umma_commit(&s_full[t & 1]);
       }
       __syncwarp();
@@ -253,7 +274,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     // ---------------- O += P V of tile i, when the softmax has written P (the same way: warp-wide loop, one lane issues)
     const uint32_t idesc_pv = instr_desc_bf16(BM, HD, true);   // V as it lies: rows = keys (MN-major B)
     const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
-    const uint32_t v_lo = smem_desc_sw128_lo(smem_u32(smem + OFF_V));
+    // head size 128: the values' second panel of 64 columns lies KV_PANEL bytes after the first
+    const uint32_t v_lo = smem_desc_sw128_lo(smem_u32(smem + OFF_V), PANELS == 1 ? 16u : (uint32_t)KV_PANEL);
     const uint32_t tmem_o = tmem_u + TMEM_O;
     bool ok = true;
 #ifdef TLLM_ATT_TIMING
@@ -271,12 +293,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       if (!ok) break;
       tc_fence_after();
       ATT_T(2)   // waited for V
-      const uint32_t a = tmem_u + TMEM_P + (i & 1) * (BNK / 2), vt_lo = v_lo + s * (V_BYTES >> 4);
+      const uint32_t a = tmem_u + TMEM_P + (i & 1) * TMEM_P_STEP, vt_lo = v_lo + s * (V_BYTES >> 4);
       const uint32_t acc0 = i > 0 ? 1u : 0u;
       if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < BNK / UMMA_K; ++kk)   // 16 keys per step: eight columns of P pairs, two 8-row groups of V
-          umma_bf16_ts_lo(tmem_o, a + kk * (UMMA_K / 2), vt_lo + (kk * UMMA_K * HD * 2 >> 4), idesc_pv, kk > 0 ? 1u : acc0);
+          umma_bf16_ts_lo(tmem_o, a + kk * (UMMA_K / 2), vt_lo + (kk * UMMA_K * 128 >> 4), idesc_pv, kk > 0 ? 1u : acc0);
         umma_commit(&kv_empty[s]);
         umma_commit(&o_done[i & 1]);
       }
@@ -361,7 +383,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         uint32_t pk[BNK / 2];
 #pragma unroll
         for (int j = 0; j < BNK / 2; ++j) pk[j] = pack_bf16(sc[2 * j], sc[2 * j + 1]);
-        tmem_st32_raw(t_p0 + (i & 1) * (BNK / 2), pk);
+        tmem_st32_raw(t_p0 + (i & 1) * TMEM_P_STEP, pk);
       }
       ATT_T(3)   // P on its way to tensor memory
       if (!__all_sync(0xffffffffu, ok && (i == 0 || corr == 1.f))) {   // the maximum of some row of this warp moved far
@@ -390,9 +412,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         if (soft_tid < BNK && j0 + soft_tid >= kv_end) {
-          uint4* vrow = reinterpret_cast<uint4*>(smem + OFF_V + s * V_BYTES + soft_tid * 128);
 #pragma unroll
-          for (int ch = 0; ch < 8; ++ch) vrow[ch] = make_uint4(0u, 0u, 0u, 0u);
+          for (int pn = 0; pn < PANELS; ++pn) {
+            uint4* vrow = reinterpret_cast<uint4*>(smem + OFF_V + s * V_BYTES + pn * KV_PANEL + soft_tid * 128);
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch) vrow[ch] = make_uint4(0u, 0u, 0u, 0u);
+          }
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // V was written by ordinary stores
       }
@@ -453,7 +478,7 @@ static bool make_map_rows(CUtensorMap* map, const void* ptr, long long rows, int
   if (!fn) return false;
   cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
-  cuuint32_t box[2] = {(cuuint32_t)HD, (cuuint32_t)box_rows};
+  cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};   // one panel: a swizzle row of 128 bytes
   cuuint32_t elem[2] = {1, 1};
   if (fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -477,7 +502,7 @@ static bool make_map_q(CUtensorMap* map, const void* ptr, int tokens, int nq, in
   if (!fn) return false;
   cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)nq, (cuuint64_t)tokens};
   cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)q_row_stride * 2};
-  cuuint32_t box[3] = {(cuuint32_t)HD, (cuuint32_t)group, (cuuint32_t)(BM / group)};
+  cuuint32_t box[3] = {64u, (cuuint32_t)group, (cuuint32_t)(BM / group)};
   cuuint32_t elem[3] = {1, 1, 1};
   if (fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, elem,
          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,

@@ -127,7 +127,11 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
 // a 64-bit descriptor built per product).  All descriptors of one kernel share their upper word; the lower one
 // is the start address in 16-byte units plus a constant, so a product needs one 32-bit add per operand.
 constexpr uint32_t SMEM_DESC_SW128_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
-__device__ __forceinline__ uint32_t smem_desc_sw128_lo(uint32_t addr) { return ((addr & 0x3FFFFu) >> 4) | (1u << 16); }
+// `lbo_bytes`: the leading byte offset.  A K-major operand does not use it (16 bytes, the customary filler); for
+// an MN-major operand wider than one swizzle row (64 values of 16 bits) it is the distance between its panels of 64.
+__device__ __forceinline__ uint32_t smem_desc_sw128_lo(uint32_t addr, uint32_t lbo_bytes = 16u) {
+  return ((addr & 0x3FFFFu) >> 4) | ((lbo_bytes >> 4) << 16);
+}
 __device__ __forceinline__ void umma_bf16_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"

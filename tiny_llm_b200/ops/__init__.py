@@ -422,11 +422,11 @@ def paged_attention(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_d
         raise KernelError("paged_attention: shapes or dtypes do not fit")
     page_size = k_cache.shape[2]
     group = num_heads // num_kv_heads
-    if qkv.dtype == torch.bfloat16 and not force_generic and attention_tc and head_dim == 64 and not window and \
-            batch.max_q_len * group >= 128 and qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0 and \
+    if qkv.dtype == torch.bfloat16 and not force_generic and attention_tc and head_dim in ATTENTION_TC_HEAD_DIMS and \
+            not window and batch.max_q_len * group >= 128 and qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0 and \
             k_cache.is_contiguous() and v_cache.is_contiguous():
         # portions of prompts: 128 rows of (token, head of the group) per CTA on the tcgen05 tensor cores
-        lib = build.load_library("attention_tc", flags=("-DTLLM_HEAD_DIM=64",))
+        lib = build.load_library("attention_tc", flags=(f"-DTLLM_HEAD_DIM={head_dim}",))
         if lib.tllm_attention_tc_fits(num_heads, num_kv_heads, head_dim, page_size, 0):
             _check(lib, lib.tllm_attention_tc(
                 _ptr(qkv), qkv.stride(0), _ptr(k_cache), _ptr(v_cache), ctypes.c_longlong(k_cache.shape[0]),
@@ -514,6 +514,7 @@ ALL_LIBRARIES = ("elementwise", "linear_generic", "linear_tc", "attention_generi
 
 
 ATTENTION_HEAD_DIMS = (16, 32, 48, 64, 128)   # head sizes `build_all` compiles ahead; others compile on first use
+ATTENTION_TC_HEAD_DIMS = (64, 128)            # head sizes the tcgen05 prompt-attention kernel is written for
 
 
 def build_all(verbose: bool = True):
@@ -521,5 +522,6 @@ def build_all(verbose: bool = True):
     paths = [build.compile_library(n, verbose=verbose) for n in ALL_LIBRARIES]
     paths += [build.compile_library("attention_mma", flags=(f"-DTLLM_HEAD_DIM={hd}",), verbose=verbose)
               for hd in ATTENTION_HEAD_DIMS]
-    paths.append(build.compile_library("attention_tc", flags=("-DTLLM_HEAD_DIM=64",), verbose=verbose))
+    paths += [build.compile_library("attention_tc", flags=(f"-DTLLM_HEAD_DIM={hd}",), verbose=verbose)
+              for hd in ATTENTION_TC_HEAD_DIMS]
     return paths
