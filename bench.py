@@ -296,12 +296,86 @@ def other_shape_points(name, shape, seed, dtype, device, pk, steps, out, points,
     torch.cuda.empty_cache()
 
 
-def reference_arm():
-    """The reference is a Bazel + Rust + CUDA >= 13 C++ project without a Python package: the one
-    allowed offline install (pip install --no-index ... of the reference checkout) has nothing to build."""
-    print(json.dumps({"impl": "reference", "unavailable":
-                      "zscey/tiny-llm is a Bazel/Rust/CUDA-13 C++ project with no setup.py or pyproject.toml; "
-                      "pip cannot install it offline and no Bazel or Rust toolchain exists here"}))
+REF_DIR = os.path.join(ROOT, "baseline", "_ref")
+
+
+def reference_arm(steps, warmup):
+    """The reference arm: zscey/tiny-llm's own engine, unmodified (its parser, plan, runtime and CUDA kernels,
+    compiled by baseline/build_reference.py and driven below the tokenizer by baseline/ref_driver.cpp as its
+    Pipeline::apply drives it), at the same configuration: TinyLlama-1.1B layer sizes, 22 layers, batch 8,
+    context 2,048, paged mode, greedy sampling on the host.  Its only dtype is float32.  pip cannot install
+    the reference (no setup.py or pyproject.toml: a Bazel + Rust project), so the arm is built from its sources."""
+    import tempfile
+    exe = os.path.join(REF_DIR, "ref_driver")
+    if not os.path.isfile(exe):
+        try:
+            res = subprocess.run([sys.executable, os.path.join(ROOT, "baseline", "build_reference.py")],
+                                 capture_output=True, text=True, timeout=1500)
+            why = (res.stderr.strip().splitlines() or res.stdout.strip().splitlines() or ["?"])[-1]
+        except (OSError, subprocess.TimeoutExpired) as e:
+            why = str(e)
+        if not os.path.isfile(exe):
+            print(json.dumps({"impl": "reference", "unavailable": f"the reference could not be built here: {why}"[:300]}))
+            return 0
+    cfg = dict(TINYLLAMA, torch_dtype="float32", eos_token_id=None, attention_bias=False, rope_scaling=None)
+    pk = peaks()
+
+    def run(mode, *extra):
+        with tempfile.NamedTemporaryFile("w", suffix=".json", delete=False) as f:
+            json.dump(cfg, f)
+        try:
+            res = subprocess.run([exe, mode, "--config", f.name] + [str(x) for x in extra], capture_output=True, text=True, timeout=900)
+        finally:
+            os.unlink(f.name)
+        if res.returncode != 0:
+            raise RuntimeError((res.stderr.strip().splitlines() or ["ref_driver failed"])[-1])
+        return json.loads(res.stdout.strip().splitlines()[-1])
+
+    try:
+        sampler = ClockSampler().start()
+        main_run = run("bench", "--batch", BATCH, "--context", CONTEXT, "--steps", steps, "--warmup", warmup, "--repeats", REPEATS)
+        clocks = sampler.stop()
+        s = min(steps, 8)
+        points, notes = {}, {}
+        for b in (1, 16, 64):
+            try:
+                r = run("bench", "--batch", b, "--context", CONTEXT, "--steps", s, "--warmup", 3, "--repeats", 3)
+                points[f"decode_b{b}"] = round(b * 1e3 / r["ms_per_step_device"], 1)
+            except RuntimeError as e:   # (at batch 64 the reference's own memory planner gives up: "Bad virtual block.")
+                points[f"decode_b{b}"] = None
+                notes[f"decode_b{b}"] = f"the reference does not run this batch: {e}"[:200]
+        pre = run("prefill", "--tokens", 2048, "--repeats", 3)
+    except (RuntimeError, OSError, subprocess.TimeoutExpired, ValueError) as e:
+        print(json.dumps({"impl": "reference", "unavailable": f"the reference's engine did not run: {e}"[:300]}))
+        return 0
+    ms = main_run["ms_per_step_device"]
+    weights = 4 * sum((TINYLLAMA["hidden_size"] * (TINYLLAMA["num_attention_heads"] + 2 * TINYLLAMA["num_key_value_heads"]) * 64 +
+                       TINYLLAMA["hidden_size"] ** 2 + 3 * TINYLLAMA["hidden_size"] * TINYLLAMA["intermediate_size"]
+                       for _ in range(TINYLLAMA["num_hidden_layers"]))) + 4 * TINYLLAMA["hidden_size"] * TINYLLAMA["vocab_size"]
+    kv_per_token = 2 * TINYLLAMA["num_hidden_layers"] * TINYLLAMA["num_key_value_heads"] * 64 * 4
+    mean_ctx = CONTEXT - (REPEATS * steps) / 2.0
+    achieved = (weights + BATCH * mean_ctx * kv_per_token) / (ms * 1e-3) / 1e9
+    line = {
+        "metric": "decode tok/s at batch 8, context 2048 (TinyLlama-1.1B layer sizes)",
+        "value": round(BATCH * 1e3 / ms, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp32", "data": "synthetic", "impl": "reference",
+        "config": {"model": "TinyLlama-1.1B shape, random weights", "global_batch": BATCH, "seq_len": CONTEXT,
+                   "parallelism": "single GPU", "layers": 22, "layers_of_model": 22, "hidden_size": 2048, "heads": 32,
+                   "kv_heads": 4, "head_dim": 64, "intermediate_size": 5632, "vocab_size": 32000, "page_size": 32,
+                   "same_config": "sizes, batch and context as the other arm; float32 is the reference's only dtype, "
+                                  "32 tokens its only page size", "peaks": pk["source"], "repeats": REPEATS,
+                   "built_from": "unmodified tiny_llm/ sources, nvcc -arch=sm_100, driven by baseline/ref_driver.cpp"},
+        "e2e": {"value": round(BATCH * 1e3 / main_run["ms_per_step_wall"], 1), "unit": "tokens/s",
+                "ms_per_step": round(main_run["ms_per_step_wall"], 4), "h2d_bytes_per_step": main_run["h2d_bytes_per_step"],
+                "d2h_bytes_per_step": main_run["d2h_bytes_per_step"]},
+        "gpu_launches": None,
+        "prefill": {"value": round(2048 * 1e3 / pre["ms"], 1), "tokens": 2048, "ms": round(pre["ms"], 3), "frac": None},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points, "points_note": notes, "clocks": clocks,
+    }
+    print(json.dumps(line))
     return 0
 
 
@@ -324,7 +398,7 @@ def main():
     args = ap.parse_args()
     PAGE = args.page_size
     if args.impl == "reference":
-        return reference_arm()
+        return reference_arm(max(1, args.steps), max(3, args.warmup))
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported (run with --gpus 1)")
         return 2

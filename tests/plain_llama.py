@@ -6,9 +6,11 @@ file and lines it restates) and shares no code with the `tiny_llm_b200` package:
 plain torch tensor arithmetic on the CPU.
 
 tiny-llm's model math exists only as CUDA kernels (it has no CPU forward pass), so it cannot be
-imported or compiled into a CPU oracle; this file therefore rests on the formulas, and
-`tests/golden/make_golden.py` checks its parts against the golden tensors that tiny-llm ships
-for its own kernel tests (tests/datas/*.safetensors).
+imported or compiled into a CPU oracle.  Two anchors tie this file to it all the same:
+`tests/golden/make_golden.py` checks its parts against the golden tensors that tiny-llm ships for its
+own kernel tests (tests/datas/*.safetensors), and `tests/golden/reference_logits.safetensors` holds
+whole-model logits that tiny-llm's own engine computed on a B200 (prompt whole, then token by token,
+paged mode) for the tiny test configurations; tests/test_plain.py compares `forward` with them.
 
 `quant` is the storage rounding of the path that is being checked: the identity for the 32-bit
 path; for the bfloat16 path a round-trip through bfloat16 at the places where that path stores

@@ -76,3 +76,28 @@ def test_sampling_chain():
     assert pl.multinomial(torch.tensor([4, 7, 9]), torch.tensor([0.2, 0.5, 0.3]), 0.19) == 4
     assert pl.multinomial(torch.tensor([4, 7, 9]), torch.tensor([0.2, 0.5, 0.3]), 0.25) == 7
     assert pl.multinomial(torch.tensor([4, 7, 9]), torch.tensor([0.2, 0.5, 0.3]), 0.9999) == 9
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_whole_model_against_the_logits_of_tiny_llm_itself(name, tmp_path):
+    """tests/golden/reference_logits.safetensors holds what zscey/tiny-llm's own engine computes
+    (unmodified, run on a B200 through baseline/ref_driver.cpp; made by tests/golden/make_reference_logits.py)
+    for a short prompt run whole and six tokens decoded greedily one by one in paged mode, on the tiny
+    configurations with the weights write_random_model makes.  The plain implementation, whole sequence and
+    no cache, must give the same logits and choose the same ids: this pins the order of the parts
+    (norm, attention, residual, norm, SwiGLU, residual, final norm, output matrix), which the goldens of
+    single kernels cannot."""
+    import os
+    from conftest import TINY
+    from tiny_llm_b200.config import LlamaConfig
+    from tiny_llm_b200.weights import SafetensorsFile, write_random_model
+    gold = SafetensorsFile(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_logits.safetensors"))
+    cfg_d, _page, seed = TINY[name]
+    write_random_model(str(tmp_path), LlamaConfig.from_dict(cfg_d), seed=seed, dtype=torch.float32)
+    cfg, w = pl.load_config(str(tmp_path)), pl.load_weights(str(tmp_path))
+    prompt, ids, want = gold.get(f"{name}.prompt").tolist(), gold.get(f"{name}.ids").tolist(), gold.get(f"{name}.logits").clone()
+    gold.close()
+    logits = pl.forward(cfg, w, prompt + ids)
+    rows = logits[len(prompt) - 1: len(prompt) - 1 + want.shape[0]]
+    assert float((rows - want).abs().max()) <= 2e-5, float((rows - want).abs().max())
+    assert [pl.greedy(r) for r in rows[:-1]] == ids
