@@ -15,6 +15,10 @@
 //   ref_driver logits --model DIR --tokens 1,2,3,... --decode N --out FILE
 //       prompt whole, then N greedy tokens; writes the float32 logits of the prompt's last position and
 //       of every decoded position ([1 + N, vocab]) and prints the chosen ids.
+//   ref_driver graph --config CONFIG.json
+//       prints the graph the reference's llama_parser builds (paged mode) as JSON: its nodes in order with
+//       their kind and tensor names, and the tensors nothing produces (weights and inputs) with their shapes.
+//       Needs no GPU.
 #include <algorithm>
 #include <chrono>
 #include <cstdio>
@@ -30,6 +34,7 @@
 #include "cuda_runtime.h"
 #include "nlohmann/json.hpp"
 #include "tiny_llm/device_managers/cuda/cuda_device_guard.hpp"
+#include "tiny_llm/graph/graph.hpp"
 #include "tiny_llm/logit_processors/argmax_processor.hpp"
 #include "tiny_llm/parser/llama_parser.hpp"
 #include "tiny_llm/runtime/cuda/cuda_runtime.hpp"
@@ -304,6 +309,33 @@ auto run_prefill(const Args &a) -> int {
   return 0;
 }
 
+auto run_graph(const Args &a) -> int {
+  std::ifstream f(a.get("config"));
+  auto config = nlohmann::json::parse(f);
+  const tiny_llm::Graph g = tiny_llm::llama_parser(config, true);
+  static const char *kinds[] = {"silu", "embedding", "rope", "rms_norm", "add", "mul", "linear", "causal_attention", "slice_linear"};
+  nlohmann::json out;
+  out["valid"] = tiny_llm::is_valid(g);
+  auto names = [&g](const std::vector<uint32_t> &ids) {
+    std::vector<std::string> r;
+    for (auto id : ids) r.push_back(g.tensor_infos.at(id)->first);
+    return r;
+  };
+  out["nodes"] = nlohmann::json::array();
+  for (const auto &n : g.nodes) {
+    if (!n) continue;
+    out["nodes"].push_back({{"name", n->first}, {"kind", kinds[n->second.param.index()]},
+                            {"inputs", names(n->second.input_tensors)}, {"outputs", names(n->second.output_tensors)}});
+  }
+  out["sources"] = nlohmann::json::object();
+  for (const auto &t : g.tensor_infos)
+    if (t && !t->second.producer_node) out["sources"][t->first] = t->second.shape;
+  out["inputs"] = std::vector<std::string>(g.input_names.begin(), g.input_names.end());
+  out["outputs"] = std::vector<std::string>(g.output_names.begin(), g.output_names.end());
+  std::cout << out.dump() << "\n";
+  return 0;
+}
+
 auto run_logits(const Args &a) -> int {
   const std::string dir = a.get("model");
   std::ifstream f(dir + "/config.json");
@@ -341,8 +373,9 @@ auto main(int argc, char **argv) -> int {
   Args a;
   for (int i = 2; i + 1 < argc; i += 2) a.kv[std::string(argv[i]).substr(2)] = argv[i + 1];
   try {
-    tiny_llm::CudaDeviceSwitchGuard guard(static_cast<tiny_llm::DeviceId>(a.num("device", 0)));
     const std::string mode = argv[1];
+    if (mode == "graph") return run_graph(a);
+    tiny_llm::CudaDeviceSwitchGuard guard(static_cast<tiny_llm::DeviceId>(a.num("device", 0)));
     if (mode == "bench") return run_bench(a);
     if (mode == "prefill") return run_prefill(a);
     if (mode == "logits") return run_logits(a);

@@ -107,6 +107,38 @@ def check_attention_block(ref_root):
     return float((out - g).abs().max()), table_diff, float(g.abs().max())
 
 
+def iramp(n):
+    return (torch.arange(n, dtype=torch.int64) % 100).to(torch.float32)
+
+
+def check_gemm(ref_root):
+    # tests/ops/cuda/test_gemm.cpp:160-199: C = A W^T with integer ramps (every sum is exact in 32-bit)
+    m, d, n = 127, 255, 353
+    out = pl.linear(iramp(m * d).view(m, d), iramp(n * d).view(n, d))
+    return float((out - golden(ref_root, "gemm_m127d255n353.safetensors").view(m, n)).abs().max())
+
+
+def check_gemm_to_heads(ref_root):
+    # tests/ops/cuda/test_gemm.cpp:201-260: the projection whose result goes head-major into rows
+    # [q_start, q_start + q) of a [b, heads, q_end, dim] buffer that held ones (the reference's Q projection)
+    b, q, d, heads, dim, q_start = 2, 61, 255, 4, 88, 3
+    q_end = q_start + q + 13
+    y = pl.linear(iramp(b * q * d).view(b, q, d), iramp(heads * dim * d).view(heads * dim, d))   # [b, q, heads * dim]
+    dst = torch.ones(b, heads, q_end, dim)
+    dst[:, :, q_start:q_start + q, :] = y.view(b, q, heads, dim).permute(0, 2, 1, 3)
+    g = golden(ref_root, "gemm_b2q61d255oh4od88qs3qe77.safetensors").view(b, heads, q_end, dim)
+    return float((dst - g).abs().max())
+
+
+def check_gemm_from_heads(ref_root):
+    # tests/ops/cuda/test_gemm.cpp:262-306: head-major [b, heads, q, d] rows joined per token, then the
+    # product (the reference's output projection)
+    b, h, q, d, out_d = 2, 4, 127, 61, 313
+    x = iramp(b * h * q * d).view(b, h, q, d).permute(0, 2, 1, 3).reshape(b, q, h * d)
+    out = pl.linear(x, iramp(out_d * h * d).view(out_d, h * d))
+    return float((out - golden(ref_root, "gemm_b2h4q127d61od313.safetensors").view(b, q, out_d)).abs().max())
+
+
 def main():
     ref_root = sys.argv[1] if len(sys.argv) > 1 else os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "..", "reference")
     block, table, scale = check_attention_block(ref_root)
@@ -116,6 +148,9 @@ def main():
         "apply_rope_b3_h4_q2_d96": check_apply_rope(ref_root),
         "attn_nomask_b2q107h4k123h2d61": check_attention(ref_root, False),
         "attn_causal_b2l107q4k2d61": check_attention(ref_root, True),
+        "gemm_m127d255n353": check_gemm(ref_root),
+        "gemm_to_heads_b2q61d255oh4od88qs3qe77": check_gemm_to_heads(ref_root),
+        "gemm_from_heads_b2h4q127d61od313": check_gemm_from_heads(ref_root),
         "llama_attn_block_b1q5h2048": block,
         "llama_attn_block_tables": table,
         "llama_attn_block_max_abs_of_golden": scale,
