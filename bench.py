@@ -393,6 +393,8 @@ def main():
                     help="measure one part only (for profiler captures of a small case)")
     ap.add_argument("--batch", type=int, default=BATCH, help="requests of the decode step (default 8)")
     ap.add_argument("--page-size", type=int, default=PAGE, help="tokens per page of the cache")
+    ap.add_argument("--shape", default="tinyllama", choices=["tinyllama"] + list(OTHER_SHAPES),
+                    help="layer sizes for --only runs (profiler captures of the other models' kernels)")
     ap.add_argument("--quick", action="store_true",
                     help="leave out the workload points and the Llama-2-7B / Llama-3-8B layer sizes")
     args = ap.parse_args()
@@ -411,7 +413,11 @@ def main():
     device = "cuda:0"
     torch.cuda.set_device(0)
     pk = peaks()
-    cfg, model = build_model(args.layers, dtype, device)
+    if args.shape != "tinyllama" and args.only == "all":
+        print("--shape goes with --only decode|prefill (the full run measures every shape)")
+        return 2
+    shape, seed = (TINYLLAMA, 2) if args.shape == "tinyllama" else OTHER_SHAPES[args.shape]
+    cfg, model = build_model(min(args.layers, shape["num_hidden_layers"]), dtype, device, shape=shape, seed=seed)
     itemsize = 2 if dtype == torch.bfloat16 else 4
     start_len = CONTEXT - (REPEATS * steps + warmup)   # the last timed step writes position CONTEXT - 1
     if start_len < 64:
@@ -425,16 +431,16 @@ def main():
         # a small, single-purpose run for a profiler capture: one plain line, no record
         if args.only == "decode":
             ms, launched, _ = timed_decode(runner, args.batch, CONTEXT - (steps + warmup), steps, warmup, out)
-            rec = {"only": "decode", "batch": args.batch, "layers": args.layers, "ms_per_step": round(ms, 4),
-                   "gpu_launches": launched}
+            rec = {"only": "decode", "shape": args.shape, "batch": args.batch, "layers": cfg.num_hidden_layers,
+                   "ms_per_step": round(ms, 4), "gpu_launches": launched}
             if TRACE:
                 rec["timeline"] = timeline_summary(timed_decode.timeline)
             print(json.dumps(rec))
         else:
-            ops.attention_tc_timing()   # (a build with cycle counters: start from zero)
-            rec = {"only": "prefill", "layers": args.layers, "tokens": 2048,
+            ops.attention_tc_timing(cfg.head_dim)   # (a build with cycle counters: start from zero)
+            rec = {"only": "prefill", "shape": args.shape, "layers": cfg.num_hidden_layers, "tokens": 2048,
                    "ms": round(timed_prefill(runner, 2048, repeats=2), 3)}
-            cycles = ops.attention_tc_timing()
+            cycles = ops.attention_tc_timing(cfg.head_dim)
             if cycles is not None:
                 # cycles per key tile in the roles of the attention kernel's first CTA, which walks 2048 / 64 tiles
                 tiles = (2048 // 64) * args.layers * 4

@@ -458,10 +458,12 @@ def paged_attention(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_d
         ctypes.c_float(scale), int(window or 0), _code(qkv.dtype), _stream()))
 
 
-def attention_tc_timing() -> Optional[dict]:
+def attention_tc_timing(head_dim: int = 64) -> Optional[dict]:
     """Cycles that the roles of the prompt-attention kernel's first CTA spent per phase since the last call, or
     None if the kernel was not built with TLLM_NVCC_FLAGS_ATTENTION_TC=-DTLLM_ATT_TIMING=1."""
-    lib = build.load_library("attention_tc", flags=("-DTLLM_HEAD_DIM=64",))
+    if head_dim not in ATTENTION_TC_HEAD_DIMS:
+        return None
+    lib = build.load_library("attention_tc", flags=(f"-DTLLM_HEAD_DIM={head_dim}",))
     if not hasattr(lib, "tllm_attention_tc_timing"):
         return None
     out = (ctypes.c_ulonglong * 16)()
