@@ -231,6 +231,7 @@ def timed_e2e(pipe, batch, context, steps, warmup, repeats=1):
         torch.cuda.synchronize()
         times.append((time.perf_counter() - t0) * 1e3 / steps)
         assert len(pipe.scheduler.running) == batch      # nobody ended inside the timed steps
+    timed_e2e.h2d_bytes = pipe.runner.last_h2d_bytes     # of a timed step: tokens, positions, request and block tables
     while pipe.has_work():
         pipe.step()
     return statistics.median(times)
@@ -464,7 +465,7 @@ def main():
     pipe = Pipeline.from_model(cfg, model, dtype=dtype, device=0, page_size=PAGE, max_tokens=BATCH * CONTEXT,
                                max_requests=BATCH, max_tokens_per_step=2048, chunk=1024)
     e2e_ms = timed_e2e(pipe, BATCH, CONTEXT, steps, warmup, repeats=REPEATS)
-    h2d = 4 * (3 * BATCH + (BATCH + 1) + 3 * BATCH + BATCH + BATCH + BATCH * pipe.runner.max_blocks)
+    h2d = timed_e2e.h2d_bytes
     del pipe
 
     # the stated workload of the model's benchmark: 512-token prompts + 256 generated tokens through the entry

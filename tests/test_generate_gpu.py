@@ -43,6 +43,7 @@ def test_greedy_generation_through_the_entry_point(model_dirs, name, dtype):
                     max_tokens_per_step=24, chunk=5)
     out = pipe.apply(prompts, max_new_tokens=16, do_sample=False, ignore_eos=True)
     assert [len(o) for o in out] == [16] * 4
+    assert pipe.counters["chained"] > 0 and pipe.runner.graph_replays > 0   # decode steps ran ahead of the host, as graphs
     cfg, w, quant = plain_model(model_dirs[name], dtype)
     for p, o in zip(prompts, out):
         check_greedy(cfg, w, quant, dtype, p, o)
@@ -99,12 +100,17 @@ def test_temperature_sampling_is_seeded_and_follows_the_chain(model_dirs, name):
 
 
 def test_eos_ends_a_request(model_dirs):
+    """Wherever the end-of-sequence id falls, the last two places included: there the chained step that ran
+    too far has already ended the request by length when the id is read."""
     from tiny_llm_b200 import Pipeline
     pipe = Pipeline(model_dirs["A"], dtype="float32", max_tokens=512, max_requests=2)
     free = pipe.apply([[9, 8, 7]], max_new_tokens=12, do_sample=False, ignore_eos=True)[0]
-    pipe.scheduler.eos = {free[4]}
-    cut = pipe.apply([[9, 8, 7]], max_new_tokens=12, do_sample=False)[0]
-    assert cut == free[: free.index(free[4]) + 1]
+    assert pipe.counters["chained"] > 0
+    for at in (4, 10, 11):
+        pipe.scheduler.eos = {free[at]}
+        cut = pipe.apply([[9, 8, 7]], max_new_tokens=12, do_sample=False)[0]
+        assert cut == free[: free.index(free[at]) + 1], at
+        assert pipe.runner.cache.groups[0].pool.num_used == 0
 
 
 def test_command_line(model_dirs):

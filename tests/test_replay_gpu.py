@@ -115,3 +115,68 @@ def test_step_refuses_what_it_cannot_hold(cases):
         runner.step([StepEntry("b", [cfg["vocab_size"]], [0])])
     with pytest.raises(KeyError):
         runner.step([StepEntry("nobody", [1], [0])])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_request_id_that_lives_twice_decodes_from_its_new_pages(cases, dtype):
+    """Steps in which every request brings one token take their block tables from rows kept per request
+    id.  An id that ends and comes back holds other pages: its kept row must not survive it."""
+    from tiny_llm_b200.engine import StepEntry
+    model_dir, cfg, page, _, _ = cases["A"]
+    reqs = ru.make_requests(cfg["vocab_size"], [40, 50, 21], 123)       # first life of x, second life of x, y
+    names = {"x1": reqs["r0"], "x2": reqs["r1"], "y": reqs["r2"]}
+    ref = ru.plain_logits(model_dir, names, dtype)
+    ref32 = ref if dtype == "float32" else ru.plain_logits(model_dir, names, "float32")
+    runner = runner_for(model_dir, dtype, page, 192)
+    cache = runner.cache
+
+    def live(rid, toks, tail, beside=None):
+        """The request's prompt in one step, its last `tail` tokens one by one (alone, or beside `beside`)."""
+        cache.add_request(rid)
+        head = len(toks) - tail
+        rows = [runner.step([StepEntry(rid, toks[:head], range(head))]).cpu().clone()]
+        for i in range(head, len(toks)):
+            entries = [StepEntry(rid, [toks[i]], [0])]
+            if beside is not None:
+                entries.append(StepEntry(beside[0], [beside[1].pop(0)], [0]))
+            rows.append(runner.step(entries).cpu()[:1].clone())
+        return torch.cat(rows), list(cache.block_table(0, rid))
+
+    got1, pages1 = live("x", names["x1"], 10)
+    cache.free_request("x")
+    cache.add_request("y")                                   # y takes the pages x gave back
+    runner.step([StepEntry("y", names["y"][:12], [])])
+    y_rest = list(names["y"][12:])
+    got2, pages2 = live("x", names["x2"], 9, beside=("y", y_rest))   # x again, other pages, decoding beside y
+    assert pages1[: len(pages2)] != pages2[: len(pages1)] and set(pages2).isdisjoint(cache.block_table(0, "y"))
+    assert runner.graph_replays > 0
+    cache.free_request("x"), cache.free_request("y")
+    ru.compare({"ax1": got1, "ax2": got2}, {"x1": ref["x1"], "x2": ref["x2"]}, "a", dtype, "a request id that lives twice",
+               {"x1": ref32["x1"], "x2": ref32["x2"]})
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_decoding_across_a_graph_bucket_of_the_context(tmp_path_factory, dtype):
+    """Replayed graphs are keyed by the power-of-two bucket of the longest context (256, 512, ...): a request
+    decodes from 247 to 275 tokens, across the edge, beside a short one (whose key slices are empty in the
+    larger bucket)."""
+    from conftest import TINY_A
+    from tiny_llm_b200.config import LlamaConfig
+    from tiny_llm_b200.weights import write_random_model
+    cfg = dict(TINY_A, max_position_embeddings=1024)
+    d = str(tmp_path_factory.mktemp("tiny_long"))
+    write_random_model(d, LlamaConfig.from_dict(cfg), seed=7, dtype=torch.float32)
+    reqs = ru.make_requests(cfg["vocab_size"], [275, 40], 5)
+    ref = ru.plain_logits(d, reqs, dtype)
+    ref32 = ref if dtype == "float32" else ru.plain_logits(d, reqs, "float32")
+    long_t, short_t = reqs["r0"], reqs["r1"]
+    steps = [{"entries": [{"id": "gr0", "tokens": long_t[:247], "want": list(range(247))},
+                          {"id": "gr1", "tokens": short_t[:12], "want": list(range(12))}], "end": []}]
+    for i in range(28):
+        steps.append({"entries": [{"id": "gr0", "tokens": [long_t[247 + i]], "want": [0]},
+                                  {"id": "gr1", "tokens": [short_t[12 + i]], "want": [0]}],
+                      "end": ["gr0", "gr1"] if i == 27 else []})
+    runner = runner_for(d, dtype, 16, 384)
+    got = ru.run_trace_runner(runner, steps, cfg["vocab_size"])
+    assert runner.graph_replays >= 20 and len(runner._graphs) == 2       # one graph per bucket, both replayed
+    ru.compare(got, ref, "g", dtype, "decoding across a graph bucket", ref32)

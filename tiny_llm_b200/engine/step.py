@@ -128,6 +128,7 @@ class ModelRunner:
         for gi in range(g):
             self._off[f"block_table{gi}"] = (cur, r * self.max_blocks)
             cur += r * self.max_blocks
+        cur += 4 * (10 + 2 * g)      # room for the 16-byte alignment of the packed layout of one-token steps
         self._meta_words = cur
         # The host side of the metadata is a ring of pinned buffers: the copy to the device is
         # asynchronous, and a caller that enqueues steps without waiting for them must not overwrite a
@@ -143,6 +144,8 @@ class ModelRunner:
         self._graphs = {}
         self._graph_seen = set()
         self._table_rows = {}
+        self._decode_layouts = {}
+        self.last_h2d_bytes = 0     # bytes of the last step's metadata copy to the device
         self.graph_replays = 0
 
     # ---- metadata
@@ -237,6 +240,7 @@ class ModelRunner:
             group_hosts.append((sm, bt))
             used_words = self._off[f"block_table{gi}"][0] + r * max_blocks
         # one copy, host to device
+        self.last_h2d_bytes = 4 * used_words
         self._dev_meta[:used_words].copy_(host_meta[:used_words], non_blocking=True)
         if self.device.type == "cuda":
             if self._staging_done[slot] is None:
@@ -277,28 +281,52 @@ class ModelRunner:
             held[1] = len(table)
         return row
 
+    def _decode_layout(self, r: int):
+        """Where the regions lie in a step of r one-token requests: the same order as the general layout, but
+        sized for r and packed from the start of the buffer (each region on a 16-byte boundary), so that the
+        copy to the device is as long as the step's own tables and not as the largest step's.  The layout
+        depends on r alone, which is also what a captured graph of such a step is keyed by."""
+        lay = self._decode_layouts.get(r)
+        if lay is None:
+            lay, cur = {}, 0
+            names = [("tokens", r), ("positions", r), ("token_request", r), ("cu_q", r + 1), ("q_start", r), ("kv_len", r),
+                     ("slots", r), ("logit_rows", r)]
+            names += [(f"slot_mapping{gi}", r) for gi in range(len(self.cache.groups))]
+            names += [(f"block_table{gi}", r * self.max_blocks) for gi in range(len(self.cache.groups))]
+            for name, n in names:
+                lay[name] = (cur, n)
+                cur += -(-n // 4) * 4
+            lay["_words"] = cur
+            self._decode_layouts[r] = lay
+        return lay
+
     def _build_decode_batch(self, entries, starts, host_meta, host, slot, device_tokens=None) -> StepBatch:
-        """The common step: every request brings one token.  Same layout as the general path, filled
-        with whole-array writes; block tables come from rows cached per request."""
+        """The common step: every request brings one token.  Filled with whole-array writes; block tables
+        come from rows cached per request; the regions are packed (see _decode_layout)."""
         cache = self.cache
         r = len(entries)
+        lay = self._decode_layout(r)
+
+        def region(buf, name, n=None):
+            off, cap = lay[name]
+            return buf[off: off + (cap if n is None else n)]
+
         starts_np = np.asarray(starts, dtype=np.int64)
-        self._region(host, "tokens", r)[:] = [e.tokens[0] for e in entries]
-        self._region(host, "positions", r)[:] = starts_np
-        self._region(host, "token_request", r)[:] = np.arange(r)
-        self._region(host, "cu_q", r + 1)[:] = np.arange(r + 1)
-        self._region(host, "q_start", r)[:] = starts_np
-        self._region(host, "kv_len", r)[:] = starts_np + 1
-        self._region(host, "slots", r)[:] = [cache.slot_of(e.rid) for e in entries]
+        region(host, "tokens")[:] = [e.tokens[0] for e in entries]
+        region(host, "positions")[:] = starts_np
+        region(host, "token_request")[:] = np.arange(r)
+        region(host, "cu_q")[:] = np.arange(r + 1)
+        region(host, "q_start")[:] = starts_np
+        region(host, "kv_len")[:] = starts_np + 1
+        region(host, "slots")[:] = [cache.slot_of(e.rid) for e in entries]
         rows = [i for i, e in enumerate(entries) if len(e.want)]
         n_out = len(rows)
         if n_out:
-            self._region(host, "logit_rows", n_out)[:] = rows
+            region(host, "logit_rows", n_out)[:] = rows
         max_blocks = self.max_blocks
-        used_words = 0
         for gi, g in enumerate(cache.groups):
-            sm = self._region(host, f"slot_mapping{gi}", r)
-            bt = self._region(host, f"block_table{gi}", r * max_blocks).reshape(r, max_blocks)
+            sm = region(host, f"slot_mapping{gi}")
+            bt = region(host, f"block_table{gi}").reshape(r, max_blocks)
             windowed = g.need.window is not None
             for i, e in enumerate(entries):
                 table = cache.block_table(gi, e.rid)
@@ -312,9 +340,8 @@ class ModelRunner:
             if (pages < 0).any():
                 raise RuntimeError("a request writes into a page it has given back")
             sm[:] = pages * g.page_size + starts_np % g.page_size
-            used_words = self._off[f"block_table{gi}"][0] + r * max_blocks
-        if not cache.groups:
-            used_words = self._off["logit_rows"][0] + self._off["logit_rows"][1]
+        used_words = lay["_words"]
+        self.last_h2d_bytes = 4 * used_words
         self._dev_meta[:used_words].copy_(host_meta[:used_words], non_blocking=True)
         if self.device.type == "cuda":
             if self._staging_done[slot] is None:
@@ -322,17 +349,17 @@ class ModelRunner:
             self._staging_done[slot].record()
         dev = self._dev_meta
         if device_tokens is not None:   # the ids were chosen on the device and have not been to the host yet
-            self._region(dev, "tokens", r).copy_(device_tokens[:r], non_blocking=True)
-        groups = [GroupMeta(block_table=self._region(dev, f"block_table{gi}", r * max_blocks).view(r, max_blocks),
-                            slot_mapping=self._region(dev, f"slot_mapping{gi}", r), max_blocks=max_blocks)
+            region(dev, "tokens").copy_(device_tokens[:r], non_blocking=True)
+        groups = [GroupMeta(block_table=region(dev, f"block_table{gi}").view(r, max_blocks),
+                            slot_mapping=region(dev, f"slot_mapping{gi}"), max_blocks=max_blocks)
                   for gi in range(len(cache.groups))]
         kv_after = [s + 1 for s in starts]
         return StepBatch(
             num_tokens=r, num_requests=r, num_logits=n_out,
-            tokens=self._region(dev, "tokens", r), positions=self._region(dev, "positions", r),
-            token_request=self._region(dev, "token_request", r), cu_q=self._region(dev, "cu_q", r + 1),
-            q_start=self._region(dev, "q_start", r), kv_len=self._region(dev, "kv_len", r),
-            slots=self._region(dev, "slots", r), logit_rows=self._region(dev, "logit_rows", n_out),
+            tokens=region(dev, "tokens"), positions=region(dev, "positions"),
+            token_request=region(dev, "token_request"), cu_q=region(dev, "cu_q"),
+            q_start=region(dev, "q_start"), kv_len=region(dev, "kv_len"),
+            slots=region(dev, "slots"), logit_rows=region(dev, "logit_rows", n_out),
             groups=groups, max_q_len=1, max_kv_len=max(kv_after), host_q_lens=[1] * r, host_kv_lens=kv_after)
 
     # ---- the step
