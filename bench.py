@@ -288,6 +288,11 @@ def other_shape_points(name, shape, seed, dtype, device, pk, steps, out, points,
         ms, _, ctx = timed_decode(runner, b, CONTEXT - (3 * s + 3), s, 3, out, repeats=3)
         points[f"{name}_decode_b{b}"] = round(b * 1e3 / ms, 1)
         fracs[f"{name}_decode_b{b}"] = round(decode_bytes(model, runner, b, ctx, itemsize) / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+    long_ctx = min(cfg.max_position_embeddings, 8192)
+    if long_ctx > CONTEXT:   # a longer context where the model has the positions: 16 requests at 8,192 tokens
+        ms, _, ctx = timed_decode(runner, 16, long_ctx - (3 * s + 3), s, 3, out, repeats=3)
+        points[f"{name}_decode_b16_ctx{long_ctx}"] = round(16 * 1e3 / ms, 1)
+        fracs[f"{name}_decode_b16_ctx{long_ctx}"] = round(decode_bytes(model, runner, 16, ctx, itemsize) / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
     ms = timed_prefill(runner, 2048, repeats=3)
     points[f"{name}_prefill_2048"] = round(2048 * 1e3 / ms, 1)
     if dtype == torch.bfloat16:

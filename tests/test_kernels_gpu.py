@@ -384,6 +384,51 @@ def test_decode_attention_over_long_contexts(ops, hd, nq, nkv, q_len, lens, wind
         assert float(p[far]) > 0.9
 
 
+@pytest.mark.parametrize("hd,nq,nkv", [(64, 8, 2), (128, 4, 1)])
+def test_attention_beyond_the_block_table_entries_kept_in_shared_memory(ops, hd, nq, nkv):
+    """Contexts of 9,000 keys in pages of 8: 1,125 block-table entries per request, more than the kernels stage in
+    shared memory (512 for the mma.sync kernels, 1,024 for the tcgen05 kernel), so the later entries come
+    from global memory.  A portion of 300 tokens at the end of one request (tcgen05), a decoded token of another
+    (key slices), and a far key at the very beginning and one past entry 1,024."""
+    from tiny_llm_b200.engine import Workspace
+    dtype, page = "bfloat16", 8
+    lens = [9000, 8200]
+    table, k_cache, v_cache, ks, vs = paged_setup(dtype, 2, lens, nkv, hd, page, seed=hd)
+    g = torch.Generator().manual_seed(31)
+    scale = 1.0 / math.sqrt(hd)
+    for q_lens in ([300, 0], [0, 1]):                       # the portion alone (tcgen05), then the decoded token alone
+        live = [r for r in range(2) if q_lens[r]]
+        t = sum(q_lens)
+        qkv = torch.randn(t, (nq + 2 * nkv) * hd, generator=g).to(DT[dtype])
+        r = live[0]
+        for key in (2, 8600 if r == 0 else 8195):             # standout keys: block 0, and a block past the staged entries
+            row = (t - 1) if key == 2 else max(0, t - 2)
+            head = 0 if key == 2 else (1 if nq > 1 else 0)
+            qkv[row, head * hd:(head + 1) * hd] *= 6.0
+            kvh = head // (nq // nkv)
+            qv = qkv[row, head * hd:(head + 1) * hd]
+            ks[r][key, kvh] = (qv / qv.float().norm() * 8.0).to(DT[dtype])
+            k_cache[int(table[r, key // page]), kvh, key % page] = ks[r][key, kvh]
+        n = q_lens[r]
+        pos = torch.arange(lens[r] - n, lens[r], dtype=torch.int32)
+        batch = types.SimpleNamespace(token_request=torch.zeros(n, dtype=torch.int32, device=DEV), positions=pos.to(DEV),
+                                      cu_q=torch.tensor([0, n], dtype=torch.int32, device=DEV),
+                                      q_start=torch.tensor([lens[r] - n], dtype=torch.int32, device=DEV),
+                                      num_requests=1, max_q_len=n, max_kv_len=lens[r])
+        out = torch.full((n, nq * hd), float("nan"), dtype=DT[dtype], device=DEV)
+        ops.paged_attention(qkv.to(DEV), nq, nkv, hd, k_cache.to(DEV), v_cache.to(DEV), table[r: r + 1].contiguous().to(DEV),
+                            batch, out, scale, None, Workspace(DEV))
+        ops.check_status()
+        out = out.float().cpu()
+        assert not torch.isnan(out).any()
+        q = qkv[:, : nq * hd].float().view(n, nq, hd)
+        ref = pl.attention(q, ks[r].float(), vs[r].float(), pos, quant=pl.bf16_quant).reshape(n, nq * hd)
+        d = float((out - ref).abs().max())
+        assert d <= tol(dtype, max(1.0, float(ref.abs().max()))), (q_lens, d)
+        p0 = torch.softmax((qkv[n - 1, :hd].float() * scale) @ ks[r][:lens[r], 0].float().t(), 0)
+        assert float(p0[2]) > 0.9                             # the far key carries its query
+
+
 def test_products_at_the_sizes_of_a_2048_token_prompt(ops):
     """The persistent 128 x 256 kernel over several rounds of tiles at the TinyLlama layer sizes: gate/up
     with SiLU * up in its epilogue (2,048 x 11,264 x 2,048) and the down projection adding into the
