@@ -321,6 +321,7 @@ def _lens64():
     return [2048, 2047, 1, 64, 65] + torch.randint(1, 2049, (59,), generator=g).tolist()
 
 
+@pytest.mark.parametrize("wide", [False, True])
 @pytest.mark.parametrize("bucket", [False, True])
 @pytest.mark.parametrize("hd,nq,nkv,q_len,lens,window,page", [
     (64, 32, 4, 1, [2048], None, 16),          # batch 1 at the longest context: the most key slices
@@ -332,12 +333,14 @@ def _lens64():
     (64, 4, 2, 1, _lens64(), None, 16),        # batch 64
     (128, 2, 1, 1, _lens64(), 500, 16),
 ], ids=["b1", "b8", "b8-q2-window", "b8-mha-hd128", "b3-hd128-page32", "b8-q4-hd128", "b64", "b64-hd128-window"])
-def test_decode_attention_over_long_contexts(ops, hd, nq, nkv, q_len, lens, window, page, bucket):
-    """Every request brings q_len tokens (q_len x group <= 16), so the decode kernel and the merge of its key
+def test_decode_attention_over_long_contexts(ops, hd, nq, nkv, q_len, lens, window, page, bucket, wide, monkeypatch):
+    """Every request brings q_len tokens (q_len x group <= 16), so the decode kernels and the merge of their key
     slices run, with the slice count the engine itself picks for these sizes; `bucket` hands the kernel
     the power-of-two bucket of the longest context, as a replayed graph does, so that short requests
-    have empty slices.  Unwritten slots of the pages are NaN; one key far back carries a query."""
+    have empty slices; `wide` takes the kernel with one warp per tile wherever the head size lets it (else the
+    kernel that walks a slice tile by tile).  Unwritten slots of the pages are NaN; one key far back carries a query."""
     from tiny_llm_b200.engine import Workspace
+    monkeypatch.setattr(ops, "decode_wide_ctas", (1, 1 << 30) if wide else (1, 0))
     dtype = "bfloat16"
     n_req = len(lens)
     lens = [max(l, q_len) for l in lens]

@@ -237,6 +237,15 @@ attention_decode_kernel(const AttnParams p) {
                                 [] { pdl_wait(); });
 }
 
+// Decoded tokens over short slices (at most four tiles each): one warp per tile.
+constexpr int WIDE_SMEM = (16 + 4 * 2 * BN) * LDS * 2 + TABLE_SLOTS * 4;
+__global__ void __launch_bounds__(128)
+attention_decode_wide_kernel(const AttnParams p) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  pdl_trigger();
+  attention_decode_item_wide(p, blockIdx.x, blockIdx.y, blockIdx.z, threadIdx.x, smem_raw, [] { pdl_wait(); });
+}
+
 // Merges the slices of every (token, head), one warp each.
 __global__ void __launch_bounds__(128)
 attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
@@ -254,6 +263,12 @@ using namespace tllm;
 
 extern "C" int tllm_attention_head_dim() { return HD; }
 
+// 1 if the kernel with one warp per tile can run at this head size: its per-warp buffers must leave room for two
+// CTAs on an SM, and the merge buffers must fit them.
+extern "C" int tllm_attention_mma_wide_fits() {
+  return WIDE_SMEM <= 113 * 1024 && 4 * 16 * (HD + 2) * 4 <= 4 * 2 * BN * LDS * 2;
+}
+
 // Bytes of scratch (float32 partials) a call with these sizes needs; 0 when splits == 1.
 extern "C" long long tllm_attention_mma_scratch_bytes(int n_tokens, int nq, int splits) {
   return splits <= 1 ? 0 : (long long)n_tokens * nq * splits * (HD + 2) * 4;
@@ -263,7 +278,7 @@ extern "C" int tllm_attention_mma(const void* q, int q_row_stride, const void* k
                                   const int* block_table, int max_blocks, const int* cu_q, const int* q_start,
                                   void* out, int n_tokens, int n_requests, int max_q_len, int nq, int nkv, int hd,
                                   int page_size, long long page_stride, long long head_stride, float scale, int window,
-                                  int splits, void* scratch, void* stream) {
+                                  int splits, void* scratch, int wide, int max_kv_len, void* stream) {
   TLLM_REQUIRE(hd == HD, "attention_mma: built for head size %d, called with %d", HD, hd);
   TLLM_REQUIRE(n_tokens > 0 && n_requests > 0 && max_q_len > 0 && nq > 0 && nkv > 0 && nq % nkv == 0,
                "attention_mma: %d tokens, %d requests, %d heads, %d key/value heads", n_tokens, n_requests, nq, nkv);
@@ -288,7 +303,20 @@ extern "C" int tllm_attention_mma(const void* q, int q_row_stride, const void* k
   const long long gx = (long long)n_requests * p.tiles_per_req;
   TLLM_REQUIRE(gx <= 2147483647LL, "attention_mma: grid too large");
   cudaStream_t s = (cudaStream_t)stream;
-  if (small) {
+  // wide != 0 (decoded tokens only): every slice has at most four tiles for the longest context of the step, and one
+  // warp takes each (tllm_attention_mma_wide_fits says whether this head size leaves room for two such CTAs on an SM)
+  if (wide) {
+    TLLM_REQUIRE(small && tllm_attention_mma_wide_fits() && max_kv_len > 0 && ((max_kv_len + BN - 1) / BN + splits - 1) / splits <= 4,
+                 "attention_mma: one warp per tile needs decoded tokens and slices of at most four tiles (%d keys in %d slices)",
+                 max_kv_len, splits);
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(attention_decode_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WIDE_SMEM);
+      if (e != cudaSuccess) TLLM_FAIL(TLLM_ERR_CUDA, "attention_mma: cannot reserve %d bytes of shared memory: %s", WIDE_SMEM, cudaGetErrorString(e));
+      configured = true;
+    }
+    TLLM_LAUNCH("attention_decode_wide", attention_decode_wide_kernel, dim3((unsigned)n_requests, nkv, splits), 128, WIDE_SMEM, s, p);
+  } else if (small) {
     constexpr int ST = 3;
     // the merge buffers (4 x 16 x (HD + 2) floats) reuse the tile stages
     static_assert(4 * 16 * (HD + 2) * 4 <= ST * BN * LDS * 2, "merge buffers must fit the key stages");

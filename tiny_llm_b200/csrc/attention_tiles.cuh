@@ -337,6 +337,207 @@ __device__ __forceinline__ void attention_decode_item(const AttnParams& p, int r
   trace_mark(2);       // merged and written
 }
 
+// One warp's share of a tile loader: the 64 key rows and 64 value rows of the tile at j0, gathered by the 32 lanes
+// of ONE warp into its own buffers (four passes of 32 rows; within a pass consecutive lanes fetch consecutive
+// 16-byte pieces of a row, the row's address coming from its lane by shuffle).
+__device__ __forceinline__ void load_kv_rows_warp(__nv_bfloat16* k_dst, __nv_bfloat16* v_dst, const PageLookup& pages, int j0,
+                                                  int j_begin, int j_end, int kvh, const AttnParams& p, int lane) {
+  const uint64_t once = l2_evict_first();
+#pragma unroll
+  for (int pass = 0; pass < 4; ++pass) {
+    const bool is_v = pass >= 2;
+    const int j = j0 + (pass & 1) * 32 + lane;
+    bool ok = j >= j_begin && j <= j_end;
+    const int page = ok ? pages(j / p.page_size) : -1;
+    ok = ok && page >= 0;
+    const __nv_bfloat16* src = is_v ? p.vcache : p.kcache;
+    if (ok) src += (long long)page * p.page_stride + (long long)kvh * p.head_stride + (long long)(j % p.page_size) * HD;
+    __nv_bfloat16* dst = (is_v ? v_dst : k_dst) + (pass & 1) * 32 * LDS;
+#pragma unroll
+    for (int idx = lane; idx < 32 * CHUNKS; idx += 32) {
+      const int r = idx / CHUNKS, c = idx % CHUNKS;
+      const unsigned long long a = __shfl_sync(0xffffffffu, (unsigned long long)src, r);
+      const int okr = __shfl_sync(0xffffffffu, (int)ok, r);
+      cp_async16_hint(dst + r * LDS + c * 8, reinterpret_cast<const __nv_bfloat16*>(a) + (okr ? c * 8 : 0), okr != 0, once);
+    }
+  }
+}
+
+// Decoded tokens, short slices: the same work as attention_decode_item for a slice of at most four 64-key tiles, with
+// ONE WARP PER TILE instead of four warps per tile.  Every warp gathers its own tile into buffers of its own (all
+// copies of the slice are in flight at once; tiles older than the step before `dep()`), the block meets once when
+// everything has landed, each warp runs S = Q K^T, the softmax and P V for 16 rows x 64 keys by itself, and the four
+// results are merged through shared memory as before.  The walk over the tiles of a slice, one block barrier and one
+// chain of dependent MMAs per tile, was what a slice's time consisted of; here that chain is one tile long.
+// Shared memory: 16 query rows, then per warp 64 key rows and 64 value rows, then TABLE_SLOTS ints.
+template <typename Dep>
+__device__ __forceinline__ void attention_decode_item_wide(const AttnParams& p, int req, int kvh, int split, int tid,
+                                                           uint8_t* smem_raw, Dep dep) {
+  static_assert(BN == 64, "a warp owns a tile of 64 keys");
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // 16 rows
+  __nv_bfloat16* kv_s = q_s + 16 * LDS;                              // [4 warps][64 key rows, 64 value rows]
+  const int group = p.nq / p.nkv;
+  const int tok0 = p.cu_q[req];
+  const int q_len = p.cu_q[req + 1] - tok0;
+  const int rows_total = q_len * group;        // <= 16 by the launch condition
+  const int start = p.q_start[req];
+  const int warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int* table = p.block_table + (size_t)req * p.max_blocks;
+
+  const int key_hi = start + q_len - 1;
+  const int key_lo = p.window > 0 ? max(0, start - p.window + 1) : 0;
+  const int first_tile = key_lo / BN, last_tile = key_hi / BN;
+  const int n_tiles = last_tile - first_tile + 1;
+  const int per_split = (n_tiles + p.splits - 1) / p.splits;     // <= 4 by the launch condition
+  const int t_begin = first_tile + split * per_split;
+  const int t_end = min(last_tile + 1, t_begin + per_split);
+  int* page_slots = reinterpret_cast<int*>(kv_s + 4 * 2 * BN * LDS);
+  const PageLookup pages = stage_pages(table, page_slots, t_begin * BN, t_end * BN, p.page_size, p.max_blocks, tid, 128);
+  __syncthreads();
+
+  const int tix = t_begin + warp;                         // this warp's tile
+  const bool has_tile = tix < t_end;
+  __nv_bfloat16* kt = kv_s + warp * 2 * BN * LDS;
+  __nv_bfloat16* vt = kt + BN * LDS;
+  const bool early = has_tile && (tix + 1) * BN <= start;  // the tile ends before the step's first token: older than the step
+  if (early) load_kv_rows_warp(kt, vt, pages, tix * BN, key_lo, key_hi, kvh, p, lane);
+  dep();
+  for (int idx = tid; idx < 16 * CHUNKS; idx += 128) {
+    const int r = idx / CHUNKS, c = idx % CHUNKS;
+    const bool ok = r < rows_total;
+    const __nv_bfloat16* src = p.q;
+    if (ok) src = p.q + (size_t)(tok0 + r / group) * p.q_row_stride + (size_t)(kvh * group + r % group) * HD + c * 8;
+    cp_async16(q_s + r * LDS + c * 8, src, ok);
+  }
+  if (has_tile && !early) load_kv_rows_warp(kt, vt, pages, tix * BN, key_lo, key_hi, kvh, p, lane);
+  cp_async_commit();
+  cp_async_wait<0>();
+  __syncthreads();     // the queries and every warp's tile have landed
+  trace_mark(0);
+
+  float m_a = -CUDART_INF_F, m_b = -CUDART_INF_F, l_a = 0.f, l_b = 0.f;
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  if (has_tile) {
+    const int pos_a = start + g / group, pos_b = start + (g + 8) / group;
+    const bool live_a = g < rows_total, live_b = g + 8 < rows_total;
+    const int lo_a = p.window > 0 ? pos_a - p.window + 1 : 0, lo_b = p.window > 0 ? pos_b - p.window + 1 : 0;
+    const int lo_max = p.window > 0 ? start + q_len - 1 - p.window + 1 : 0;
+    // ---- S = Q K^T for the 16 rows x this warp's 64 keys
+    float s[BN / 8][4];
+#pragma unroll
+    for (int i = 0; i < BN / 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+#pragma unroll
+    for (int k0 = 0; k0 < HD; k0 += 16) {
+      uint32_t a[4];
+      ldmatrix_x4(a, q_s + (lane & 15) * LDS + k0 + (lane >> 4) * 8);
+#pragma unroll
+      for (int n0 = 0; n0 < BN; n0 += 16) {
+        uint32_t b[4];
+        ldmatrix_x4(b, kt + (n0 + (lane & 7) + (lane >> 4) * 8) * LDS + k0 + ((lane >> 3) & 1) * 8);
+        mma_bf16(s[n0 / 8], a, b[0], b[1]);
+        mma_bf16(s[n0 / 8 + 1], a, b[2], b[3]);
+      }
+    }
+    const int j_base = tix * BN;
+    const float c = p.scale_log2;
+    if (!(j_base + BN - 1 <= start && j_base >= lo_max)) {   // else every row sees these 64 keys
+#pragma unroll
+      for (int i = 0; i < BN / 8; ++i) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int j = j_base + i * 8 + t4 * 2 + e;
+          if (!(live_a && j <= pos_a && j >= lo_a)) s[i][e] = -CUDART_INF_F;
+          if (!(live_b && j <= pos_b && j >= lo_b)) s[i][2 + e] = -CUDART_INF_F;
+        }
+      }
+    }
+    float mx_a = -CUDART_INF_F, mx_b = -CUDART_INF_F;
+#pragma unroll
+    for (int i = 0; i < BN / 8; ++i) {
+      mx_a = fmaxf(mx_a, fmaxf(s[i][0], s[i][1]));
+      mx_b = fmaxf(mx_b, fmaxf(s[i][2], s[i][3]));
+    }
+    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+    m_a = mx_a * c; m_b = mx_b * c;                                           // in scaled (log2) units
+    const float ms_a = m_a == -CUDART_INF_F ? 0.f : m_a, ms_b = m_b == -CUDART_INF_F ? 0.f : m_b;
+    uint32_t pfrag[BN / 16][4];
+#pragma unroll
+    for (int i = 0; i < BN / 8; ++i) {
+      const float p0 = ex2(fmaf(s[i][0], c, -ms_a)), p1 = ex2(fmaf(s[i][1], c, -ms_a));
+      const float p2 = ex2(fmaf(s[i][2], c, -ms_b)), p3 = ex2(fmaf(s[i][3], c, -ms_b));
+      l_a += p0 + p1;
+      l_b += p2 + p3;
+      pfrag[i / 2][(i & 1) * 2 + 0] = pack_bf16(p0, p1);
+      pfrag[i / 2][(i & 1) * 2 + 1] = pack_bf16(p2, p3);
+    }
+    // ---- O = P V
+#pragma unroll
+    for (int kk = 0; kk < BN / 16; ++kk) {
+#pragma unroll
+      for (int d0 = 0; d0 < HD; d0 += 16) {
+        uint32_t b[4];
+        ldmatrix_x4_trans(b, vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDS + d0 + (lane >> 4) * 8);
+        mma_bf16(o[d0 / 8], pfrag[kk], b[0], b[1]);
+        mma_bf16(o[d0 / 8 + 1], pfrag[kk], b[2], b[3]);
+      }
+    }
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+  }
+  trace_mark(1);       // the tiles of this slice are done
+
+  // ---- merge the four warps' results through shared memory (every warp has finished reading its tile)
+  __syncthreads();
+  float* o_sh = reinterpret_cast<float*>(kv_s);       // [4 warps][16 rows][HD]
+  float* ml_sh = o_sh + 4 * 16 * HD;                  // [4 warps][16 rows][2]
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i) {
+    *reinterpret_cast<float2*>(o_sh + (warp * 16 + g) * HD + i * 8 + t4 * 2) = make_float2(o[i][0], o[i][1]);
+    *reinterpret_cast<float2*>(o_sh + (warp * 16 + g + 8) * HD + i * 8 + t4 * 2) = make_float2(o[i][2], o[i][3]);
+  }
+  if (t4 == 0) {
+    ml_sh[(warp * 16 + g) * 2] = m_a; ml_sh[(warp * 16 + g) * 2 + 1] = l_a;
+    ml_sh[(warp * 16 + g + 8) * 2] = m_b; ml_sh[(warp * 16 + g + 8) * 2 + 1] = l_b;
+  }
+  __syncthreads();
+  for (int idx = tid; idx < rows_total * (HD / 2); idx += 128) {
+    const int r = idx / (HD / 2), d = (idx % (HD / 2)) * 2;
+    float m = -CUDART_INF_F;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) m = fmaxf(m, ml_sh[(w * 16 + r) * 2]);
+    const float m_ref = m == -CUDART_INF_F ? 0.f : m;
+    float l = 0.f, acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float f = exp2f(ml_sh[(w * 16 + r) * 2] - m_ref);   // 0 for a warp that saw no key of the row
+      l += f * ml_sh[(w * 16 + r) * 2 + 1];
+      const float2 ov = *reinterpret_cast<const float2*>(o_sh + (w * 16 + r) * HD + d);
+      acc0 += f * ov.x;
+      acc1 += f * ov.y;
+    }
+    const size_t th = (size_t)(tok0 + r / group) * p.nq + (size_t)(kvh * group + r % group);
+    if (p.splits == 1) {
+      const float inv = 1.f / l;
+      *reinterpret_cast<uint32_t*>(p.out + th * HD + d) = pack_bf16(acc0 * inv, acc1 * inv);
+    } else {
+      *reinterpret_cast<float2*>(p.part_o + (th * p.splits + split) * HD + d) = make_float2(acc0, acc1);
+      if (d == 0) {
+        p.part_ml[(th * p.splits + split) * 2] = m;
+        p.part_ml[(th * p.splits + split) * 2 + 1] = l;
+      }
+    }
+  }
+  trace_mark(2);       // merged and written
+}
+
 // Merges the slices of one (token, head) `th` by one warp: out = sum_s 2^(m_s - m) o_s / sum_s 2^(m_s - m) l_s.
 // Lane s reads the maximum and sum of slices s, s + 32, ...; the weights 2^(m_s - m) go round by
 // shuffle while every lane gathers its elements of o, so no load waits for another.  A slice that

@@ -405,6 +405,21 @@ def _attention_splits(num_requests: int, max_q_len: int, group: int, num_kv_head
     return max(1, min(-(-2 * sms // ctas), max_kv_len // 256))
 
 
+# Decoded tokens with one warp per 64-key tile (slices of four tiles, all of a slice's copies in flight at once, one
+# block barrier instead of one per tile): taken when it gives this many CTAs.  Measured at the TinyLlama sizes,
+# context 2,048, against the kernel that walks a slice tile by tile with four warps per tile (ms per step): batch 4
+# 0.754 / 0.778, 8 0.810 / 0.826, 16 0.938 / 0.942; outside the range it loses: batch 1 0.724 / 0.716 (32 CTAs),
+# batch 32 1.193 / 1.124 (1,024 CTAs).  TLLM_DECODE_WIDE=0 turns it off (a switch for measurements).
+decode_wide_ctas = (96, 640) if os.environ.get("TLLM_DECODE_WIDE", "1") != "0" else (1, 0)
+
+
+def _wide_splits(num_requests: int, num_kv_heads: int, max_kv_len: int) -> int:
+    """Slices of four tiles for the kernel with one warp per tile, or 0 where it is not taken."""
+    splits = -(-max(1, -(-max_kv_len // 64)) // 4)
+    lo, hi = decode_wide_ctas
+    return splits if lo <= num_requests * num_kv_heads * splits <= hi else 0
+
+
 def paged_attention(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, k_cache: torch.Tensor,
                     v_cache: torch.Tensor, block_table: torch.Tensor, batch, out: torch.Tensor, scale: float,
                     window: Optional[int] = None, workspace=None) -> None:
@@ -437,9 +452,13 @@ def paged_attention(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_d
     if qkv.dtype == torch.bfloat16 and not force_generic and head_dim % 16 == 0 and 16 <= head_dim <= 256 and \
             qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0:
         lib = build.load_library("attention_mma", flags=(f"-DTLLM_HEAD_DIM={head_dim}",))
-        splits = 1
+        splits, wide = 1, 0
         if workspace is not None:
             splits = _attention_splits(batch.num_requests, batch.max_q_len, group, num_kv_heads, batch.max_kv_len)
+            if batch.max_q_len * group <= 16 and lib.tllm_attention_mma_wide_fits():
+                wide_splits = _wide_splits(batch.num_requests, num_kv_heads, batch.max_kv_len)
+                if wide_splits:
+                    splits, wide = wide_splits, 1
         scratch = None
         if splits > 1:
             scratch = workspace.get("attention_partials", (t * num_heads * splits * (head_dim + 2),), torch.float32)
@@ -448,7 +467,7 @@ def paged_attention(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_d
             _ptr(batch.cu_q), _ptr(batch.q_start), _ptr(out), t, batch.num_requests, batch.max_q_len, num_heads,
             num_kv_heads, head_dim, page_size, ctypes.c_longlong(k_cache.stride(0)),
             ctypes.c_longlong(k_cache.stride(1)), ctypes.c_float(scale), int(window or 0), splits, _ptr(scratch),
-            _stream()))
+            wide, int(batch.max_kv_len), _stream()))
         return
     lib = build.load_library("attention_generic")
     _check(lib, lib.tllm_paged_attention_generic(
