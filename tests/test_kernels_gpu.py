@@ -321,7 +321,7 @@ def _lens64():
     return [2048, 2047, 1, 64, 65] + torch.randint(1, 2049, (59,), generator=g).tolist()
 
 
-@pytest.mark.parametrize("wide", [False, True])
+@pytest.mark.parametrize("wide", [False, True, "cluster"])
 @pytest.mark.parametrize("bucket", [False, True])
 @pytest.mark.parametrize("hd,nq,nkv,q_len,lens,window,page", [
     (64, 32, 4, 1, [2048], None, 16),          # batch 1 at the longest context: the most key slices
@@ -338,9 +338,11 @@ def test_decode_attention_over_long_contexts(ops, hd, nq, nkv, q_len, lens, wind
     slices run, with the slice count the engine itself picks for these sizes; `bucket` hands the kernel
     the power-of-two bucket of the longest context, as a replayed graph does, so that short requests
     have empty slices; `wide` takes the kernel with one warp per tile wherever the head size lets it (else the
-    kernel that walks a slice tile by tile).  Unwritten slots of the pages are NaN; one key far back carries a query."""
+    kernel that walks a slice tile by tile), "cluster" with its slices merged inside a thread-block cluster instead
+    of by a kernel behind it.  Unwritten slots of the pages are NaN; one key far back carries a query."""
     from tiny_llm_b200.engine import Workspace
     monkeypatch.setattr(ops, "decode_wide_ctas", (1, 1 << 30) if wide else (1, 0))
+    monkeypatch.setattr(ops, "_cluster_merge", lambda n_req, n_kv, splits: wide == "cluster" and 2 <= splits <= 8)   # at every batch
     dtype = "bfloat16"
     n_req = len(lens)
     lens = [max(l, q_len) for l in lens]

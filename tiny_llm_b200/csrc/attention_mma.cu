@@ -239,11 +239,13 @@ attention_decode_kernel(const AttnParams p) {
 
 // Decoded tokens over short slices (at most four tiles each): one warp per tile.
 constexpr int WIDE_SMEM = (16 + 4 * 2 * BN) * LDS * 2 + TABLE_SLOTS * 4;
+template <bool CLUSTER>
 __global__ void __launch_bounds__(128)
 attention_decode_wide_kernel(const AttnParams p) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   pdl_trigger();
-  attention_decode_item_wide(p, blockIdx.x, blockIdx.y, blockIdx.z, threadIdx.x, smem_raw, [] { pdl_wait(); });
+  // CLUSTER: launched with clusters of (1, 1, splits) on a grid whose z extent is `splits`: blockIdx.z is the rank
+  attention_decode_item_wide<CLUSTER>(p, blockIdx.x, blockIdx.y, blockIdx.z, threadIdx.x, smem_raw, [] { pdl_wait(); });
 }
 
 // Merges the slices of every (token, head), one warp each.
@@ -266,7 +268,7 @@ extern "C" int tllm_attention_head_dim() { return HD; }
 // 1 if the kernel with one warp per tile can run at this head size: its per-warp buffers must leave room for two
 // CTAs on an SM, and the merge buffers must fit them.
 extern "C" int tllm_attention_mma_wide_fits() {
-  return WIDE_SMEM <= 113 * 1024 && 4 * 16 * (HD + 2) * 4 <= 4 * 2 * BN * LDS * 2;
+  return WIDE_SMEM <= 113 * 1024 && 5 * 16 * (HD + 2) * 4 <= 4 * 2 * BN * LDS * 2;
 }
 
 // Bytes of scratch (float32 partials) a call with these sizes needs; 0 when splits == 1.
@@ -286,7 +288,7 @@ extern "C" int tllm_attention_mma(const void* q, int q_row_stride, const void* k
   TLLM_REQUIRE(page_size > 0 && max_blocks > 0 && window >= 0 && splits >= 1, "attention_mma: page size %d, %d blocks, window %d, %d splits", page_size, max_blocks, window, splits);
   TLLM_REQUIRE(((uintptr_t)q % 16) == 0 && (q_row_stride % 8) == 0 && ((uintptr_t)kcache % 16) == 0 && ((uintptr_t)vcache % 16) == 0 &&
                (page_stride % 8) == 0 && (head_stride % 8) == 0, "attention_mma: rows must be 16-byte aligned");
-  TLLM_REQUIRE(splits == 1 || scratch != nullptr, "attention_mma: %d splits need scratch", splits);
+  TLLM_REQUIRE(splits == 1 || wide == 2 || scratch != nullptr, "attention_mma: %d splits need scratch", splits);
   TLLM_REQUIRE(nkv <= 65535 && splits <= 65535, "attention_mma: grid too large");
   const int group = nq / nkv;
   AttnParams p;
@@ -311,11 +313,33 @@ extern "C" int tllm_attention_mma(const void* q, int q_row_stride, const void* k
                  max_kv_len, splits);
     static bool configured = false;
     if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(attention_decode_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WIDE_SMEM);
+      cudaError_t e = cudaFuncSetAttribute(attention_decode_wide_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, WIDE_SMEM);
+      if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_decode_wide_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, WIDE_SMEM);
       if (e != cudaSuccess) TLLM_FAIL(TLLM_ERR_CUDA, "attention_mma: cannot reserve %d bytes of shared memory: %s", WIDE_SMEM, cudaGetErrorString(e));
       configured = true;
     }
-    TLLM_LAUNCH("attention_decode_wide", attention_decode_wide_kernel, dim3((unsigned)n_requests, nkv, splits), 128, WIDE_SMEM, s, p);
+    if (wide == 2) {
+      // the slices of a (request, key/value head) as one cluster, merged over distributed shared memory
+      TLLM_REQUIRE(splits >= 2 && splits <= 8, "attention_mma: a cluster merges 2 to 8 slices (got %d)", splits);
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3((unsigned)n_requests, nkv, splits);
+      cfg.blockDim = dim3(128);
+      cfg.dynamicSmemBytes = WIDE_SMEM;
+      cfg.stream = s;
+      cudaLaunchAttribute attr[2];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 1;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = splits;
+      attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[1].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = pdl_enabled() ? 2 : 1;
+      cudaError_t e = cudaLaunchKernelEx(&cfg, attention_decode_wide_kernel<true>, p);
+      if (e != cudaSuccess) TLLM_FAIL(TLLM_ERR_CUDA, "attention_decode_wide (cluster of %d): %s", splits, cudaGetErrorString(e));
+      return TLLM_OK;
+    }
+    TLLM_LAUNCH("attention_decode_wide", attention_decode_wide_kernel<false>, dim3((unsigned)n_requests, nkv, splits), 128, WIDE_SMEM, s, p);
   } else if (small) {
     constexpr int ST = 3;
     // the merge buffers (4 x 16 x (HD + 2) floats) reuse the tile stages

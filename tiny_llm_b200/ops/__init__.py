@@ -411,6 +411,16 @@ def _attention_splits(num_requests: int, max_q_len: int, group: int, num_kv_head
 # 0.754 / 0.778, 8 0.810 / 0.826, 16 0.938 / 0.942; outside the range it loses: batch 1 0.724 / 0.716 (32 CTAs),
 # batch 32 1.193 / 1.124 (1,024 CTAs).  TLLM_DECODE_WIDE=0 turns it off (a switch for measurements).
 decode_wide_ctas = (96, 640) if os.environ.get("TLLM_DECODE_WIDE", "1") != "0" else (1, 0)
+# ... and its 2 to 8 slices of a (request, key/value head) as one thread-block cluster that merges them over
+# distributed shared memory, in place of partial results in global memory and a merging kernel behind it, while the
+# CTAs are at most 1.75 per SM: a cluster starts only when all its CTAs find room at once, and past that count whole
+# clusters wait for a second round (ms per step with / without, context 2,048: batch 4 0.744 / 0.753, 6 0.774 / 0.777,
+# 8 0.800 / 0.811, but 9 0.871 / 0.829, 12 0.931 / 0.872, 16 0.973 / 0.940).  TLLM_DECODE_CLUSTER=0 turns it off.
+decode_cluster_merge = os.environ.get("TLLM_DECODE_CLUSTER", "1") != "0"
+
+
+def _cluster_merge(num_requests: int, num_kv_heads: int, splits: int) -> bool:
+    return decode_cluster_merge and 2 <= splits <= 8 and num_requests * num_kv_heads * splits * 4 <= 7 * sm_count()
 
 
 def _wide_splits(num_requests: int, num_kv_heads: int, max_kv_len: int) -> int:
@@ -458,9 +468,9 @@ def paged_attention(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_d
             if batch.max_q_len * group <= 16 and lib.tllm_attention_mma_wide_fits():
                 wide_splits = _wide_splits(batch.num_requests, num_kv_heads, batch.max_kv_len)
                 if wide_splits:
-                    splits, wide = wide_splits, 1
+                    splits, wide = wide_splits, (2 if _cluster_merge(batch.num_requests, num_kv_heads, wide_splits) else 1)
         scratch = None
-        if splits > 1:
+        if splits > 1 and wide != 2:
             scratch = workspace.get("attention_partials", (t * num_heads * splits * (head_dim + 2),), torch.float32)
         _check(lib, lib.tllm_attention_mma(
             _ptr(qkv), qkv.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
