@@ -40,9 +40,9 @@ __global__ void rms_norm_kernel(const float* __restrict__ x, const float* __rest
     ss += v * v;
   }
   ss = block_sum(ss, scratch);
-  const float denom = sqrtf(ss / (float)hidden + eps);
+  const float inv = 1.f / sqrtf(ss / (float)hidden + eps);   // one division per row; the elements are multiplied
   T* dst = out + (size_t)r * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = from_f32<T>((w[i] * src[i]) / denom);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = from_f32<T>((w[i] * src[i]) * inv);
 }
 
 __device__ __forceinline__ void store4(float* p, float a, float b, float c, float d) {
@@ -87,13 +87,13 @@ __global__ void rms_norm_vec_kernel(const float* __restrict__ x, const float* __
     ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
   }
   ss = block_sum(ss, scratch);
-  const float denom = sqrtf(ss / (float)hidden + eps);
+  const float inv = 1.f / sqrtf(ss / (float)hidden + eps);   // one division per row; the elements are multiplied
   T* dst = out + (size_t)r * hidden;
 #pragma unroll
   for (int i = 0; i < VEC; ++i) {
     const int idx = threadIdx.x + i * blockDim.x;
     if (idx < n4)
-      store4(dst + 4 * idx, (g[i].x * v[i].x) / denom, (g[i].y * v[i].y) / denom, (g[i].z * v[i].z) / denom, (g[i].w * v[i].w) / denom);
+      store4(dst + 4 * idx, (g[i].x * v[i].x) * inv, (g[i].y * v[i].y) * inv, (g[i].z * v[i].z) * inv, (g[i].w * v[i].w) * inv);
   }
 }
 
