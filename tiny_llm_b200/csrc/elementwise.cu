@@ -3,6 +3,7 @@
 // their pages).  All take float32 or bfloat16 activations; statistics and angles are 32-bit.
 // Reference counterparts: tiny_llm/ops/cuda/embedding.cu:10-29, norm.cu:16-49, silu.cu:7-12,
 // arithmetic.cu:7-22, rope.cu:26-95, gemm.cu:380-411 (the scatter of K/V rows into pages).
+#include <algorithm>
 #include "common.cuh"
 
 TLLM_DEFINE_LAST_ERROR
@@ -229,7 +230,9 @@ __global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, float* __restrict_
     slot_base = (long long)(slot / page_size) * page_stride + (long long)(slot % page_size) * hd;
   }
   const float zeros[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  for (int idx = threadIdx.x; idx < heads * groups; idx += blockDim.x) {
+  // gridDim.y CTAs share a token's work items
+  const int first = blockIdx.y * blockDim.x + threadIdx.x, step = gridDim.y * blockDim.x;
+  for (int idx = first; idx < heads * groups; idx += step) {
     const int h = idx / groups, i = (idx % groups) * 8;
     const int e = h * hd + i;
     float va[8], vb[8], oa[8], ob[8];
@@ -255,7 +258,7 @@ __global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, float* __restrict_
   }
   if (write_kv) {
     const int v0 = (nq + nkv) * hd;
-    for (int idx = threadIdx.x; idx < nkv * hd / 8; idx += blockDim.x) {
+    for (int idx = first; idx < nkv * hd / 8; idx += step) {
       const int h = (idx * 8) / hd, i = (idx * 8) % hd;
       float v[8];
       if (srow) { load8(srow + v0 + idx * 8, v); store8(srow + v0 + idx * 8, zeros); }
@@ -361,11 +364,15 @@ extern "C" int tllm_rope_kv_write(void* qkv, float* src, int src_stride, const i
                                       (page_stride * esz) % 16 == 0 && (head_stride * esz) % 16 == 0)) &&
                    (!c || (((uintptr_t)c % 16) == 0 && ((uintptr_t)sn % 16) == 0));
   if (vec) {
-    const int vthreads = (nq + nkv) * (hd / 16) >= 256 ? 256 : 128;
+    const int items = (nq + nkv) * (hd / 16);
+    const int vthreads = items >= 256 ? 256 : 128;
+    // few tokens: up to four CTAs per token, so that no thread walks its items one after the other
+    const int parts = n_tokens <= 256 ? std::min(4, (items + vthreads - 1) / vthreads) : 1;
+    const dim3 vgrid((unsigned)n_tokens, (unsigned)parts);
     if (dtype == TLLM_F32)
-      TLLM_LAUNCH("rope_kv_write", rope_kv_write_vec_kernel<float>, n_tokens, vthreads, 0, s, (float*)qkv, src, src_stride, positions, c, sn, n_tokens, nq, nkv, hd, row_stride, (float*)kcache, (float*)vcache, slot_mapping, page_size, page_stride, head_stride);
+      TLLM_LAUNCH("rope_kv_write", rope_kv_write_vec_kernel<float>, vgrid, vthreads, 0, s, (float*)qkv, src, src_stride, positions, c, sn, n_tokens, nq, nkv, hd, row_stride, (float*)kcache, (float*)vcache, slot_mapping, page_size, page_stride, head_stride);
     else if (dtype == TLLM_BF16)
-      TLLM_LAUNCH("rope_kv_write", rope_kv_write_vec_kernel<__nv_bfloat16>, n_tokens, vthreads, 0, s, (__nv_bfloat16*)qkv, src, src_stride, positions, c, sn, n_tokens, nq, nkv, hd, row_stride, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, slot_mapping, page_size, page_stride, head_stride);
+      TLLM_LAUNCH("rope_kv_write", rope_kv_write_vec_kernel<__nv_bfloat16>, vgrid, vthreads, 0, s, (__nv_bfloat16*)qkv, src, src_stride, positions, c, sn, n_tokens, nq, nkv, hd, row_stride, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, slot_mapping, page_size, page_stride, head_stride);
     else
       TLLM_FAIL(TLLM_ERR_ARG, "rope_kv_write: unknown dtype code %d", dtype);
     return TLLM_OK;
