@@ -297,14 +297,16 @@ def linear_rope_kv(h: torch.Tensor, w_qkv: torch.Tensor, qkv: torch.Tensor, posi
 
 
 # Up to this many tokens (and above 128, where the product runs as 128 x 256 tiles) the Q/K/V projection takes the
-# kernel with rotation and cache write in its epilogue.  Between, its cluster hands round 128 x tokens float32 values per
-# slice of K, and K slices added with float32 atomics plus the rotate-and-cache kernel are faster (ms per decode step at
-# the TinyLlama sizes, fused / separate: 16 tokens 0.935 / 0.932, 24 1.059 / 1.063, 32 1.123 / 1.097, 64 1.576 / 1.518).
+# kernel with rotation and cache write in its epilogue, whatever the sizes.  Between, a cluster of eight K slices hands
+# round 8 x 128 x tokens float32 values per weight tile, and K slices added with float32 atomics plus the
+# rotate-and-cache kernel are faster (ms per decode step at the TinyLlama sizes, 8 slices, fused / separate: 16 tokens
+# 0.935 / 0.932, 24 1.059 / 1.063, 32 1.123 / 1.097, 64 1.576 / 1.518); with fewer slices the fused kernel stays
+# (Llama-3-8B sizes, 4 slices, 8 layers: 32 tokens 1.326 / 1.428, 64 1.802 / 1.840).
 qkv_fused_rows = int(os.environ.get("TLLM_QKV_FUSED_ROWS", "24"))
 
 
-def fused_qkv_preferred(m: int) -> bool:
-    return m <= qkv_fused_rows or m > 128
+def fused_qkv_preferred(m: int, n: int, k: int) -> bool:
+    return m <= qkv_fused_rows or m > 128 or _cluster_slices(n, k) < 8
 
 
 def prefers_split(a: torch.Tensor, w: torch.Tensor) -> bool:

@@ -67,7 +67,7 @@ class GQAttention:
         pos = self.position
         fused = getattr(pos, "fused", False)
         kv_slots = None if self.shares_cache else cache.slot_mapping
-        if fused and ops.fused_qkv_preferred(t) and ops.linear_rope_kv(
+        if fused and ops.fused_qkv_preferred(t, self.qkv_dim, h.shape[1]) and ops.linear_rope_kv(
                 h, self.w_qkv, qkv, ctx.batch.positions, pos.cos, pos.sin, self.num_heads, self.num_kv_heads,
                 self.head_dim, cache.k, cache.v, kv_slots):
             pass    # projection, rotation and cache write were one kernel
