@@ -82,6 +82,31 @@ def test_linear(ops, dtype, m, n, k):
     ops.check_status()
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 2048, 2048), (2, 37, 132), (3, 640, 5632), (4, 16, 4), (5, 331, 80), (8, 2560, 2048),
+                                   (9, 250, 1000), (16, 24, 388), (13, 7, 128)])
+def test_float32_linear_of_few_rows_gives_the_bits_of_the_tile_kernel(ops, m, n, k, monkeypatch):
+    """Up to 16 float32 rows run on a kernel of their own; every output element is the same chain of fmaf over
+    ascending k as in the 64 x 64 tiles, so the two agree to the bit, for every row count, for widths and depths
+    that fill no tile or chunk, for a strided input and when adding into the output."""
+    torch.manual_seed(m * 1000 + n)
+    a = torch.randn(m, k + 8, device=DEV)[:, :k]
+    w = torch.randn(n, k, device=DEV)
+    ref = pl.linear(a.double().cpu(), w.double().cpu()).float()
+    outs = []
+    for skinny in (True, False):
+        monkeypatch.setattr(ops, "linear_skinny", skinny)
+        out = torch.empty(m, n + 4, device=DEV)[:, :n]
+        ops.linear(a, w, out)
+        acc = torch.full((m, n), 0.25, device=DEV)
+        ops.linear(a, w, acc, accumulate=True)
+        outs.append((out.clone(), acc))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    scale = max(1.0, float(ref.abs().max()))
+    assert float((outs[0][0].cpu() - ref).abs().max()) <= 2e-5 * scale
+    assert float((outs[0][1].cpu() - ref - 0.25).abs().max()) <= 2e-5 * scale
+    ops.check_status()
+
+
 @pytest.mark.parametrize("dtype", DT)
 @pytest.mark.parametrize("m,inter,block", [(37, 176, 16), (5, 208, 16), (3, 5632, 128), (9, 7, 1)])
 def test_silu_mul(ops, dtype, m, inter, block):
@@ -257,6 +282,44 @@ def test_paged_attention(ops, dtype, nq, nkv, hd, page, window):
     if window is None:   # the far key carries the first query's first head
         p = torch.softmax((qkv[0, :hd].float() * scale) @ ks[0][:lens[0] - q_lens[0] + 1, 0].float().t(), 0)
         assert float(p[3]) > 0.9
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("window", [None, 300])
+def test_attention_of_the_32_bit_path_gives_the_same_bits_with_one_warp_or_eight_per_head(ops, dtype, window, monkeypatch):
+    """The kernel of the 32-bit path walks the keys as eight interleaved running softmaxes that are merged in a fixed
+    order; with few (token, head) pairs eight warps carry one each, with many one warp carries all eight.  Both must
+    agree with the plain implementation and with each other to the bit, at contexts of a few tiles and of dozens, with
+    a window and without: else a token's logits would depend on how many others shared its step."""
+    from tiny_llm_b200.engine import Workspace
+    nq, nkv, hd, page = 6, 2, 48, 8
+    lens, q_lens = [2100, 700, 33, 9], [1, 3, 2, 9]
+    table, k_cache, v_cache, ks, vs = paged_setup(dtype, 4, lens, nkv, hd, page, seed=5)
+    g = torch.Generator().manual_seed(3)
+    t = sum(q_lens)
+    qkv = torch.randn(t, (nq + 2 * nkv) * hd, generator=g).to(DT[dtype])
+    tok_req = torch.cat([torch.full((n,), r, dtype=torch.int32) for r, n in enumerate(q_lens)])
+    pos = torch.cat([torch.arange(l - n, l, dtype=torch.int32) for l, n in zip(lens, q_lens)])
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
+    starts = torch.tensor([l - n for l, n in zip(lens, q_lens)], dtype=torch.int32)
+    batch = types.SimpleNamespace(token_request=tok_req.to(DEV), positions=pos.to(DEV), cu_q=cu.to(DEV),
+                                  q_start=starts.to(DEV), num_requests=4, max_q_len=max(q_lens), max_kv_len=max(lens))
+    monkeypatch.setattr(ops, "force_generic", True)
+    outs = []
+    for split in (False, True):
+        monkeypatch.setattr(ops, "generic_attention_split", split)
+        out = torch.empty(t, nq * hd, dtype=DT[dtype], device=DEV)
+        ops.paged_attention(qkv.to(DEV), nq, nkv, hd, k_cache.to(DEV), v_cache.to(DEV), table.to(DEV), batch, out,
+                            1.0 / math.sqrt(hd), window, Workspace(DEV))
+        outs.append(out.cpu())
+    assert torch.equal(outs[0], outs[1])
+    cur = 0
+    for r, (l, n) in enumerate(zip(lens, q_lens)):
+        q = qkv[cur: cur + n, : nq * hd].float().view(n, nq, hd)
+        ref = pl.attention(q, ks[r].float(), vs[r].float(), pos[cur: cur + n], window=window).reshape(n, nq * hd)
+        d = float((outs[0][cur: cur + n].float() - ref).abs().max())
+        assert d <= tol(dtype, max(1.0, float(ref.abs().max()))), (r, d)
+        cur += n
 
 
 @pytest.mark.parametrize("hd,nq,nkv,page", [(64, 8, 1, 16), (64, 32, 4, 16), (64, 4, 4, 8), (64, 2, 1, 64), (64, 16, 2, 32),

@@ -1,12 +1,19 @@
-// Attention of the step's queries over the paged cache, one warp per (token, query head), any
-// head size that is a multiple of 16 up to 256, any number of heads and groups, any page size.
-// It is the attention of the true 32-bit path and the fallback of the bfloat16 path.
+// Attention of the step's queries over the paged cache on the CUDA cores, any head size that is a
+// multiple of 16 up to 256, any number of heads and groups, any page size.  It is the attention of
+// the true 32-bit path and the fallback of the bfloat16 path.
 //
 // The keys a query at position p sees are j in [max(0, p - window + 1), p].  They are walked in
-// tiles of 32 that start at multiples of 32 of the absolute position, with a running softmax
-// (m, l, o) in 32-bit, so the order of the sums is a function of p alone: the result does not
-// depend on how the request's tokens were cut into steps, on the rest of the batch or on the
-// page ids.  Reference counterpart: tiny_llm/ops/cuda/flash_attention.cu:338-442 (64-key tiles,
+// tiles of 32 that start at multiples of 32 of the absolute position.  Tile number i (= j / 32) belongs
+// to lane i mod 8 of eight running softmaxes (m, l, o) in 32-bit, each of which takes its tiles in
+// ascending order; at the end the eight are merged in the order 0..7.  So the order of every sum is a
+// function of p alone: the result does not depend on how the request's tokens were cut into steps, on
+// the rest of the batch or on the page ids.  Two launches of the same arithmetic: with many (token,
+// head) pairs one warp carries all eight softmaxes of a pair (prompts); with few, eight warps carry
+// one each and merge through shared memory (decoded tokens over a long context, where one warp per
+// pair would leave most of the GPU idle and walk thousands of keys as one chain of memory latencies).
+// Every step of both is written with explicit fmaf / __fmul_rn, so that the two compile to the same
+// operations and give the same bits.
+// Reference counterpart: tiny_llm/ops/cuda/flash_attention.cu:338-442 (64-key tiles,
 // one lane per key, P.V by shuffles), whose mask compares a chunk-local query index with the
 // absolute key index (:63-66, :402-405).
 #include <math_constants.h>
@@ -38,19 +45,96 @@ __device__ __forceinline__ void load16(const __nv_bfloat16* p, float* dst) {
   }
 }
 
-template <typename T>
-__global__ void __launch_bounds__(WARPS * 32)
+constexpr int WAYS = 8;   // running softmaxes per (token, head); a constant of the arithmetic, not a tuning knob
+
+template <int OD>   // OD * 32 >= head size: the output values of a lane
+struct Softmax {
+  float m, l;
+  float o[OD];
+};
+
+// One tile of 32 keys starting at j0 into the running softmax `st` (all lanes of the warp).
+template <typename T, int OD>
+__device__ __forceinline__ void attend_tile(Softmax<OD>& st, int j0, int lo, int p, const float* q_row, const T* kcache,
+                                            const T* vcache, const int* table, int max_blocks, int kvh, int hd,
+                                            int page_size, long long page_stride, long long head_stride, int lane) {
+  const int j = j0 + lane;
+  bool valid = j >= lo && j <= p && j / page_size < max_blocks;
+  const int page = valid ? table[j / page_size] : -1;
+  valid = valid && page >= 0;   // a table entry that names no page is never followed
+  long long row_off = 0;
+  float s = -CUDART_INF_F;
+  if (valid) {
+    row_off = (long long)page * page_stride + (long long)kvh * head_stride + (long long)(j % page_size) * hd;
+    const T* krow = kcache + row_off;
+    float acc = 0.f;
+#pragma unroll 4
+    for (int d = 0; d < hd; d += Vec<T>::N) {
+      float kv[Vec<T>::N];
+      load16(krow + d, kv);
+#pragma unroll
+      for (int e = 0; e < Vec<T>::N; ++e) acc = fmaf(q_row[d + e], kv[e], acc);
+    }
+    s = acc;
+  }
+  const float m_new = fmaxf(st.m, warp_max(s));
+  const float m_ref = m_new == -CUDART_INF_F ? 0.f : m_new;   // a tile without a visible key changes nothing
+  const float pr = valid ? expf(s - m_ref) : 0.f;
+  const float corr = expf(st.m - m_ref);           // 0 on the first tile (m = -inf)
+  st.l = fmaf(st.l, corr, warp_sum(pr));
+  st.m = m_new;
+#pragma unroll
+  for (int i = 0; i < OD; ++i) st.o[i] = __fmul_rn(st.o[i], corr);
+  const int last = min(31, p - j0);
+  const int first = max(0, lo - j0);
+  for (int kk = first; kk <= last; ++kk) {
+    const float pk = __shfl_sync(0xffffffffu, pr, kk);
+    if (pk == 0.f) continue;   // uniform across the warp: nothing to add, and the row may name no page
+    const long long off = __shfl_sync(0xffffffffu, row_off, kk);
+    const T* vrow = vcache + off;
+#pragma unroll
+    for (int i = 0; i < OD; ++i) {
+      const int d = lane + 32 * i;
+      if (d < hd) st.o[i] = fmaf(pk, to_f32(vrow[d]), st.o[i]);
+    }
+  }
+}
+
+// The merge of the eight softmaxes, way 0 first: `m`, `l`, `o` of way w are read through the three functions.
+template <int OD, typename FM, typename FL, typename FO>
+__device__ __forceinline__ void merge_ways(FM way_m, FL way_l, FO way_o, float* o_out, float& l_out) {
+  float mx = -CUDART_INF_F;
+#pragma unroll
+  for (int w = 0; w < WAYS; ++w) mx = fmaxf(mx, way_m(w));
+  const float m_ref = mx == -CUDART_INF_F ? 0.f : mx;
+  l_out = 0.f;
+#pragma unroll
+  for (int i = 0; i < OD; ++i) o_out[i] = 0.f;
+#pragma unroll
+  for (int w = 0; w < WAYS; ++w) {
+    const float f = expf(way_m(w) - m_ref);   // 0 for a way that saw no key
+    l_out = fmaf(way_l(w), f, l_out);
+#pragma unroll
+    for (int i = 0; i < OD; ++i) o_out[i] = fmaf(way_o(w, i), f, o_out[i]);
+  }
+}
+
+// SPLIT = false: WARPS (token, head) pairs per CTA, one warp each, eight softmaxes in its registers.
+// SPLIT = true: one pair per CTA of eight warps, warp w carries softmax w.
+template <typename T, bool SPLIT, int OD>
+__global__ void __launch_bounds__(SPLIT ? WAYS * 32 : WARPS * 32)
 paged_attention_generic_kernel(const T* __restrict__ q, int q_row_stride, const T* __restrict__ kcache,
                                const T* __restrict__ vcache, const int* __restrict__ block_table,
                                int max_blocks, const int* __restrict__ token_request,
                                const int* __restrict__ positions, T* __restrict__ out, int n_tokens,
                                int nq, int nkv, int hd, int page_size, long long page_stride,
                                long long head_stride, float scale, int window) {
-  __shared__ __align__(16) float q_s[WARPS][MAX_HD];
+  __shared__ __align__(16) float q_s[SPLIT ? 1 : WARPS][MAX_HD];
+  __shared__ float merge_s[SPLIT ? WAYS : 1][SPLIT ? OD * 32 + 2 : 1];
   pdl_trigger();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long task = (long long)blockIdx.x * WARPS + warp;
+  const long long task = SPLIT ? (long long)blockIdx.x : (long long)blockIdx.x * WARPS + warp;
   if (task >= (long long)n_tokens * nq) return;
   const int t = (int)(task / nq), h = (int)(task % nq);
   const int kvh = h / (nq / nkv);
@@ -60,59 +144,55 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_row_stride, const 
   const int* table = block_table + (size_t)req * max_blocks;
 
   const T* qrow = q + (size_t)t * q_row_stride + (size_t)h * hd;
-  for (int d = lane; d < hd; d += 32) q_s[warp][d] = to_f32(qrow[d]) * scale;
-  __syncwarp();
+  float* q_row = q_s[SPLIT ? 0 : warp];
+  if (SPLIT) {
+    for (int d = threadIdx.x; d < hd; d += WAYS * 32) q_row[d] = to_f32(qrow[d]) * scale;
+    __syncthreads();
+  } else {
+    for (int d = lane; d < hd; d += 32) q_row[d] = to_f32(qrow[d]) * scale;
+    __syncwarp();
+  }
 
-  float m = -CUDART_INF_F, l = 0.f;
-  float o[MAX_HD / 32];
+  const int first_group = (lo / (32 * WAYS)) * (32 * WAYS);   // tile numbers are absolute: way = (j0 / 32) % WAYS
+  float o[OD], l;
+  if (SPLIT) {
+    Softmax<OD> st;
+    st.m = -CUDART_INF_F; st.l = 0.f;
 #pragma unroll
-  for (int i = 0; i < MAX_HD / 32; ++i) o[i] = 0.f;
-
-  for (int j0 = (lo / 32) * 32; j0 <= p; j0 += 32) {
-    const int j = j0 + lane;
-    bool valid = j >= lo && j <= p && j / page_size < max_blocks;
-    const int page = valid ? table[j / page_size] : -1;
-    valid = valid && page >= 0;   // a table entry that names no page is never followed
-    long long row_off = 0;
-    float s = -CUDART_INF_F;
-    if (valid) {
-      row_off = (long long)page * page_stride + (long long)kvh * head_stride + (long long)(j % page_size) * hd;
-      const T* krow = kcache + row_off;
-      float acc = 0.f;
-      for (int d = 0; d < hd; d += Vec<T>::N) {
-        float kv[Vec<T>::N];
-        load16(krow + d, kv);
+    for (int i = 0; i < OD; ++i) st.o[i] = 0.f;
+    for (int j0 = first_group + warp * 32; j0 <= p; j0 += 32 * WAYS)
+      if (j0 + 31 >= lo)
+        attend_tile(st, j0, lo, p, q_row, kcache, vcache, table, max_blocks, kvh, hd, page_size, page_stride, head_stride, lane);
+    if (lane == 0) { merge_s[warp][OD * 32] = st.m; merge_s[warp][OD * 32 + 1] = st.l; }
 #pragma unroll
-        for (int e = 0; e < Vec<T>::N; ++e) acc = fmaf(q_s[warp][d + e], kv[e], acc);
-      }
-      s = acc;
+    for (int i = 0; i < OD; ++i)
+      if (lane + 32 * i < hd) merge_s[warp][lane + 32 * i] = st.o[i];
+    __syncthreads();
+    if (warp != 0) return;
+    merge_ways<OD>([&](int w) { return merge_s[w][OD * 32]; }, [&](int w) { return merge_s[w][OD * 32 + 1]; },
+               [&](int w, int i) { return lane + 32 * i < hd ? merge_s[w][lane + 32 * i] : 0.f; }, o, l);
+  } else {
+    Softmax<OD> st[WAYS];
+#pragma unroll
+    for (int w = 0; w < WAYS; ++w) {
+      st[w].m = -CUDART_INF_F; st[w].l = 0.f;
+#pragma unroll
+      for (int i = 0; i < OD; ++i) st[w].o[i] = 0.f;
     }
-    const float m_new = fmaxf(m, warp_max(s));
-    const float m_ref = m_new == -CUDART_INF_F ? 0.f : m_new;   // a tile without a visible key changes nothing
-    const float pr = valid ? expf(s - m_ref) : 0.f;
-    const float corr = expf(m - m_ref);           // 0 on the first tile (m = -inf)
-    l = l * corr + warp_sum(pr);
-    m = m_new;
+    for (int g0 = first_group; g0 <= p; g0 += 32 * WAYS) {
 #pragma unroll
-    for (int i = 0; i < MAX_HD / 32; ++i) o[i] *= corr;
-    const int last = min(31, p - j0);
-    const int first = max(0, lo - j0);
-    for (int kk = first; kk <= last; ++kk) {
-      const float pk = __shfl_sync(0xffffffffu, pr, kk);
-      if (pk == 0.f) continue;   // uniform across the warp: nothing to add, and the row may name no page
-      const long long off = __shfl_sync(0xffffffffu, row_off, kk);
-      const T* vrow = vcache + off;
-#pragma unroll
-      for (int i = 0; i < MAX_HD / 32; ++i) {
-        const int d = lane + 32 * i;
-        if (d < hd) o[i] = fmaf(pk, to_f32(vrow[d]), o[i]);
+      for (int w = 0; w < WAYS; ++w) {
+        const int j0 = g0 + w * 32;
+        if (j0 <= p && j0 + 31 >= lo)
+          attend_tile(st[w], j0, lo, p, q_row, kcache, vcache, table, max_blocks, kvh, hd, page_size, page_stride, head_stride, lane);
       }
     }
+    merge_ways<OD>([&](int w) { return st[w].m; }, [&](int w) { return st[w].l; }, [&](int w, int i) { return st[w].o[i]; }, o, l);
   }
   T* orow = out + (size_t)t * nq * hd + (size_t)h * hd;
   const float inv = 1.f / l;
 #pragma unroll
-  for (int i = 0; i < MAX_HD / 32; ++i) {
+  for (int i = 0; i < OD; ++i) {
     const int d = lane + 32 * i;
     if (d < hd) orow[d] = from_f32<T>(o[i] * inv);
   }
@@ -126,7 +206,7 @@ extern "C" int tllm_paged_attention_generic(const void* q, int q_row_stride, con
                                             const int* block_table, int max_blocks, const int* token_request,
                                             const int* positions, void* out, int n_tokens, int nq, int nkv, int hd,
                                             int page_size, long long page_stride, long long head_stride,
-                                            float scale, int window, int dtype, void* stream) {
+                                            float scale, int window, int dtype, int split_override, void* stream) {
   TLLM_REQUIRE(n_tokens > 0 && nq > 0 && nkv > 0 && nq % nkv == 0,
                "attention: %d tokens, %d heads, %d key/value heads (heads must be a multiple of key/value heads)", n_tokens, nq, nkv);
   TLLM_REQUIRE(hd >= 16 && hd <= MAX_HD && hd % 16 == 0,
@@ -136,19 +216,33 @@ extern "C" int tllm_paged_attention_generic(const void* q, int q_row_stride, con
   TLLM_REQUIRE(((size_t)kcache % 16) == 0 && ((size_t)vcache % 16) == 0 && (page_stride * elem) % 16 == 0 && (head_stride * elem) % 16 == 0,
                "attention: cache rows must be 16-byte aligned");
   const long long tasks = (long long)n_tokens * nq;
-  const long long blocks = (tasks + WARPS - 1) / WARPS;
+  // few pairs (decoded tokens): eight warps per pair; the result is the same to the bit
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+    TLLM_FAIL(TLLM_ERR_CUDA, "attention: cannot read the number of SMs");
+  const bool split = split_override >= 0 ? split_override != 0 : tasks <= 8LL * sms;
+  const long long blocks = split ? tasks : (tasks + WARPS - 1) / WARPS;
   TLLM_REQUIRE(blocks <= 2147483647LL, "attention: %lld (token, head) pairs exceed the grid", tasks);
   cudaStream_t s = (cudaStream_t)stream;
-  if (dtype == TLLM_F32)
-    TLLM_LAUNCH("paged_attention_generic", paged_attention_generic_kernel<float>, (unsigned)blocks, WARPS * 32, 0, s,
-        (const float*)q, q_row_stride, (const float*)kcache, (const float*)vcache, block_table, max_blocks,
-        token_request, positions, (float*)out, n_tokens, nq, nkv, hd, page_size, page_stride, head_stride, scale, window);
-  else if (dtype == TLLM_BF16)
-    TLLM_LAUNCH("paged_attention_generic", paged_attention_generic_kernel<__nv_bfloat16>, (unsigned)blocks, WARPS * 32, 0, s,
-        (const __nv_bfloat16*)q, q_row_stride, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, block_table,
-        max_blocks, token_request, positions, (__nv_bfloat16*)out, n_tokens, nq, nkv, hd, page_size, page_stride,
-        head_stride, scale, window);
-  else
+#define TLLM_ATT_GENERIC(T_, SPLIT_, OD_)                                                                             \
+  TLLM_LAUNCH("paged_attention_generic", (paged_attention_generic_kernel<T_, SPLIT_, OD_>), (unsigned)blocks,          \
+              (SPLIT_ ? WAYS : WARPS) * 32, 0, s, (const T_*)q, q_row_stride, (const T_*)kcache, (const T_*)vcache,    \
+              block_table, max_blocks, token_request, positions, (T_*)out, n_tokens, nq, nkv, hd, page_size,           \
+              page_stride, head_stride, scale, window)
+#define TLLM_ATT_GENERIC_HD(T_, SPLIT_)                              \
+  do {                                                              \
+    if (hd <= 64) TLLM_ATT_GENERIC(T_, SPLIT_, 2);                   \
+    else if (hd <= 128) TLLM_ATT_GENERIC(T_, SPLIT_, 4);             \
+    else TLLM_ATT_GENERIC(T_, SPLIT_, 8);                            \
+  } while (0)
+  if (dtype == TLLM_F32) {
+    if (split) TLLM_ATT_GENERIC_HD(float, true); else TLLM_ATT_GENERIC_HD(float, false);
+  } else if (dtype == TLLM_BF16) {
+    if (split) TLLM_ATT_GENERIC_HD(__nv_bfloat16, true); else TLLM_ATT_GENERIC_HD(__nv_bfloat16, false);
+  } else {
     TLLM_FAIL(TLLM_ERR_ARG, "attention: unknown dtype code %d", dtype);
+  }
+#undef TLLM_ATT_GENERIC_HD
+#undef TLLM_ATT_GENERIC
   return TLLM_OK;
 }

@@ -1,8 +1,16 @@
 // C[M,N] = A[M,K] . W[N,K]^T on the CUDA cores with 32-bit accumulation (FFMA only, no tensor-core
 // mode): the product of the true 32-bit path, and the fallback of the bfloat16 path for sizes the
-// tensor-core kernels refuse.  Any M, N, K.  Every output element is a sum over k in ascending
-// order of 16-wide slices, whatever M is, so a row's result does not depend on its batch.
+// tensor-core kernels refuse.  Any M, N, K.  Every output element is ONE chain of fmaf over k in
+// ascending order starting from zero, whatever M is and whichever of the two kernels below computes it,
+// so a row's result does not depend on its batch, to the bit.
+//   linear_generic_kernel: 64 x 64 tiles, 4 x 4 outputs per thread (many rows);
+//   linear_skinny_kernel: float32, at most 16 rows (decoded tokens): a CTA takes 8 or 16 weight rows and
+//     streams them through shared memory in chunks of 128 k (cp.async, four stages), one thread per
+//     output element.  With so few rows the 64-row tile left 32 CTAs to stream a matrix that 148 SMs could
+//     pull, each with one load in flight per thread.
 // Reference counterpart: tiny_llm/ops/cuda/gemm.cu:67-106 (64x256 tile, 8x8 outputs per thread).
+#include <cstdint>
+
 #include "common.cuh"
 
 TLLM_DEFINE_LAST_ERROR
@@ -73,6 +81,120 @@ linear_generic_kernel(const T* __restrict__ a, const T* __restrict__ w, void* __
   }
 }
 
+// ---------------------------------------------------------------- at most 16 rows, float32
+constexpr int SK_KC = 128, SK_LD = SK_KC + 4, SK_STAGES = 4, SK_THREADS = 128;
+
+__device__ __forceinline__ void sk_cp16(float* dst, const float* src, bool ok) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  const int bytes = ok ? 16 : 0;   // 0: the 16 bytes are filled with zeros, which leave a chain of fmaf as it is
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+// A shared-memory load that stays where it is written: the loads of the next 32 k are issued before the 32 dependent
+// fmaf of this block, so that a thread waits for shared memory once per block and not once per four fmaf (a warp
+// issues in order, and there are too few warps here to hide a load behind another warp).
+__device__ __forceinline__ float4 sk_lds(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  return v;
+}
+
+template <int R, int MODE>   // R rows of A per CTA (1, 2, 4, 8 or 16); BNS weight rows: R x BNS = at most 128 threads compute
+__global__ void __launch_bounds__(SK_THREADS)
+linear_skinny_kernel(const float* __restrict__ a, const float* __restrict__ w, float* __restrict__ out,
+                     int m, int n, int k, int lda, int ldo) {
+  constexpr int BNS = R == 16 ? 8 : 16;
+  extern __shared__ __align__(16) uint8_t sk_smem[];
+  float (*w_s)[BNS][SK_LD] = reinterpret_cast<float (*)[BNS][SK_LD]>(sk_smem);
+  float (*a_s)[R][SK_LD] = reinterpret_cast<float (*)[R][SK_LD]>(sk_smem + sizeof(float) * SK_STAGES * BNS * SK_LD);
+  pdl_trigger();
+  const int tid = threadIdx.x;
+  const int n0 = blockIdx.x * BNS, m0 = blockIdx.y * R;
+  const int chunks = (k + SK_KC - 1) / SK_KC;
+  auto load_w = [&](int chunk, int stage) {
+    const int k0 = chunk * SK_KC;
+    for (int idx = tid; idx < BNS * (SK_KC / 4); idx += SK_THREADS) {
+      const int row = idx / (SK_KC / 4), kk = (idx % (SK_KC / 4)) * 4;
+      const bool ok = n0 + row < n && k0 + kk < k;   // k is a multiple of 4
+      sk_cp16(&w_s[stage][row][kk], ok ? w + (size_t)(n0 + row) * k + k0 + kk : w, ok);
+    }
+  };
+  auto load_a = [&](int chunk, int stage) {
+    const int k0 = chunk * SK_KC;
+    for (int idx = tid; idx < R * (SK_KC / 4); idx += SK_THREADS) {
+      const int row = idx / (SK_KC / 4), kk = (idx % (SK_KC / 4)) * 4;
+      const bool ok = m0 + row < m && k0 + kk < k;
+      sk_cp16(&a_s[stage][row][kk], ok ? a + (size_t)(m0 + row) * lda + k0 + kk : a, ok);
+    }
+  };
+  // the weights depend on no earlier kernel: their first chunks are on the way before the wait
+  for (int st = 0; st < SK_STAGES - 1; ++st)
+    if (st < chunks) load_w(st, st);
+  pdl_wait();
+  for (int st = 0; st < SK_STAGES - 1; ++st) {
+    if (st < chunks) load_a(st, st);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  const bool computes = tid < R * BNS;
+  const int r = tid / BNS, c = tid % BNS;
+  float acc = 0.f;
+  for (int i = 0; i < chunks; ++i) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(SK_STAGES - 2) : "memory");
+    __syncthreads();   // chunk i has landed for every thread, and everyone has left chunk i - 1, whose stage is refilled now
+    const int nxt = i + SK_STAGES - 1;
+    if (nxt < chunks) { load_w(nxt, nxt % SK_STAGES); load_a(nxt, nxt % SK_STAGES); }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    if (computes) {
+      const uint32_t ar = (uint32_t)__cvta_generic_to_shared(a_s[i % SK_STAGES][r]);
+      const uint32_t wr = (uint32_t)__cvta_generic_to_shared(w_s[i % SK_STAGES][c]);
+      float4 av[2][8], wv[2][8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { av[0][j] = sk_lds(ar + j * 16); wv[0][j] = sk_lds(wr + j * 16); }
+#pragma unroll
+      for (int b = 0; b < SK_KC / 32; ++b) {
+        if (b + 1 < SK_KC / 32) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            av[(b + 1) & 1][j] = sk_lds(ar + (b + 1) * 128 + j * 16);
+            wv[(b + 1) & 1][j] = sk_lds(wr + (b + 1) * 128 + j * 16);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          acc = fmaf(av[b & 1][j].x, wv[b & 1][j].x, acc);
+          acc = fmaf(av[b & 1][j].y, wv[b & 1][j].y, acc);
+          acc = fmaf(av[b & 1][j].z, wv[b & 1][j].z, acc);
+          acc = fmaf(av[b & 1][j].w, wv[b & 1][j].w, acc);
+        }
+      }
+    }
+  }
+  const int gm = m0 + r, gn = n0 + c;
+  if (computes && gm < m && gn < n) {
+    const size_t o = (size_t)gm * ldo + gn;
+    if (MODE == OUT_ACC) out[o] += acc;
+    else out[o] = acc;
+  }
+}
+
+template <int R>
+int launch_skinny(const float* a, const float* w, float* out, int m, int n, int k, int lda, int ldo, int mode, cudaStream_t s) {
+  constexpr int BNS = R == 16 ? 8 : 16;
+  constexpr int SMEM = (int)sizeof(float) * SK_STAGES * (BNS + R) * SK_LD;   // at most 50 KB
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(linear_skinny_kernel<R, OUT_ACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(linear_skinny_kernel<R, OUT_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) TLLM_FAIL(TLLM_ERR_CUDA, "linear_skinny: cannot reserve %d bytes of shared memory: %s", SMEM, cudaGetErrorString(e));
+    configured = true;
+  }
+  dim3 grid((n + BNS - 1) / BNS, (m + R - 1) / R);
+  if (mode == OUT_ACC)
+    TLLM_LAUNCH("linear_skinny", (linear_skinny_kernel<R, OUT_ACC>), grid, SK_THREADS, SMEM, s, a, w, out, m, n, k, lda, ldo);
+  else
+    TLLM_LAUNCH("linear_skinny", (linear_skinny_kernel<R, OUT_F32>), grid, SK_THREADS, SMEM, s, a, w, out, m, n, k, lda, ldo);
+  return TLLM_OK;
+}
+
 template <typename T>
 int launch(const void* a, const void* w, void* out, int m, int n, int k, int lda, int ldo, int mode, cudaStream_t s) {
   dim3 grid((n + BN - 1) / BN, (m + BM - 1) / BM);
@@ -89,11 +211,24 @@ int launch(const void* a, const void* w, void* out, int m, int n, int k, int lda
 
 }  // namespace tllm
 
+// skinny: 0 keeps the tile kernel even for few float32 rows (tests compare the two, which must agree to the bit)
 extern "C" int tllm_linear_generic(const void* a, const void* w, void* out, int m, int n, int k, int lda, int ldo,
-                                   int dtype, int mode, void* stream) {
+                                   int dtype, int mode, int skinny, void* stream) {
   TLLM_REQUIRE(m > 0 && n > 0 && k > 0, "linear: empty product %d x %d x %d", m, n, k);
   TLLM_REQUIRE(lda >= k && ldo >= n, "linear: row strides %d, %d are shorter than the rows %d, %d", lda, ldo, k, n);
   TLLM_REQUIRE((m + tllm::BM - 1) / tllm::BM <= 65535, "linear: %d rows exceed the grid", m);
+  if (dtype == TLLM_F32 && m <= 16 && skinny != 0 && k % 4 == 0 && lda % 4 == 0 && ((uintptr_t)a % 16) == 0 && ((uintptr_t)w % 16) == 0 &&
+      (mode == tllm::OUT_SAME || mode == tllm::OUT_F32 || mode == tllm::OUT_ACC)) {
+    const float* af = (const float*)a;
+    const float* wf = (const float*)w;
+    float* of = (float*)out;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (m <= 1) return tllm::launch_skinny<1>(af, wf, of, m, n, k, lda, ldo, mode, s);
+    if (m <= 2) return tllm::launch_skinny<2>(af, wf, of, m, n, k, lda, ldo, mode, s);
+    if (m <= 4) return tllm::launch_skinny<4>(af, wf, of, m, n, k, lda, ldo, mode, s);
+    if (m <= 8) return tllm::launch_skinny<8>(af, wf, of, m, n, k, lda, ldo, mode, s);
+    return tllm::launch_skinny<16>(af, wf, of, m, n, k, lda, ldo, mode, s);
+  }
   if (dtype == TLLM_F32) return tllm::launch<float>(a, w, out, m, n, k, lda, ldo, mode, (cudaStream_t)stream);
   if (dtype == TLLM_BF16) return tllm::launch<__nv_bfloat16>(a, w, out, m, n, k, lda, ldo, mode, (cudaStream_t)stream);
   TLLM_FAIL(TLLM_ERR_ARG, "linear: unknown dtype code %d", dtype);

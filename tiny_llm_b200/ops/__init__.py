@@ -309,6 +309,11 @@ def fused_qkv_preferred(m: int, n: int, k: int) -> bool:
     return m <= qkv_fused_rows or m > 128 or _cluster_slices(n, k) < 8
 
 
+# float32 products of at most 16 rows take a kernel of their own (one thread per output element, weights streamed
+# through shared memory); False keeps the 64 x 64 tiles.  Both give the same bits (tests compare them).
+linear_skinny = True
+
+
 def prefers_split(a: torch.Tensor, w: torch.Tensor) -> bool:
     """True when `linear` would cut K into slices for this product if it may add into a float32
     output: few rows (decode), so few weight tiles that the SMs only fill when K is split too.
@@ -358,7 +363,7 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool
         return
     lib = build.load_library("linear_generic")
     _check(lib, lib.tllm_linear_generic(_ptr(a), _ptr(w), _ptr(out), m, n, k, a.stride(0), out.stride(0),
-                                        _code(a.dtype), mode, _stream()))
+                                        _code(a.dtype), mode, int(linear_skinny), _stream()))
 
 
 def linear_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, block: int, workspace) -> None:
@@ -443,6 +448,11 @@ def _wide_splits(num_requests: int, num_kv_heads: int, max_kv_len: int) -> int:
     return splits if lo <= num_requests * num_kv_heads * splits <= hi else 0
 
 
+# The attention of the 32-bit path runs one warp or eight warps per (token, head), by the number of pairs; both give
+# the same bits.  True / False force one of them (tests compare the two).
+generic_attention_split: Optional[bool] = None
+
+
 def paged_attention(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, k_cache: torch.Tensor,
                     v_cache: torch.Tensor, block_table: torch.Tensor, batch, out: torch.Tensor, scale: float,
                     window: Optional[int] = None, workspace=None) -> None:
@@ -497,7 +507,8 @@ def paged_attention(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_d
         _ptr(qkv), qkv.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
         _ptr(batch.token_request), _ptr(batch.positions), _ptr(out), t, num_heads, num_kv_heads, head_dim,
         page_size, ctypes.c_longlong(k_cache.stride(0)), ctypes.c_longlong(k_cache.stride(1)),
-        ctypes.c_float(scale), int(window or 0), _code(qkv.dtype), _stream()))
+        ctypes.c_float(scale), int(window or 0), _code(qkv.dtype),
+        -1 if generic_attention_split is None else int(generic_attention_split), _stream()))
 
 
 def attention_tc_timing(head_dim: int = 64) -> Optional[dict]:
