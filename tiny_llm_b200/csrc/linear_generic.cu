@@ -5,7 +5,7 @@
 // so a row's result does not depend on its batch, to the bit.
 //   linear_generic_kernel: 64 x 64 tiles, 4 x 4 outputs per thread (many rows);
 //   linear_skinny_kernel: float32, at most 16 rows (decoded tokens): a CTA takes 8 or 16 weight rows and
-//     streams them through shared memory in chunks of 128 k (cp.async, four stages), one thread per
+//     streams them through shared memory in chunks of 128 k (cp.async, three stages), one thread per
 //     output element.  With so few rows the 64-row tile left 32 CTAs to stream a matrix that 148 SMs could
 //     pull, each with one load in flight per thread.
 // Reference counterpart: tiny_llm/ops/cuda/gemm.cu:67-106 (64x256 tile, 8x8 outputs per thread).
@@ -82,22 +82,13 @@ linear_generic_kernel(const T* __restrict__ a, const T* __restrict__ w, void* __
 }
 
 // ---------------------------------------------------------------- at most 16 rows, float32
-constexpr int SK_KC = 128, SK_LD = SK_KC + 4, SK_STAGES = 4, SK_THREADS = 128;
+constexpr int SK_KC = 128, SK_LD = SK_KC + 4, SK_STAGES = 3, SK_THREADS = 128;
 
 __device__ __forceinline__ void sk_cp16(float* dst, const float* src, bool ok) {
   const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
   const int bytes = ok ? 16 : 0;   // 0: the 16 bytes are filled with zeros, which leave a chain of fmaf as it is
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
 }
-// A shared-memory load that stays where it is written: the loads of the next 32 k are issued before the 32 dependent
-// fmaf of this block, so that a thread waits for shared memory once per block and not once per four fmaf (a warp
-// issues in order, and there are too few warps here to hide a load behind another warp).
-__device__ __forceinline__ float4 sk_lds(uint32_t addr) {
-  float4 v;
-  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
-  return v;
-}
-
 template <int R, int MODE>   // R rows of A per CTA (1, 2, 4, 8 or 16); BNS weight rows: R x BNS = at most 128 threads compute
 __global__ void __launch_bounds__(SK_THREADS)
 linear_skinny_kernel(const float* __restrict__ a, const float* __restrict__ w, float* __restrict__ out,
@@ -144,27 +135,16 @@ linear_skinny_kernel(const float* __restrict__ a, const float* __restrict__ w, f
     if (nxt < chunks) { load_w(nxt, nxt % SK_STAGES); load_a(nxt, nxt % SK_STAGES); }
     asm volatile("cp.async.commit_group;" ::: "memory");
     if (computes) {
-      const uint32_t ar = (uint32_t)__cvta_generic_to_shared(a_s[i % SK_STAGES][r]);
-      const uint32_t wr = (uint32_t)__cvta_generic_to_shared(w_s[i % SK_STAGES][c]);
-      float4 av[2][8], wv[2][8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) { av[0][j] = sk_lds(ar + j * 16); wv[0][j] = sk_lds(wr + j * 16); }
-#pragma unroll
-      for (int b = 0; b < SK_KC / 32; ++b) {
-        if (b + 1 < SK_KC / 32) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            av[(b + 1) & 1][j] = sk_lds(ar + (b + 1) * 128 + j * 16);
-            wv[(b + 1) & 1][j] = sk_lds(wr + (b + 1) * 128 + j * 16);
-          }
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          acc = fmaf(av[b & 1][j].x, wv[b & 1][j].x, acc);
-          acc = fmaf(av[b & 1][j].y, wv[b & 1][j].y, acc);
-          acc = fmaf(av[b & 1][j].z, wv[b & 1][j].z, acc);
-          acc = fmaf(av[b & 1][j].w, wv[b & 1][j].w, acc);
-        }
+      const float* ar = a_s[i % SK_STAGES][r];
+      const float* wr = w_s[i % SK_STAGES][c];
+#pragma unroll 8
+      for (int kk = 0; kk < SK_KC; kk += 4) {
+        const float4 av = *reinterpret_cast<const float4*>(ar + kk);
+        const float4 wv = *reinterpret_cast<const float4*>(wr + kk);
+        acc = fmaf(av.x, wv.x, acc);
+        acc = fmaf(av.y, wv.y, acc);
+        acc = fmaf(av.z, wv.z, acc);
+        acc = fmaf(av.w, wv.w, acc);
       }
     }
   }
@@ -179,7 +159,7 @@ linear_skinny_kernel(const float* __restrict__ a, const float* __restrict__ w, f
 template <int R>
 int launch_skinny(const float* a, const float* w, float* out, int m, int n, int k, int lda, int ldo, int mode, cudaStream_t s) {
   constexpr int BNS = R == 16 ? 8 : 16;
-  constexpr int SMEM = (int)sizeof(float) * SK_STAGES * (BNS + R) * SK_LD;   // at most 50 KB
+  constexpr int SMEM = (int)sizeof(float) * SK_STAGES * (BNS + R) * SK_LD;   // at most 38 KB
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(linear_skinny_kernel<R, OUT_ACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
