@@ -60,7 +60,8 @@ def find_headers():
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("TLLM_REFERENCE", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("TLLM_REFERENCE", os.path.join(HERE, "..", "..", "reference")),
+                    help="a tiny-llm checkout (default: TLLM_REFERENCE, else the folder `reference` beside this repository)")
     ap.add_argument("--jobs", type=int, default=os.cpu_count() or 4)
     ap.add_argument("--arch", default="sm_100")
     args = ap.parse_args()
