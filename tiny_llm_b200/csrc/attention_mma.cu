@@ -237,6 +237,26 @@ attention_decode_kernel(const AttnParams p) {
                                 [] { pdl_wait(); });
 }
 
+// A launch whose grid.z CTAs of every (x, y) form one thread-block cluster.
+template <typename Kernel>
+static cudaError_t launch_z_clusters(Kernel kernel, dim3 grid, int smem, cudaStream_t s, const AttnParams& p) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(128);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = grid.z;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
+  return cudaLaunchKernelEx(&cfg, kernel, p);
+}
+
 // Decoded tokens over short slices (at most four tiles each): one warp per tile.
 constexpr int WIDE_SMEM = (16 + 4 * 2 * BN) * LDS * 2 + TABLE_SLOTS * 4;
 template <bool CLUSTER>
@@ -288,7 +308,7 @@ extern "C" int tllm_attention_mma(const void* q, int q_row_stride, const void* k
   TLLM_REQUIRE(page_size > 0 && max_blocks > 0 && window >= 0 && splits >= 1, "attention_mma: page size %d, %d blocks, window %d, %d splits", page_size, max_blocks, window, splits);
   TLLM_REQUIRE(((uintptr_t)q % 16) == 0 && (q_row_stride % 8) == 0 && ((uintptr_t)kcache % 16) == 0 && ((uintptr_t)vcache % 16) == 0 &&
                (page_stride % 8) == 0 && (head_stride % 8) == 0, "attention_mma: rows must be 16-byte aligned");
-  TLLM_REQUIRE(splits == 1 || wide == 2 || scratch != nullptr, "attention_mma: %d splits need scratch", splits);
+  TLLM_REQUIRE(splits == 1 || (wide & 2) || scratch != nullptr, "attention_mma: %d splits need scratch", splits);
   TLLM_REQUIRE(nkv <= 65535 && splits <= 65535, "attention_mma: grid too large");
   const int group = nq / nkv;
   AttnParams p;
@@ -307,7 +327,10 @@ extern "C" int tllm_attention_mma(const void* q, int q_row_stride, const void* k
   cudaStream_t s = (cudaStream_t)stream;
   // wide != 0 (decoded tokens only): every slice has at most four tiles for the longest context of the step, and one
   // warp takes each (tllm_attention_mma_wide_fits says whether this head size leaves room for two such CTAs on an SM)
-  if (wide) {
+  const bool cluster = (wide & 2) != 0;   // bit 1: the slices of a (request, key/value head) merge inside a cluster
+  if (cluster) TLLM_REQUIRE((wide & 1) && splits >= 2 && splits <= 8,
+                            "attention_mma: a cluster merges the 2 to 8 slices of the kernel with one warp per tile (got %d)", splits);
+  if (wide & 1) {
     TLLM_REQUIRE(small && tllm_attention_mma_wide_fits() && max_kv_len > 0 && ((max_kv_len + BN - 1) / BN + splits - 1) / splits <= 4,
                  "attention_mma: one warp per tile needs decoded tokens and slices of at most four tiles (%d keys in %d slices)",
                  max_kv_len, splits);
@@ -318,24 +341,8 @@ extern "C" int tllm_attention_mma(const void* q, int q_row_stride, const void* k
       if (e != cudaSuccess) TLLM_FAIL(TLLM_ERR_CUDA, "attention_mma: cannot reserve %d bytes of shared memory: %s", WIDE_SMEM, cudaGetErrorString(e));
       configured = true;
     }
-    if (wide == 2) {
-      // the slices of a (request, key/value head) as one cluster, merged over distributed shared memory
-      TLLM_REQUIRE(splits >= 2 && splits <= 8, "attention_mma: a cluster merges 2 to 8 slices (got %d)", splits);
-      cudaLaunchConfig_t cfg = {};
-      cfg.gridDim = dim3((unsigned)n_requests, nkv, splits);
-      cfg.blockDim = dim3(128);
-      cfg.dynamicSmemBytes = WIDE_SMEM;
-      cfg.stream = s;
-      cudaLaunchAttribute attr[2];
-      attr[0].id = cudaLaunchAttributeClusterDimension;
-      attr[0].val.clusterDim.x = 1;
-      attr[0].val.clusterDim.y = 1;
-      attr[0].val.clusterDim.z = splits;
-      attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-      attr[1].val.programmaticStreamSerializationAllowed = 1;
-      cfg.attrs = attr;
-      cfg.numAttrs = pdl_enabled() ? 2 : 1;
-      cudaError_t e = cudaLaunchKernelEx(&cfg, attention_decode_wide_kernel<true>, p);
+    if (cluster) {
+      cudaError_t e = launch_z_clusters(attention_decode_wide_kernel<true>, dim3((unsigned)n_requests, nkv, splits), WIDE_SMEM, s, p);
       if (e != cudaSuccess) TLLM_FAIL(TLLM_ERR_CUDA, "attention_decode_wide (cluster of %d): %s", splits, cudaGetErrorString(e));
       return TLLM_OK;
     }

@@ -135,6 +135,59 @@ __device__ __forceinline__ void load_kv_rows(__nv_bfloat16* k_dst, __nv_bfloat16
   }
 }
 
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// two floats at `ptr` of this CTA's shared memory, read from the CTA of rank `rank` in the cluster
+__device__ __forceinline__ float2 ld_cluster_f32x2(const float* ptr, uint32_t rank) {
+  uint32_t remote;
+  float2 v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(ptr)), "r"(rank));
+  asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(remote) : "memory");
+  return v;
+}
+
+
+// The end of a decode work item whose key slices are the CTAs of one thread-block cluster (2 to 8 of them, the slice
+// index being the rank): each has left its result in its own shared memory (`c_o` [16][HD] unnormalised, `c_ml` [16][2]
+// maximum and sum), the cluster meets, and every CTA finishes a share of the output elements from all the peers'
+// results over distributed shared memory: no partial results in global memory and no merging kernel after this one.
+__device__ __forceinline__ void cluster_merge_and_write(const AttnParams& p, const float* c_o, const float* c_ml, int split,
+                                                        int tid, int rows_total, int tok0, int group, int kvh) {
+  cluster_sync_all();       // every slice's result lies in its CTA's shared memory
+  for (int idx = split * 128 + tid; idx < rows_total * (HD / 2); idx += p.splits * 128) {
+    const int r = idx / (HD / 2), d = (idx % (HD / 2)) * 2;
+    float2 ml[8], ov[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      ml[j] = make_float2(-CUDART_INF_F, 0.f);
+      ov[j] = make_float2(0.f, 0.f);
+      if (j < p.splits) {
+        ml[j] = ld_cluster_f32x2(c_ml + r * 2, (uint32_t)j);
+        ov[j] = ld_cluster_f32x2(c_o + r * HD + d, (uint32_t)j);
+      }
+    }
+    float m = -CUDART_INF_F;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) m = fmaxf(m, ml[j].x);
+    const float m_ref = m == -CUDART_INF_F ? 0.f : m;
+    float l = 0.f, acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float f = exp2f(ml[j].x - m_ref);    // 0 for a slice that saw no key of the row
+      l += f * ml[j].y;
+      acc0 += f * ov[j].x;
+      acc1 += f * ov[j].y;
+    }
+    const size_t th = (size_t)(tok0 + r / group) * p.nq + (size_t)(kvh * group + r % group);
+    const float inv = 1.f / l;
+    *reinterpret_cast<uint32_t*>(p.out + th * HD + d) = pack_bf16(acc0 * inv, acc1 * inv);
+  }
+  trace_mark(3);
+  cluster_sync_all();       // no CTA leaves while a peer still reads its shared memory
+}
+
 // Decoded tokens: at most 16 rows (new tokens x query heads of the group) of one request and
 // key/value head over one slice of its keys, by 128 threads (`tid` in [0, 128)) that share
 // `smem_raw` ((16 + 2 STAGES 64) rows of LDS elements, then TABLE_SLOTS ints) and meet at `sync()`.  The four warps split
@@ -363,19 +416,6 @@ __device__ __forceinline__ void load_kv_rows_warp(__nv_bfloat16* k_dst, __nv_bfl
   }
 }
 
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// two floats at `ptr` of this CTA's shared memory, read from the CTA of rank `rank` in the cluster
-__device__ __forceinline__ float2 ld_cluster_f32x2(const float* ptr, uint32_t rank) {
-  uint32_t remote;
-  float2 v;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(ptr)), "r"(rank));
-  asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(remote) : "memory");
-  return v;
-}
-
 // Decoded tokens, short slices: the same work as attention_decode_item for a slice of at most four 64-key tiles, with
 // ONE WARP PER TILE instead of four warps per tile.  Every warp gathers its own tile into buffers of its own (all
 // copies of the slice are in flight at once; tiles older than the step before `dep()`), the block meets once when
@@ -558,39 +598,7 @@ __device__ __forceinline__ void attention_decode_item_wide(const AttnParams& p, 
     }
   }
   trace_mark(2);       // merged and written
-  if (CLUSTER) {
-    cluster_sync_all();       // every slice's result lies in its CTA's shared memory
-    for (int idx = split * 128 + tid; idx < rows_total * (HD / 2); idx += p.splits * 128) {
-      const int r = idx / (HD / 2), d = (idx % (HD / 2)) * 2;
-      float2 ml[8], ov[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        ml[j] = make_float2(-CUDART_INF_F, 0.f);
-        ov[j] = make_float2(0.f, 0.f);
-        if (j < p.splits) {
-          ml[j] = ld_cluster_f32x2(c_ml + r * 2, (uint32_t)j);
-          ov[j] = ld_cluster_f32x2(c_o + r * HD + d, (uint32_t)j);
-        }
-      }
-      float m = -CUDART_INF_F;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) m = fmaxf(m, ml[j].x);
-      const float m_ref = m == -CUDART_INF_F ? 0.f : m;
-      float l = 0.f, acc0 = 0.f, acc1 = 0.f;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float f = exp2f(ml[j].x - m_ref);    // 0 for a slice that saw no key of the row
-        l += f * ml[j].y;
-        acc0 += f * ov[j].x;
-        acc1 += f * ov[j].y;
-      }
-      const size_t th = (size_t)(tok0 + r / group) * p.nq + (size_t)(kvh * group + r % group);
-      const float inv = 1.f / l;
-      *reinterpret_cast<uint32_t*>(p.out + th * HD + d) = pack_bf16(acc0 * inv, acc1 * inv);
-    }
-    trace_mark(3);
-    cluster_sync_all();       // no CTA leaves while a peer still reads its shared memory
-  }
+  if (CLUSTER) cluster_merge_and_write(p, c_o, c_ml, split, tid, rows_total, tok0, group, kvh);
 }
 
 // Merges the slices of one (token, head) `th` by one warp: out = sum_s 2^(m_s - m) o_s / sum_s 2^(m_s - m) l_s.

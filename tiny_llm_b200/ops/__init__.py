@@ -433,7 +433,8 @@ decode_wide_ctas = (96, 640) if os.environ.get("TLLM_DECODE_WIDE", "1") != "0" e
 # distributed shared memory, in place of partial results in global memory and a merging kernel behind it, while the
 # CTAs are at most 1.75 per SM: a cluster starts only when all its CTAs find room at once, and past that count whole
 # clusters wait for a second round (ms per step with / without, context 2,048: batch 4 0.744 / 0.753, 6 0.774 / 0.777,
-# 8 0.800 / 0.811, but 9 0.871 / 0.829, 12 0.931 / 0.872, 16 0.973 / 0.940).  TLLM_DECODE_CLUSTER=0 turns it off.
+# 8 0.800 / 0.811, but 9 0.871 / 0.829, 12 0.931 / 0.872, 16 0.973 / 0.940; the kernel that walks a slice tile by tile
+# gains nothing from it at any batch: 64 1.547 / 1.506, 32 1.080 / 1.085, 24 1.084 / 1.063).  TLLM_DECODE_CLUSTER=0 turns it off.
 decode_cluster_merge = os.environ.get("TLLM_DECODE_CLUSTER", "1") != "0"
 
 
@@ -485,15 +486,16 @@ def paged_attention(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_d
     if qkv.dtype == torch.bfloat16 and not force_generic and head_dim % 16 == 0 and 16 <= head_dim <= 256 and \
             qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0:
         lib = build.load_library("attention_mma", flags=(f"-DTLLM_HEAD_DIM={head_dim}",))
-        splits, wide = 1, 0
+        splits, wide = 1, 0   # wide: bit 0 = one warp per tile, bit 1 = the slices merge inside a cluster
         if workspace is not None:
             splits = _attention_splits(batch.num_requests, batch.max_q_len, group, num_kv_heads, batch.max_kv_len)
-            if batch.max_q_len * group <= 16 and lib.tllm_attention_mma_wide_fits():
-                wide_splits = _wide_splits(batch.num_requests, num_kv_heads, batch.max_kv_len)
+            if batch.max_q_len * group <= 16:
+                wide_splits = _wide_splits(batch.num_requests, num_kv_heads, batch.max_kv_len) \
+                    if lib.tllm_attention_mma_wide_fits() else 0
                 if wide_splits:
-                    splits, wide = wide_splits, (2 if _cluster_merge(batch.num_requests, num_kv_heads, wide_splits) else 1)
+                    splits, wide = wide_splits, (3 if _cluster_merge(batch.num_requests, num_kv_heads, wide_splits) else 1)
         scratch = None
-        if splits > 1 and wide != 2:
+        if splits > 1 and not wide & 2:
             scratch = workspace.get("attention_partials", (t * num_heads * splits * (head_dim + 2),), torch.float32)
         _check(lib, lib.tllm_attention_mma(
             _ptr(qkv), qkv.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
