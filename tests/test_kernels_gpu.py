@@ -526,6 +526,24 @@ def test_products_at_the_sizes_of_a_2048_token_prompt(ops):
     assert float(d2.max()) <= 5e-4 * max(1.0, float(ref2.abs().max())), float(d2.max())   # 32-bit sums of exact bfloat16 products
 
 
+@pytest.mark.parametrize("m,n,k", [(512, 2048, 5632), (1024, 2048, 2048), (300, 520, 1000), (129, 256, 512), (640, 2304, 712),
+                                   (200, 200, 456)])
+def test_residual_adding_product_of_few_tiles_with_its_k_in_runs(ops, m, n, k):
+    """Between 129 and about 1,000 tokens the residual-adding products have fewer 128 x 256 tiles than the GPU has SMs, and
+    every tile's K is cut into runs that different CTAs add into the output: widths and depths that fill no tile, a
+    last run that is shorter than the others, an output that already holds values."""
+    g = torch.Generator().manual_seed(m + n + k)
+    a = (torch.randn(m, k, generator=g)).to(torch.bfloat16)
+    w = (torch.randn(n, k, generator=g) / math.sqrt(k)).to(torch.bfloat16)
+    out0 = torch.randn(m, n, generator=g)
+    out = out0.to(DEV)
+    ops.linear(a.to(DEV), w.to(DEV), out, accumulate=True)
+    ops.check_status()
+    ref = (out0.double() + pl.linear(a.double(), w.double())).float()
+    d = float((out.cpu() - ref).abs().max())
+    assert d <= 5e-4 * max(1.0, float(ref.abs().max())), d   # 32-bit sums of exact bfloat16 products
+
+
 def test_attention_refuses_sizes_it_is_not_built_for(ops):
     from tiny_llm_b200.ops import KernelError
     z = torch.zeros(2, dtype=torch.int32, device=DEV)

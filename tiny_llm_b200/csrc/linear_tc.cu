@@ -69,6 +69,9 @@ struct ClusterArgs {
   // persistent kernel: the tiles of the last, incomplete round are cut into strips of `tail_width` columns so
   // that they spread over all SMs (0: no cutting); tiles [0, tail_from) are whole
   int tail_from, tail_width;
+  // persistent kernel, residual-adding epilogue only: every tile is cut into `k_splits` runs of k-blocks that
+  // different CTAs add into the output (0 or 1: whole K per tile); fills the SMs when there are few tiles
+  int k_splits, k_per;             // runs per tile and k-blocks per run (the last run may be shorter, never empty)
 };
 
 // Epilogue of one 128 x BN tile of C in the NORMAL orientation: this thread owns row `row` of the
@@ -211,7 +214,7 @@ __device__ __forceinline__ void store_tile_normal(uint32_t taddr, int row, int t
             for (int j = 0; j < 32; j += 4) {
               if (EPI == EPI_ADD_F32) {
                 // the add happens in L2 (a 16-byte reduction, nothing comes back): a load, an add and a store
-                // per chunk would make the epilogue a chain of round trips; this thread is the element's only writer
+                // per chunk would make the epilogue a chain of round trips
                 asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + j), "f"(v[j]), "f"(v[j + 1]), "f"(v[j + 2]),
                              "f"(v[j + 3]) : "memory");
               } else {
@@ -221,7 +224,10 @@ __device__ __forceinline__ void store_tile_normal(uint32_t taddr, int row, int t
           } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              if (n0 + c + j < rows_b) dst[j] = EPI == EPI_ADD_F32 ? dst[j] + v[j] : v[j];
+              if (n0 + c + j < rows_b) {
+                if (EPI == EPI_ADD_F32) atomicAdd(dst + j, v[j]);   // (runs of K of the same tile add side by side)
+                else dst[j] = v[j];
+              }
           }
         }
       }
@@ -690,10 +696,15 @@ linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
   // Work items: the whole tiles [0, tail_from), then the tiles of the last, incomplete round cut into strips
   // of tail_width columns (160 tiles on 148 SMs: 148 whole tiles, then 12 x 4 strips for 48 of the SMs,
   // instead of 12 whole tiles for 12 of them).  Item i -> (row tile, first column, width).
-  const int whole = ca.tail_width > 0 ? ca.tail_from : n_tiles;
-  const int strips = ca.tail_width > 0 ? BN / ca.tail_width : 1;
-  const int n_items = whole + (n_tiles - whole) * strips;
-  auto item_tile = [&](int i) { return i < whole ? i : whole + (i - whole) / strips; };
+  // With K splits (residual-adding products of few tiles; no strips then) item i is run i / n_tiles of tile i % n_tiles.
+  const int k_splits = (EPI == EPI_ADD_F32 && ca.k_splits > 1) ? ca.k_splits : 1;
+  const int k_per = k_splits > 1 ? ca.k_per : k_blocks;
+  const int whole = k_splits > 1 ? n_tiles * k_splits : (ca.tail_width > 0 ? ca.tail_from : n_tiles);
+  const int strips = (k_splits == 1 && ca.tail_width > 0) ? BN / ca.tail_width : 1;
+  const int n_items = k_splits > 1 ? whole : whole + (n_tiles - whole) * strips;
+  auto item_tile = [&](int i) { return k_splits > 1 ? i % n_tiles : (i < whole ? i : whole + (i - whole) / strips); };
+  auto item_kb0 = [&](int i) { return k_splits > 1 ? (i / n_tiles) * k_per : 0; };
+  auto item_kbn = [&](int i) { return k_splits > 1 ? max(0, min(k_blocks, (i / n_tiles + 1) * k_per) - (i / n_tiles) * k_per) : k_blocks; };
   auto item_col = [&](int i) { return (item_tile(i) / tiles_m) * BN + (i < whole ? 0 : ((i - whole) % strips) * ca.tail_width); };
   auto item_width = [&](int i) { return i < whole ? BN : ca.tail_width; };
 
@@ -713,12 +724,12 @@ linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
   // before this grid waits for its predecessors.
   pdl_trigger();
   const int first_tile = blockIdx.x;
-  const int n_pre = first_tile < whole ? min(k_blocks, STAGES) : 0;   // (a CTA's first item is a whole tile, or it has none worth the trouble)
+  const int n_pre = first_tile < whole ? min(item_kbn(first_tile), STAGES) : 0;   // (a CTA's first item is a whole tile, or it has none worth the trouble)
   if (warp == 0 && lane == 0) {
-    const int tn = first_tile / tiles_m;
+    const int tn = item_tile(first_tile) / tiles_m, kb0 = item_kb0(first_tile);
     for (int i = 0; i < n_pre; ++i) {
       mbar_expect_tx(&full_bar[i], L::STAGE_BYTES);
-      tma_load_2d(smem + i * L::STAGE_BYTES + L::A_BYTES, &map_b, i * BK, tn * BN, &full_bar[i]);
+      tma_load_2d(smem + i * L::STAGE_BYTES + L::A_BYTES, &map_b, (kb0 + i) * BK, tn * BN, &full_bar[i]);
     }
   }
   pdl_wait();
@@ -730,7 +741,8 @@ linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     bool ok = true;
     for (int t = first_tile; t < n_items && ok; t += gridDim.x) {
       const int tm = item_tile(t) % tiles_m, col = item_col(t), width = item_width(t);
-      for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+      const int kb0 = item_kb0(t), kb1 = kb0 + item_kbn(t);
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
         const int s = it % STAGES;
         uint8_t* a_dst = smem + s * L::STAGE_BYTES;
         const bool pre = it < n_pre;
@@ -755,7 +767,8 @@ linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       if (!ok) break;
       tc_fence_after();
       const uint32_t d_tmem = tmem_u + buf * BN;
-      for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+      const int kb0 = item_kb0(t), kb1 = kb0 + item_kbn(t);
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
         const int s = it % STAGES;
         ok = __all_sync(0xffffffffu, mbar_wait(&full_bar[s], (it / STAGES) & 1, abort_flag));
         if (!ok) break;
@@ -764,7 +777,7 @@ linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         if (elect_one()) {
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)
-            umma_bf16_lo(d_tmem, a_lo + (k * UMMA_K * 2 >> 4), b_lo + (k * UMMA_K * 2 >> 4), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_bf16_lo(d_tmem, a_lo + (k * UMMA_K * 2 >> 4), b_lo + (k * UMMA_K * 2 >> 4), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           umma_commit(&empty_bar[s]);
         }
         __syncwarp();
@@ -789,7 +802,7 @@ linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quad * 32) << 16);
       if (EPI == EPI_ROPE_KV)
         store_tile_rope_kv<BN>(taddr, (item_tile(t) % tiles_m) * BM + row, item_col(t), item_width(t), rows_a, rows_b, out, ldo, ca);
-      else store_tile_normal<BN, EPI>(taddr, row, t % tiles_m, t / tiles_m, rows_a, rows_b, out, ldo);   // (no strips for these)
+      else store_tile_normal<BN, EPI>(taddr, row, item_tile(t) % tiles_m, item_tile(t) / tiles_m, rows_a, rows_b, out, ldo);   // (no strips for these)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buf]);   // four arrivals free the accumulator
@@ -861,10 +874,21 @@ static int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, void*
     configured = true;
   }
   const int tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
-  const int grid = tiles < sm_count ? tiles : sm_count;
   ClusterArgs args = ca;
   args.tail_from = tiles;
   args.tail_width = 0;
+  // a residual-adding product of few tiles (fewer than 2,048 tokens): its K in runs of at least four k-blocks,
+  // as many as fill the SMs; the runs add into the output with the same reductions as whole tiles do
+  const int kb = (k + BK - 1) / BK;
+  args.k_splits = 1;
+  args.k_per = kb;
+  if (EPI == EPI_ADD_F32 && 2 * tiles <= sm_count && kb >= 8) {
+    const int want = std::min(sm_count / tiles, kb / 4);
+    args.k_per = (kb + want - 1) / want;
+    args.k_splits = (kb + args.k_per - 1) / args.k_per;
+  }
+  const int items = tiles * args.k_splits;
+  const int grid = items < sm_count ? items : sm_count;
   const CUtensorMap* strip_map = &mb;
   CUtensorMap ms;
   if (EPI == EPI_ROPE_KV && tiles > sm_count && tiles % sm_count != 0) {
