@@ -466,6 +466,12 @@ def main():
         points[key] = round(b * 1e3 / pms, 1)
         fracs[key] = round(decode_bytes(model, runner, b, ctx, itemsize) / (pms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
     prefill_ms = timed_prefill(runner, 2048)
+    if not args.quick and dtype == torch.bfloat16:
+        # shorter prompt steps: fewer tiles than SMs in every product
+        for tt in (512, 1024):
+            pms = timed_prefill(runner, tt, repeats=3)
+            points[f"prefill_{tt}"] = round(tt * 1e3 / pms, 1)
+            fracs[f"prefill_{tt}"] = round(prefill_flops(cfg, args.layers, tt) / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)
 
     pipe = Pipeline.from_model(cfg, model, dtype=dtype, device=0, page_size=PAGE, max_tokens=BATCH * CONTEXT,
                                max_requests=BATCH, max_tokens_per_step=2048, chunk=1024)
