@@ -544,6 +544,26 @@ def test_residual_adding_product_of_few_tiles_with_its_k_in_runs(ops, m, n, k):
     assert d <= 5e-4 * max(1.0, float(ref.abs().max())), d   # 32-bit sums of exact bfloat16 products
 
 
+@pytest.mark.parametrize("m,inter,k", [(512, 5632, 2048), (1024, 5632, 520), (600, 5632, 264), (1024, 2560, 1024), (1000, 2688, 72)])
+def test_gate_up_product_with_its_last_round_in_strips(ops, m, inter, k):
+    """More 128 x 256 tiles than SMs and an incomplete last round: its tiles run as four or two strips of gate columns
+    with their up columns (176 tiles -> 148 + 28 x 4; 352 -> 296 + 56 x 2; 220 -> 148 + 72 x 2; 160 -> 148 + 12 x 4;
+    168 -> 148 + 20 x 4 with rows that fill no tile)."""
+    from tiny_llm_b200.engine import Workspace
+    from tiny_llm_b200.parts import interleave_gate_up
+    g = torch.Generator().manual_seed(m + inter + k)
+    a = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    wg = (torch.randn(inter, k, generator=g) / math.sqrt(k)).to(torch.bfloat16)
+    wu = (torch.randn(inter, k, generator=g) / math.sqrt(k)).to(torch.bfloat16)
+    act = torch.full((m, inter), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.linear_swiglu(a.to(DEV), interleave_gate_up(wg, wu, 128).to(DEV), act, 128, Workspace(DEV))
+    ops.check_status()
+    ref = pl.silu(pl.linear(a.float(), wg.float())) * pl.linear(a.float(), wu.float())
+    d = (act.float().cpu() - ref).abs()
+    assert not torch.isnan(act).any()
+    assert float(d.max()) <= tol("bfloat16", max(1.0, float(ref.abs().max()))), float(d.max())
+
+
 def test_attention_refuses_sizes_it_is_not_built_for(ops):
     from tiny_llm_b200.ops import KernelError
     z = torch.zeros(2, dtype=torch.int32, device=DEV)

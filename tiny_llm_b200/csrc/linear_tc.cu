@@ -235,6 +235,37 @@ __device__ __forceinline__ void store_tile_normal(uint32_t taddr, int row, int t
   }
 }
 
+// SiLU(gate) * up for a STRIP of a gate/up tile: the accumulator holds `w` gate columns and, behind them, the `w`
+// matching up columns; the strip's results go to output columns [out_col, out_col + w).  This thread owns row m.
+__device__ __forceinline__ void store_strip_swiglu(uint32_t taddr, int m, int out_col, int w, int rows_a, int n_out,
+                                                   __nv_bfloat16* __restrict__ out, int ldo) {
+  const bool vec_ok = (reinterpret_cast<uintptr_t>(out) & 15) == 0 && (ldo & 7) == 0;
+#pragma unroll 1
+  for (int c = 0; c < w; c += 32) {
+    float g[32], u[32];
+    tmem_ld32(taddr + c, g);
+    tmem_ld32(taddr + w + c, u);
+    if (m < rows_a && out_col + c < n_out) {
+      __nv_bfloat16* dst = out + (size_t)m * ldo + out_col + c;
+      if (out_col + c + 32 <= n_out && vec_ok) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          uint4 pk;
+          __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            h[e] = __floats2bfloat162_rn(silu_f(g[j + 2 * e]) * u[j + 2 * e], silu_f(g[j + 2 * e + 1]) * u[j + 2 * e + 1]);
+          *reinterpret_cast<uint4*>(dst + j) = pk;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (out_col + c + j < n_out) dst[j] = __float2bfloat16_rn(silu_f(g[j]) * u[j]);
+      }
+    }
+  }
+}
+
 // rows_a / rows_b: extents of the 128-row operand and of the BN-row operand.  NORMAL: rows_a = M,
 // rows_b = N, out[M, N].  SWAP: rows_a = N (weights), rows_b = M (tokens), out[M, N] all the same.
 template <int BN, int STAGES, bool SWAP, int EPI>
@@ -705,7 +736,10 @@ linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
   auto item_tile = [&](int i) { return k_splits > 1 ? i % n_tiles : (i < whole ? i : whole + (i - whole) / strips); };
   auto item_kb0 = [&](int i) { return k_splits > 1 ? (i / n_tiles) * k_per : 0; };
   auto item_kbn = [&](int i) { return k_splits > 1 ? max(0, min(k_blocks, (i / n_tiles + 1) * k_per) - (i / n_tiles) * k_per) : k_blocks; };
-  auto item_col = [&](int i) { return (item_tile(i) / tiles_m) * BN + (i < whole ? 0 : ((i - whole) % strips) * ca.tail_width); };
+  // (a strip of a gate/up tile: tail_width / 2 gate rows from item_col on, and the matching up rows BN / 2 further on)
+  auto item_col = [&](int i) {
+    return (item_tile(i) / tiles_m) * BN + (i < whole ? 0 : ((i - whole) % strips) * (EPI == EPI_SWIGLU ? ca.tail_width / 2 : ca.tail_width));
+  };
   auto item_width = [&](int i) { return i < whole ? BN : ca.tail_width; };
 
   if (threadIdx.x == 0) {
@@ -749,7 +783,12 @@ linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         if (!pre) {
           if (!mbar_wait(&empty_bar[s], ((it / STAGES) & 1) ^ 1, abort_flag)) { *abort_flag = 1; atomicExch(status, ERR_PRODUCER); ok = false; break; }
           mbar_expect_tx(&full_bar[s], (uint32_t)(L::A_BYTES + width * BK * 2));
-          tma_load_2d(a_dst + L::A_BYTES, width == BN ? &map_b : &map_b_strip, kb * BK, col, &full_bar[s]);
+          if (EPI == EPI_SWIGLU && width != BN) {   // the strip's gate rows, then its up rows behind them
+            tma_load_2d(a_dst + L::A_BYTES, &map_b_strip, kb * BK, col, &full_bar[s]);
+            tma_load_2d(a_dst + L::A_BYTES + (width / 2) * BK * 2, &map_b_strip, kb * BK, col + BN / 2, &full_bar[s]);
+          } else {
+            tma_load_2d(a_dst + L::A_BYTES, width == BN ? &map_b : &map_b_strip, kb * BK, col, &full_bar[s]);
+          }
         }
         tma_load_2d(a_dst, &map_a, kb * BK, tm * BM, &full_bar[s]);
       }
@@ -802,7 +841,11 @@ linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quad * 32) << 16);
       if (EPI == EPI_ROPE_KV)
         store_tile_rope_kv<BN>(taddr, (item_tile(t) % tiles_m) * BM + row, item_col(t), item_width(t), rows_a, rows_b, out, ldo, ca);
-      else store_tile_normal<BN, EPI>(taddr, row, item_tile(t) % tiles_m, item_tile(t) / tiles_m, rows_a, rows_b, out, ldo);   // (no strips for these)
+      else if (EPI == EPI_SWIGLU && item_width(t) != BN)
+        store_strip_swiglu(taddr, (item_tile(t) % tiles_m) * BM + row,
+                           (item_tile(t) / tiles_m) * (BN / 2) + (item_col(t) - (item_tile(t) / tiles_m) * BN), item_width(t) / 2,
+                           rows_a, rows_b / 2, reinterpret_cast<__nv_bfloat16*>(out), ldo);
+      else store_tile_normal<BN, EPI>(taddr, row, item_tile(t) % tiles_m, item_tile(t) / tiles_m, rows_a, rows_b, out, ldo);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buf]);   // four arrivals free the accumulator
@@ -900,6 +943,17 @@ static int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, void*
       strip_map = &ms;
     }
   }
+  if (EPI == EPI_SWIGLU && tiles > sm_count && tiles % sm_count != 0 && w_ptr != nullptr && n % BN == 0) {
+    // gate/up: the tiles of the incomplete last round as 4 or 2 strips (32 or 64 gate columns with their up columns),
+    // as many as still fit one round
+    const int left = tiles % sm_count;
+    const int parts = left * 4 <= sm_count ? 4 : (left * 2 <= sm_count ? 2 : 1);
+    if (parts > 1 && make_map(&ms, w_ptr, n, k, k, BN / 2 / parts)) {
+      args.tail_from = tiles - left;
+      args.tail_width = BN / parts;
+      strip_map = &ms;
+    }
+  }
   TLLM_LAUNCH("linear_tc_persistent", kern, grid, THREADS, L::TOTAL, s, ma, mb, *strip_map, out, m, n, (k + BK - 1) / BK, ldo, args, status);
   return TLLM_OK;
 }
@@ -965,7 +1019,7 @@ extern "C" int tllm_linear_tc(const void* a, const void* w, void* out, int m, in
       case EPI_BF16: return launch_persistent<EPI_BF16>(ma, mb, out, m, n, k, ldo, status, s);
       case EPI_F32: return launch_persistent<EPI_F32>(ma, mb, out, m, n, k, ldo, status, s);
       case EPI_ADD_F32: return launch_persistent<EPI_ADD_F32>(ma, mb, out, m, n, k, ldo, status, s);
-      case EPI_SWIGLU: return launch_persistent<EPI_SWIGLU>(ma, mb, out, m, n, k, ldo, status, s);
+      case EPI_SWIGLU: return launch_persistent<EPI_SWIGLU>(ma, mb, out, m, n, k, ldo, status, s, ClusterArgs(), w);
     }
     TLLM_FAIL(TLLM_ERR_ARG, "linear_tc: unknown epilogue %d", epi);
   }
