@@ -36,7 +36,7 @@ CONTEXT = 2048
 BATCH = 8
 PAGE = 16
 REPEATS = 5
-FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
 def peaks():
@@ -45,7 +45,8 @@ def peaks():
         try:
             with open(path) as f:
                 d = json.load(f)
-            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                    "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
         except (ValueError, KeyError):
             pass
     return dict(FALLBACK_PEAKS)
@@ -515,8 +516,12 @@ def main():
         "e2e": {"value": round(BATCH * 1e3 / e2e_ms, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * (BATCH + 1)},
         "gpu_launches": launched,
+        # frac: of the burst peak of a library product timed alone; frac_of_sustained: of what the same product holds
+        # back to back under the power cap, which is the state of the GPU inside a step of thousands of tokens
         "prefill": {"value": round(t * 1e3 / prefill_ms, 1), "tokens": t, "ms": round(prefill_ms, 3),
-                    "frac": None if peak_flops is None else round(flops / (prefill_ms * 1e-3) / peak_flops, 4)},
+                    "frac": None if peak_flops is None else round(flops / (prefill_ms * 1e-3) / peak_flops, 4),
+                    "frac_of_sustained": None if peak_flops is None else
+                    round(flops / (prefill_ms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points, "points_frac": fracs, "clocks": clocks,
