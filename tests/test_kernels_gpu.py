@@ -376,6 +376,53 @@ def test_paged_attention_on_tcgen05(ops, hd, nq, nkv, page):
     assert float(p[450]) > 0.9
 
 
+@pytest.mark.parametrize("split", [True, False])
+@pytest.mark.parametrize("hd,nq,nkv,page", [(64, 32, 4, 16), (128, 8, 2, 32), (64, 4, 4, 8)])
+def test_attention_of_decoded_tokens_beside_portions(ops, hd, nq, nkv, page, split, monkeypatch):
+    """A step as the scheduler lays it out: requests with one token first, then portions.  The decoded tokens run on
+    the decode kernel and the portions on the tcgen05 kernel, as two launches over two runs of the same tables
+    (`split`), or all of them on the tcgen05 kernel; both against the plain implementation."""
+    from tiny_llm_b200.engine import Workspace
+    monkeypatch.setattr(ops, "split_mixed_attention", split)
+    dtype = "bfloat16"
+    lens = [1500, 1, 333, 64, 700, 300, 40]
+    q_lens = [1, 1, 1, 1, 389, 300, 17]
+    n_req = len(lens)
+    table, k_cache, v_cache, ks, vs = paged_setup(dtype, n_req, lens, nkv, hd, page, seed=nq + page + 1)
+    g = torch.Generator().manual_seed(18)
+    t = sum(q_lens)
+    qkv = torch.randn(t, (nq + 2 * nkv) * hd, generator=g).to(DT[dtype])
+    # a far key among 1,500 for the first decoded token
+    qkv[0, :hd] *= 6.0
+    ks[0][77, 0] = (qkv[0, :hd] / qkv[0, :hd].float().norm() * 8.0).to(DT[dtype])
+    k_cache[int(table[0, 77 // page]), 0, 77 % page] = ks[0][77, 0]
+    pos = torch.cat([torch.arange(l - n, l, dtype=torch.int32) for l, n in zip(lens, q_lens)])
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
+    starts = torch.tensor([l - n for l, n in zip(lens, q_lens)], dtype=torch.int32)
+    tok_req = torch.cat([torch.full((n,), r, dtype=torch.int32) for r, n in enumerate(q_lens)])
+    batch = types.SimpleNamespace(token_request=tok_req.to(DEV), positions=pos.to(DEV), cu_q=cu.to(DEV),
+                                  q_start=starts.to(DEV), num_requests=n_req, max_q_len=max(q_lens), max_kv_len=2048,
+                                  num_leading_decodes=4)
+    out = torch.full((t, nq * hd), float("nan"), dtype=DT[dtype], device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    before = ops.launches
+    ops.paged_attention(qkv.to(DEV), nq, nkv, hd, k_cache.to(DEV), v_cache.to(DEV), table.to(DEV), batch, out,
+                        scale, None, Workspace(DEV))
+    ops.check_status()
+    assert ops.launches - before == (2 if split else 1)
+    out = out.float().cpu()
+    assert not torch.isnan(out).any()
+    cur = 0
+    for r, (l, n) in enumerate(zip(lens, q_lens)):
+        q = qkv[cur: cur + n, : nq * hd].float().view(n, nq, hd)
+        ref = pl.attention(q, ks[r].float(), vs[r].float(), pos[cur: cur + n], quant=pl.bf16_quant).reshape(n, nq * hd)
+        d = float((out[cur: cur + n] - ref).abs().max())
+        assert d <= tol(dtype, max(1.0, float(ref.abs().max()))), (r, d)
+        cur += n
+    p = torch.softmax((qkv[0, :hd].float() * scale) @ ks[0][:lens[0], 0].float().t(), 0)
+    assert float(p[77]) > 0.9
+
+
 LENS8 = [2048, 2047, 1000, 700, 65, 1, 1999, 513]
 
 

@@ -180,3 +180,54 @@ def test_decoding_across_a_graph_bucket_of_the_context(tmp_path_factory, dtype):
     got = ru.run_trace_runner(runner, steps, cfg["vocab_size"])
     assert runner.graph_replays >= 20 and len(runner._graphs) == 2       # one graph per bucket, both replayed
     ru.compare(got, ref, "g", dtype, "decoding across a graph bucket", ref32)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_steps_run_again_from_the_tape_of_their_launches(cases, name, dtype):
+    """A step whose sizes (tokens, requests, wanted places, longest portion, context bucket) were seen before is not
+    walked through the model's Python code again: the launches noted the first time run again, and the kernels read
+    the new ids, positions, tables and slots from device memory.  Two rounds of the same shapes with other contents
+    (other ids, other request ids, other pages since the pool is used again) on a runner with tapes and on one
+    without: in 32-bit the logits agree to the bit, in bfloat16 within what atomic sums allow, and both match plain."""
+    from tiny_llm_b200.engine import StepEntry
+    model_dir, cfg, page, reqs, ref = cases[name]
+    lens = [37, 5, 64, 18]
+    rounds = [ru.make_requests(cfg["vocab_size"], lens, 500 + r) for r in range(3)]
+    outs = {}
+    for taped in (True, False):
+        runner = runner_for(model_dir, dtype, page, 4 * 128)
+        runner.use_tapes = taped
+        got = []
+        for r, rq in enumerate(rounds):
+            ids = list(rq)
+            toks = [rq[i] for i in ids]
+            live = [f"{r}-{i}" for i in ids]
+            for rid in live:
+                runner.cache.add_request(rid)
+            # a portion of each beside single tokens of others, cut so that the shapes repeat from round to round
+            steps = [[(0, 0, 20, [19]), (1, 0, 3, [])],
+                     [(0, 20, 37, [16]), (1, 3, 4, [0]), (2, 0, 40, [])],
+                     [(1, 4, 5, [0]), (2, 40, 64, [23]), (3, 0, 18, [0, 17])]]
+            for step in steps:
+                entries = [StepEntry(live[q], toks[q][a:b], want) for q, a, b, want in step]
+                logits = runner.step(entries)
+                got.append(logits.float().cpu().clone())
+            for rid in live:
+                runner.cache.free_request(rid)
+        outs[taped] = (got, runner.tape_replays)
+    assert outs[True][1] >= 6 and outs[False][1] == 0        # rounds two and three ran from the tapes of round one
+    for a, b in zip(outs[True][0], outs[False][0]):
+        if dtype == "float32":
+            assert torch.equal(a, b)
+        else:
+            assert float((a - b).abs().max()) <= 1e-2 * max(1.0, float(b.abs().max()))
+    # and against the plain implementation: the last place of request 0 of every round
+    import plain_llama as pl
+    c, w = pl.load_config(model_dir), pl.load_weights(model_dir)
+    for r, rq in enumerate(rounds):
+        t0 = rq[list(rq)[0]]
+        want = pl.forward(c, w, t0, dtype=torch.float32)[36]
+        have = outs[True][0][3 * r + 1][0]
+        tol = 2e-5 if dtype == "float32" else 0.05
+        assert float((have - want).abs().max()) <= tol * max(1.0, float(want.abs().max()))

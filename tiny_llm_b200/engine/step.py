@@ -14,6 +14,8 @@ A token's position is the number of tokens its request held before it; key j is 
 j <= position, whatever mix of portions and decoded tokens the batch has."""
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass, field
 from typing import Hashable, List, Optional, Sequence
 
@@ -78,6 +80,7 @@ class StepBatch:
     # host copies for parts that plan on the host
     host_q_lens: List[int] = field(default_factory=list)
     host_kv_lens: List[int] = field(default_factory=list)
+    num_leading_decodes: int = 0   # how many requests at the front of the batch bring exactly one token
 
 
 class StepContext:
@@ -147,6 +150,11 @@ class ModelRunner:
         self._decode_layouts = {}
         self.last_h2d_bytes = 0     # bytes of the last step's metadata copy to the device
         self.graph_replays = 0
+        # Tapes of the launches of all other steps, keyed by what their launches depend on; a step with a key seen
+        # before runs its tape again instead of the model's Python code (a quarter of the host time per launch)
+        self.use_tapes = self.use_graphs and os.environ.get("TLLM_TAPES", "1") != "0"
+        self._tapes = {}
+        self.tape_replays = 0
 
     # ---- metadata
     def _region(self, buf, name, n=None):
@@ -259,7 +267,8 @@ class ModelRunner:
             q_start=self._region(dev, "q_start", r), kv_len=self._region(dev, "kv_len", r),
             slots=self._region(dev, "slots", r), logit_rows=self._region(dev, "logit_rows", n_out),
             groups=groups, max_q_len=max(q_lens), max_kv_len=max(kv_after),
-            host_q_lens=q_lens, host_kv_lens=kv_after)
+            host_q_lens=q_lens, host_kv_lens=kv_after,
+            num_leading_decodes=next((i for i, n in enumerate(q_lens) if n != 1), r))
 
     def _table_row(self, gi: int, rid, table: List[int]) -> np.ndarray:
         """The request's block table as a cached int32 row of max_blocks entries (-1 beyond its pages)."""
@@ -404,10 +413,46 @@ class ModelRunner:
             bucket *= 2
         return (batch.num_requests, bucket)
 
+    def _tape_key(self, batch: StepBatch):
+        """What the launches of a step are made from on the host: the numbers of tokens, requests and wanted places,
+        the longest portion, the bucket of the longest context (it fixes how attention slices the keys), how many
+        requests at the front bring one token (attention runs those apart), the stream and the kernel switches.  All else (ids, positions, tables, slots) the kernels read from device memory at
+        addresses that do not move."""
+        if not self.use_tapes:
+            return None
+        bucket = 256
+        while bucket < batch.max_kv_len:
+            bucket *= 2
+        return (batch.num_tokens, batch.num_requests, batch.num_logits, batch.max_q_len, bucket,
+                batch.num_leading_decodes, torch.cuda.current_stream(self.device).cuda_stream, ops.knobs())
+
+    MAX_TAPES = 64
+
+    def _run_taped(self, batch: StepBatch):
+        key = self._tape_key(batch)
+        if key is None:
+            return self.model.forward(StepContext(self, batch))
+        batch.max_kv_len = key[4]
+        held = self._tapes.get(key)
+        if held is not None:
+            ops.replay_tape(held[0])
+            self.tape_replays += 1
+            return held[1]
+        ops.begin_tape()
+        try:
+            logits = self.model.forward(StepContext(self, batch))
+        finally:
+            tape = ops.end_tape()
+        if len(self._tapes) >= self.MAX_TAPES:
+            self._tapes.pop(next(iter(self._tapes)))     # the oldest
+        # the tape's launches point into these buffers: keep them alive even if the workspace grows
+        self._tapes[key] = (tape, logits, list(self.workspace._buffers.values()))
+        return logits
+
     def _run(self, entries, batch: StepBatch):
         key = self._graph_key(entries, batch)
         if key is None:
-            return self.model.forward(StepContext(self, batch))
+            return self._run_taped(batch)
         batch.max_kv_len = key[1]
         held = self._graphs.get(key)
         if held is None:

@@ -58,11 +58,46 @@ def set_pdl(on: bool) -> None:
         lib.tllm_set_pdl(1 if _pdl else 0)
 
 
-def _check(lib, rc: int):
+_tape = None   # while a list: every launch is also noted there as (library, function, arguments), see begin_tape()
+
+
+def _call(lib, fn, *args):
+    """Calls one entry point of a compiled library (one kernel launch, or a few) and raises its message if it refuses."""
     global launches
-    if rc != 0:
+    if fn(*args) != 0:
         raise KernelError(lib.tllm_last_error().decode())
     launches += 1
+    if _tape is not None:
+        _tape.append((lib, fn, args))
+
+
+def begin_tape() -> None:
+    """From here to end_tape() the launches are noted as they are made: the compiled functions with the very argument
+    objects they got.  A step whose launches depend on nothing but what the caller knows (the sizes of the step and the
+    addresses of buffers that stay where they are) can be run again from such a tape without walking the model's
+    Python code: the step's tables are read by the kernels from device memory, as in a captured graph."""
+    global _tape
+    _tape = []
+
+
+def end_tape():
+    global _tape
+    tape, _tape = _tape, None
+    return tape
+
+
+def replay_tape(tape) -> None:
+    global launches
+    for lib, fn, args in tape:
+        if fn(*args) != 0:
+            raise KernelError(lib.tllm_last_error().decode())
+    launches += len(tape)
+
+
+def knobs():
+    """The module's switches that decide which kernels a step launches; a tape or graph holds for one setting of them."""
+    return (force_generic, split_k, cluster_mask, attention_tc, decode_wide_ctas, decode_cluster_merge, qkv_fused_rows,
+            linear_skinny, generic_attention_split, split_mixed_attention, _pdl)
 
 
 def _i32(t: Optional[torch.Tensor], name: str):
@@ -100,7 +135,7 @@ def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> N
             or tokens.numel() != t:
         raise KernelError("embedding: shapes or dtypes do not fit")
     lib = build.load_library("elementwise")
-    _check(lib, lib.tllm_embedding(_ptr(tokens), _ptr(table), _ptr(out), t, h, _code(table.dtype), _stream()))
+    _call(lib, lib.tllm_embedding, _ptr(tokens), _ptr(table), _ptr(out), t, h, _code(table.dtype), _stream())
 
 
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
@@ -115,8 +150,8 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tenso
             (rows is None and n != x.shape[0]) or (rows is not None and rows.numel() != n):
         raise KernelError("rms_norm: shapes or dtypes do not fit")
     lib = build.load_library("elementwise")
-    _check(lib, lib.tllm_rms_norm(_ptr(x), _ptr(weight), _ptr(out), _ptr(rows), n, h, ctypes.c_float(eps),
-                                  _code(out.dtype), _stream()))
+    _call(lib, lib.tllm_rms_norm, _ptr(x), _ptr(weight), _ptr(out), _ptr(rows), n, h, ctypes.c_float(eps),
+                                  _code(out.dtype), _stream())
 
 
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, block: int, consume: bool = False) -> None:
@@ -128,8 +163,8 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, block: int, consume: bool
             (consume and gate_up.dtype != torch.float32) or (not consume and gate_up.dtype != out.dtype):
         raise KernelError("silu_mul: shapes or dtypes do not fit")
     lib = build.load_library("elementwise")
-    _check(lib, lib.tllm_silu_mul(_ptr(gate_up), _ptr(out), m, inter, block, _code(gate_up.dtype), _code(out.dtype),
-                                  1 if consume else 0, _stream()))
+    _call(lib, lib.tllm_silu_mul, _ptr(gate_up), _ptr(out), m, inter, block, _code(gate_up.dtype), _code(out.dtype),
+                                  1 if consume else 0, _stream())
 
 
 def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, cos: Optional[torch.Tensor],
@@ -158,12 +193,12 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, cos: Optional[torc
     if cos is not None and (cos.dtype != torch.float32 or not cos.is_contiguous() or cos.shape[1] * 2 != rot_dim):
         raise KernelError("rope_kv_write: rotary tables do not fit")
     lib = build.load_library("elementwise")
-    _check(lib, lib.tllm_rope_kv_write(
+    _call(lib, lib.tllm_rope_kv_write,
         _ptr(qkv), _ptr(src), 0 if src is None else src.stride(0), _ptr(positions), _ptr(cos), _ptr(sin), rot_dim, t,
         num_heads, num_kv_heads, head_dim,
         qkv.stride(0), _ptr(k_cache if slot_mapping is not None else None),
         _ptr(v_cache if slot_mapping is not None else None), _ptr(slot_mapping), page_size,
-        ctypes.c_longlong(page_stride), ctypes.c_longlong(head_stride), _code(qkv.dtype), _stream()))
+        ctypes.c_longlong(page_stride), ctypes.c_longlong(head_stride), _code(qkv.dtype), _stream())
 
 
 # ----------------------------------------------------------------------------- matrix products
@@ -261,10 +296,10 @@ def _cluster_call(epi, a, w, out, slices, positions=None, cos=None, sin=None, nq
     page_size = page_stride = head_stride = 0
     if k_cache is not None:
         page_size, page_stride, head_stride = k_cache.shape[2], k_cache.stride(0), k_cache.stride(1)
-    _check(lib, lib.tllm_linear_tc_cluster(
+    _call(lib, lib.tllm_linear_tc_cluster,
         _ptr(a), _ptr(w), _ptr(out), m, w.shape[0], k, a.stride(0), out.stride(0), epi, slices, _ptr(positions),
         _ptr(cos), _ptr(sin), nq, nkv, hd, _ptr(k_cache), _ptr(v_cache), _ptr(slot_mapping), page_size,
-        ctypes.c_longlong(page_stride), ctypes.c_longlong(head_stride), _ptr(status_word(a.device)), _stream()))
+        ctypes.c_longlong(page_stride), ctypes.c_longlong(head_stride), _ptr(status_word(a.device)), _stream())
 
 
 def linear_rope_kv(h: torch.Tensor, w_qkv: torch.Tensor, qkv: torch.Tensor, positions: torch.Tensor,
@@ -358,12 +393,12 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool
             splits = _swap_splits(n, k, atomic_ok=(mode == OUT_ACC))
             if splits > 1:
                 epi = EPI_ATOMIC_F32
-        _check(lib, lib.tllm_linear_tc(_ptr(a), _ptr(w), _ptr(out), m, n, k, a.stride(0), out.stride(0), epi, swap,
-                                       splits, _ptr(status_word(a.device)), _stream()))
+        _call(lib, lib.tllm_linear_tc, _ptr(a), _ptr(w), _ptr(out), m, n, k, a.stride(0), out.stride(0), epi, swap,
+                                       splits, _ptr(status_word(a.device)), _stream())
         return
     lib = build.load_library("linear_generic")
-    _check(lib, lib.tllm_linear_generic(_ptr(a), _ptr(w), _ptr(out), m, n, k, a.stride(0), out.stride(0),
-                                        _code(a.dtype), mode, int(linear_skinny), _stream()))
+    _call(lib, lib.tllm_linear_generic, _ptr(a), _ptr(w), _ptr(out), m, n, k, a.stride(0), out.stride(0),
+                                        _code(a.dtype), mode, int(linear_skinny), _stream())
 
 
 def linear_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, block: int, workspace) -> None:
@@ -374,8 +409,8 @@ def linear_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, b
     if _tc_ok(a, w_gate_up, out) and block == 128 and m > 128 and n2 % 256 == 0 and out.is_contiguous():
         _need_cuda(a, w_gate_up, out)
         lib = build.load_library("linear_tc")
-        _check(lib, lib.tllm_linear_tc(_ptr(a), _ptr(w_gate_up), _ptr(out), m, n2, a.shape[1], a.stride(0),
-                                       out.stride(0), EPI_SWIGLU, 0, 1, _ptr(status_word(a.device)), _stream()))
+        _call(lib, lib.tllm_linear_tc, _ptr(a), _ptr(w_gate_up), _ptr(out), m, n2, a.shape[1], a.stride(0),
+                                       out.stride(0), EPI_SWIGLU, 0, 1, _ptr(status_word(a.device)), _stream())
         return
     if (cluster_mask & 4) and _tc_ok(a, w_gate_up, out) and block == 128 and m <= 128 and n2 % 256 == 0 and \
             out.stride(1) == 1 and w_gate_up.is_contiguous():
@@ -459,6 +494,23 @@ def _wide_splits(num_requests: int, num_kv_heads: int, max_kv_len: int) -> int:
 generic_attention_split: Optional[bool] = None
 
 
+split_mixed_attention = os.environ.get("TLLM_SPLIT_MIXED_ATTENTION", "1") != "0"   # (a switch for measurements)
+
+
+class _SubBatch:
+    """Requests [lo, hi) of a step's batch, for a kernel that takes a run of the per-request tables."""
+
+    def __init__(self, batch, lo: int, hi: int, max_q_len: int):
+        self.cu_q = batch.cu_q[lo: hi + 1]
+        self.q_start = batch.q_start[lo: hi]
+        self.num_requests = hi - lo
+        self.max_q_len = max_q_len
+        self.max_kv_len = batch.max_kv_len
+        self.token_request = batch.token_request
+        self.positions = batch.positions
+        self.num_leading_decodes = 0
+
+
 def paged_attention(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, k_cache: torch.Tensor,
                     v_cache: torch.Tensor, block_table: torch.Tensor, batch, out: torch.Tensor, scale: float,
                     window: Optional[int] = None, workspace=None) -> None:
@@ -482,11 +534,21 @@ def paged_attention(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_d
         # portions of prompts: 128 rows of (token, head of the group) per CTA on the tcgen05 tensor cores
         lib = build.load_library("attention_tc", flags=(f"-DTLLM_HEAD_DIM={head_dim}",))
         if lib.tllm_attention_tc_fits(num_heads, num_kv_heads, head_dim, page_size, 0):
-            _check(lib, lib.tllm_attention_tc(
+            lead = getattr(batch, "num_leading_decodes", 0)
+            if 0 < lead < batch.num_requests and group <= 16 and split_mixed_attention:
+                # Decoded tokens beside portions, the decoded ones first (as the scheduler lays a step out): a CTA of
+                # 128 rows would walk a whole context for the one token of a request.  They go to the decode kernel,
+                # the rest to this one: two launches over two runs of the same tables.
+                paged_attention(qkv, num_heads, num_kv_heads, head_dim, k_cache, v_cache, block_table[:lead],
+                                _SubBatch(batch, 0, lead, 1), out, scale, window, workspace)
+                paged_attention(qkv, num_heads, num_kv_heads, head_dim, k_cache, v_cache, block_table[lead:],
+                                _SubBatch(batch, lead, batch.num_requests, batch.max_q_len), out, scale, window, workspace)
+                return
+            _call(lib, lib.tllm_attention_tc,
                 _ptr(qkv), qkv.stride(0), _ptr(k_cache), _ptr(v_cache), ctypes.c_longlong(k_cache.shape[0]),
                 _ptr(block_table), block_table.shape[1], _ptr(batch.cu_q), _ptr(batch.q_start), _ptr(out), t,
                 batch.num_requests, batch.max_q_len, num_heads, num_kv_heads, head_dim, page_size,
-                ctypes.c_float(scale), _ptr(status_word(qkv.device)), _stream()))
+                ctypes.c_float(scale), _ptr(status_word(qkv.device)), _stream())
             return
     if qkv.dtype == torch.bfloat16 and not force_generic and head_dim % 16 == 0 and 16 <= head_dim <= 256 and \
             qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0:
@@ -502,20 +564,20 @@ def paged_attention(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_d
         scratch = None
         if splits > 1 and not wide & 2:
             scratch = workspace.get("attention_partials", (t * num_heads * splits * (head_dim + 2),), torch.float32)
-        _check(lib, lib.tllm_attention_mma(
+        _call(lib, lib.tllm_attention_mma,
             _ptr(qkv), qkv.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
             _ptr(batch.cu_q), _ptr(batch.q_start), _ptr(out), t, batch.num_requests, batch.max_q_len, num_heads,
             num_kv_heads, head_dim, page_size, ctypes.c_longlong(k_cache.stride(0)),
             ctypes.c_longlong(k_cache.stride(1)), ctypes.c_float(scale), int(window or 0), splits, _ptr(scratch),
-            wide, int(batch.max_kv_len), _stream()))
+            wide, int(batch.max_kv_len), _stream())
         return
     lib = build.load_library("attention_generic")
-    _check(lib, lib.tllm_paged_attention_generic(
+    _call(lib, lib.tllm_paged_attention_generic,
         _ptr(qkv), qkv.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
         _ptr(batch.token_request), _ptr(batch.positions), _ptr(out), t, num_heads, num_kv_heads, head_dim,
         page_size, ctypes.c_longlong(k_cache.stride(0)), ctypes.c_longlong(k_cache.stride(1)),
         ctypes.c_float(scale), int(window or 0), _code(qkv.dtype),
-        -1 if generic_attention_split is None else int(generic_attention_split), _stream()))
+        -1 if generic_attention_split is None else int(generic_attention_split), _stream())
 
 
 def attention_tc_timing(head_dim: int = 64) -> Optional[dict]:
@@ -548,7 +610,7 @@ def argmax(logits: torch.Tensor, out: torch.Tensor, status: Optional[torch.Tenso
     if logits.dtype != torch.float32 or not logits.is_contiguous() or out.numel() != n + (status is not None):
         raise KernelError("argmax: logits must be contiguous float32 [n, V] and out int32 [n] (n + 1 with a status word)")
     lib = build.load_library("sampling")
-    _check(lib, lib.tllm_argmax(_ptr(logits), _ptr(out), n, v, _ptr(status), _stream()))
+    _call(lib, lib.tllm_argmax, _ptr(logits), _ptr(out), n, v, _ptr(status), _stream())
 
 
 def sample(logits: torch.Tensor, work: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
@@ -568,8 +630,8 @@ def sample(logits: torch.Tensor, work: torch.Tensor, temperature: torch.Tensor, 
             any(x.numel() != n for x in (temperature, top_k, top_p, seeds, counters)):
         raise KernelError("sample: shapes or dtypes do not fit")
     lib = build.load_library("sampling")
-    _check(lib, lib.tllm_sample(_ptr(logits), _ptr(work), n, v, _ptr(temperature), _ptr(top_k), _ptr(top_p),
-                                _ptr(seeds), _ptr(counters), _ptr(out), _ptr(status), _stream()))
+    _call(lib, lib.tllm_sample, _ptr(logits), _ptr(work), n, v, _ptr(temperature), _ptr(top_k), _ptr(top_p),
+                                _ptr(seeds), _ptr(counters), _ptr(out), _ptr(status), _stream())
 
 
 ALL_LIBRARIES = ("elementwise", "linear_generic", "linear_tc", "attention_generic", "sampling")

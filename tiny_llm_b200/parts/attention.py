@@ -22,7 +22,6 @@ from .registry import build_part, register_part
 
 
 class GQAttention:
-    graph_safe = True   # launches kernels only: a step through this part can be captured in a CUDA graph
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: PartSpec, window: Optional[int] = None, shares_cache: bool = False,
@@ -37,6 +36,9 @@ class GQAttention:
         self.shares_cache = shares_cache
         self.scale = 1.0 / math.sqrt(head_dim) if scale is None else float(scale)
         self.position = build_part("position", position)
+        # launches this package's kernels only (a step through this part can be captured in a CUDA graph or run again
+        # from a tape of its launches), unless the position encoding computes by itself
+        self.graph_safe = bool(getattr(self.position, "fused", False) or getattr(self.position, "graph_safe", False))
         self.q_dim = num_heads * head_dim
         self.kv_dim = num_kv_heads * head_dim
         # a call that reads another call's cache projects queries only
