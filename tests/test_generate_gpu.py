@@ -150,3 +150,34 @@ def test_command_line_random_weights_and_a_batch_of_prompts(model_dirs, tmp_path
         assert out == " ".join(map(str, pipe.apply([prompt], max_new_tokens=6, do_sample=False)[0]))
     bad = subprocess.run([sys.executable, "-m", "tiny_llm_b200", "--random_weights"], capture_output=True, text=True, cwd=ROOT)
     assert bad.returncode == 1 and "--config" in bad.stderr
+
+
+def test_many_requests_through_one_engine_give_what_each_gives_alone(model_dirs):
+    """Two dozen requests of random lengths through one engine with a small token budget and a pool that cannot hold
+    them all: steps of every mix (portions beside decoded tokens, requests pushed out and computed again), many of them
+    with sizes seen before, so that graphs are replayed and launches run again from their tapes, with other contents and
+    other pages each time.  In 32-bit every request must get exactly the tokens it gets alone on an engine that walks
+    the model's code for every step."""
+    from tiny_llm_b200 import Pipeline
+    cfg_d, page, _ = TINY["B"]
+    g = torch.Generator().manual_seed(77)
+    lens = torch.randint(1, 60, (24,), generator=g).tolist()
+    news = torch.randint(4, 30, (24,), generator=g).tolist()
+    prompts = [torch.randint(8, cfg_d["vocab_size"], (n,), generator=g).tolist() for n in lens]
+    plain = Pipeline(model_dirs["B"], dtype="float32", device=0, page_size=page, max_tokens=2048, max_requests=4)
+    plain.runner.use_tapes = False
+    plain.runner.use_graphs = False
+    want = [plain.apply([p], max_new_tokens=n, do_sample=False, ignore_eos=True)[0] for p, n in zip(prompts, news)]
+    assert plain.runner.tape_replays == 0 and plain.runner.graph_replays == 0
+    busy = Pipeline(model_dirs["B"], dtype="float32", device=0, page_size=page, max_tokens=20 * page, max_requests=6,
+                    max_tokens_per_step=48, chunk=16)
+    for rounds in range(2):
+        got = []
+        for lo in range(0, 24, 8):   # eight at a time, each with its own length to generate
+            n = max(news[lo: lo + 8])
+            out = busy.apply(prompts[lo: lo + 8], max_new_tokens=n, do_sample=False, ignore_eos=True)
+            got += [o[:k] for o, k in zip(out, news[lo: lo + 8])]
+        assert got == want
+    assert busy.runner.tape_replays > 0 and busy.runner.graph_replays > 0
+    assert busy.scheduler.counters["pushed_out"] > 0
+    assert busy.runner.cache.groups[0].pool.num_used == 0
