@@ -11,6 +11,7 @@ class Workspace:
     def __init__(self, device):
         self.device = device
         self._buffers: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+        self._views: Dict[tuple, torch.Tensor] = {}    # (name, dtype, shape) -> the view handed out before
         self.frozen = False
 
     def reserve(self, name: str, numel: int, dtype: torch.dtype) -> None:
@@ -21,13 +22,26 @@ class Workspace:
                 raise RuntimeError(f"workspace buffer {name!r} would have to grow to {numel} elements "
                                    f"while its address is pinned by a captured graph")
             self._buffers[key] = torch.empty(max(numel, 1), dtype=dtype, device=self.device)
+            self._drop_views(key)
+
+    def _drop_views(self, key) -> None:
+        for k in [k for k in self._views if k[0] == key[0] and k[1] == key[1]]:
+            del self._views[k]
 
     def get(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+        vkey = (name, dtype, tuple(shape))
+        view = self._views.get(vkey)       # a step asks for the same few views over and over: making one costs 3 us
+        if view is not None:
+            return view
         numel = 1
         for s in shape:
             numel *= int(s)
         self.reserve(name, numel, dtype)
-        return self._buffers[(name, dtype)][:numel].view(*shape)
+        view = self._buffers[(name, dtype)][:numel].view(*shape)
+        if len(self._views) > 4096:
+            self._views.clear()
+        self._views[vkey] = view
+        return view
 
     def get_zeroed(self, name: str, shape, dtype: torch.dtype = torch.float32) -> torch.Tensor:
         """A buffer that holds zeros when it is handed out for the first time and that every user
@@ -41,4 +55,5 @@ class Workspace:
             if self.frozen:
                 raise RuntimeError(f"workspace buffer {name!r} would have to grow while its address is pinned")
             self._buffers[key] = torch.zeros(max(numel, 1), dtype=dtype, device=self.device)
+            self._drop_views(key)
         return self._buffers[key][:numel].view(*shape)

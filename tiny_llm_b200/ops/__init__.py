@@ -36,7 +36,7 @@ def _ptr(t: Optional[torch.Tensor]):
 def _stream():
     # torch's current stream of the current device as a raw cudaStream_t (the private accessor is
     # an order of magnitude cheaper than building a Stream object for every launch)
-    return ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(torch.cuda.current_device()))
+    return ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice()))
 
 
 def _need_cuda(*tensors):
