@@ -36,7 +36,7 @@ FLAGS = {
     "num_pages": (int, 0, "Pages of the cache pool (another way to say max_tokens = num_pages x page_size)"),
     "max_requests": (int, 4, "Requests that run side by side (state slots)"),
     "max_tokens_per_step": (int, 2048, "Token budget of one step"),
-    "chunk": (int, 512, "Largest portion of a prompt that runs in one step"),
+    "chunk": (int, 0, "Largest portion of a prompt that runs in one step (0: the step's token budget)"),
     "prompt_per_line": (bool, False, "Every line of an input block is a prompt; a block is generated as one batch"),
     "random_weights": (bool, False, "Make the model from --config and --seed instead of reading --model_path"),
     "config": (str, "", "config.json of the model to make with --random_weights"),
@@ -125,7 +125,7 @@ def main(argv=None) -> int:
         max_tokens = f["max_tokens"] or f["num_pages"] * f["page_size"] or None
         pipeline = Pipeline(model_path, dtype=f["dtype"], device=f["device"], page_size=f["page_size"],
                             max_tokens=max_tokens, max_requests=f["max_requests"],
-                            max_tokens_per_step=f["max_tokens_per_step"], chunk=f["chunk"])
+                            max_tokens_per_step=f["max_tokens_per_step"], chunk=f["chunk"] or None)
         print("\n>>> [Page Mode] Interactive Mode (Multi-line enabled) <<<")
         print(">>> Enter your prompt as token ids. Enter a blank line to end the current input. "
               "Enter EOF (Ctrl+D) to exit. <<<")
