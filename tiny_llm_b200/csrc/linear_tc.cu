@@ -72,6 +72,7 @@ struct ClusterArgs {
   // persistent kernel, residual-adding epilogue only: every tile is cut into `k_splits` runs of k-blocks that
   // different CTAs add into the output (0 or 1: whole K per tile); fills the SMs when there are few tiles
   int k_splits, k_per;             // runs per tile and k-blocks per run (the last run may be shorter, never empty)
+  int out_by_tma;                  // residual-adding epilogue: the sums leave as TMA reductions (the output's map is valid)
 };
 
 // Epilogue of one 128 x BN tile of C in the NORMAL orientation: this thread owns row `row` of the
@@ -699,14 +700,41 @@ struct PersistentSmem {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  // behind the stages: two staging chunks of 128 rows x 32 floats from which the residual-adding epilogue hands its
+  // sums to the TMA unit (cp.reduce.async.bulk.tensor ... add), 128-byte swizzled like every other tile
+  static constexpr int OUT_CHUNK_BYTES = BM * 32 * 4;
+  static constexpr int OUT_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int BAR_OFFSET = OUT_OFFSET + 2 * OUT_CHUNK_BYTES;
   static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16 + 1024;
 };
+
+// The epilogue's side of the TMA unit: a reduction of a shared-memory box into global memory, in bulk groups.
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const void* src, int c0, int c1) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(smem_u32(src)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }   // the four epilogue warps
+// ... and their agreement: true only if `ok` holds in all of them (a warp that gave up a wait must not leave the
+// others standing at the barriers of the staging chunks)
+__device__ __forceinline__ bool epilogue_all(bool ok) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %1, 0;\n\t"
+      "bar.red.and.pred p, 1, 128, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(r) : "r"((uint32_t)ok) : "memory");
+  return r != 0;
+}
 
 template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                            const __grid_constant__ CUtensorMap map_b_strip, void* __restrict__ out, int rows_a, int rows_b,
+                            const __grid_constant__ CUtensorMap map_b_strip, const __grid_constant__ CUtensorMap map_out,
+                            void* __restrict__ out, int rows_a, int rows_b,
                             int k_blocks, int ldo, const ClusterArgs ca, int* __restrict__ status) {
   static_assert(2 * BN <= 512, "two accumulators must fit tensor memory");
   using L = PersistentSmem<BN, STAGES>;
@@ -831,16 +859,43 @@ linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     const int quad = warp & 3;
     const int row = quad * 32 + lane;
     int local = 0;
+    int out_chunks = 0;   // staging chunks handed to the TMA unit so far (their buffers alternate)
     for (int t = first_tile; t < n_items; t += gridDim.x, ++local) {
       const int buf = local & 1;
       bool ok = mbar_wait(&acc_full[buf], (local >> 1) & 1, abort_flag);
       if (!ok) { *abort_flag = 1; atomicExch(status, ERR_EPILOGUE); }
       ok = __all_sync(0xffffffffu, ok);
+      if (EPI == EPI_ADD_F32 && ca.out_by_tma) ok = epilogue_all(ok);
       if (!ok) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quad * 32) << 16);
       if (EPI == EPI_ROPE_KV)
         store_tile_rope_kv<BN>(taddr, (item_tile(t) % tiles_m) * BM + row, item_col(t), item_width(t), rows_a, rows_b, out, ldo, ca);
+      else if (EPI == EPI_ADD_F32 && ca.out_by_tma) {
+        // The sums go to the TMA unit: 32 columns at a time every thread lays its row into a swizzled staging chunk,
+        // the four warps meet, and one thread hands the chunk over as one reduction (add) into the output.  Stores of
+        // 16 bytes per thread, a row apart from lane to lane, kept this epilogue at 4.8 us per tile.
+        uint8_t* stage_out = smem + L::OUT_OFFSET;
+        const int row0 = (item_tile(t) % tiles_m) * BM, col0 = (item_tile(t) / tiles_m) * BN;
+        const bool issuer = warp == 2 && lane == 0;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32, ++out_chunks) {
+          float v[32];
+          tmem_ld32(taddr + c, v);
+          uint8_t* buf = stage_out + (out_chunks & 1) * L::OUT_CHUNK_BYTES;
+          if (issuer) bulk_wait_read<1>();     // the reduction that read this buffer two chunks ago has its data
+          epilogue_barrier();
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<float4*>(buf + row * 128 + ((j ^ (row & 7)) << 4)) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          epilogue_barrier();
+          if (issuer && col0 + c < rows_b) {
+            tma_reduce_add_2d(&map_out, buf, col0 + c, row0);   // rows and columns past the output's end are clipped
+            bulk_commit();
+          }
+        }
+      }
       else if (EPI == EPI_SWIGLU && item_width(t) != BN)
         store_strip_swiglu(taddr, (item_tile(t) % tiles_m) * BM + row,
                            (item_tile(t) / tiles_m) * (BN / 2) + (item_col(t) - (item_tile(t) / tiles_m) * BN), item_width(t) / 2,
@@ -850,6 +905,7 @@ linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buf]);   // four arrivals free the accumulator
     }
+    if (EPI == EPI_ADD_F32 && warp == 2 && lane == 0) bulk_wait_all();   // every reduction of this CTA has been performed
   }
   tc_fence_before();
   __syncthreads();
@@ -874,6 +930,31 @@ static bool make_map(CUtensorMap* map, const void* ptr, int rows, int k, long lo
   cuuint32_t elem[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  if (cache.size() > 4096) cache.clear();
+  cache[key] = *map;
+  return true;
+}
+
+// A 2-D float32 tensor [rows, cols] with row stride ld (elements), in boxes of 128 rows x 32 columns: the output of the
+// residual-adding products as the TMA unit's reductions see it.
+static bool make_out_map(CUtensorMap* map, const void* ptr, int rows, int cols, long long ld) {
+  using Key = std::tuple<const void*, int, int, long long>;
+  static std::map<Key, CUtensorMap> cache;
+  static std::mutex mu;
+  const Key key(ptr, rows, cols, ld);
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) { *map = it->second; return true; }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
+  cuuint32_t box[2] = {32u, (cuuint32_t)BM};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return false;
   if (cache.size() > 4096) cache.clear();
@@ -934,6 +1015,14 @@ static int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, void*
   const int grid = items < sm_count ? items : sm_count;
   const CUtensorMap* strip_map = &mb;
   CUtensorMap ms;
+  // the residual-adding epilogue through the TMA unit where its rules hold: base and row stride on 16 bytes
+  const CUtensorMap* out_map = &ma;   // (a valid map that is never used)
+  CUtensorMap mo;
+  args.out_by_tma = 0;
+  if (EPI == EPI_ADD_F32 && ((uintptr_t)out % 16) == 0 && ldo % 4 == 0 && make_out_map(&mo, out, m, n, ldo)) {
+    args.out_by_tma = 1;
+    out_map = &mo;
+  }
   if (EPI == EPI_ROPE_KV && tiles > sm_count && tiles % sm_count != 0) {
     // the last round is incomplete: cut its tiles into strips of whole heads if those then fit one round
     const int width = ca.hd <= 64 ? 64 : ca.hd, left = tiles % sm_count;
@@ -954,7 +1043,7 @@ static int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, void*
       strip_map = &ms;
     }
   }
-  TLLM_LAUNCH("linear_tc_persistent", kern, grid, THREADS, L::TOTAL, s, ma, mb, *strip_map, out, m, n, (k + BK - 1) / BK, ldo, args, status);
+  TLLM_LAUNCH("linear_tc_persistent", kern, grid, THREADS, L::TOTAL, s, ma, mb, *strip_map, *out_map, out, m, n, (k + BK - 1) / BK, ldo, args, status);
   return TLLM_OK;
 }
 
