@@ -574,11 +574,13 @@ def test_products_at_the_sizes_of_a_2048_token_prompt(ops):
 
 
 @pytest.mark.parametrize("m,n,k", [(512, 2048, 5632), (1024, 2048, 2048), (300, 520, 1000), (129, 256, 512), (640, 2304, 712),
-                                   (200, 200, 456)])
+                                   (200, 200, 456), (255, 96, 256), (900, 72, 96), (2048, 40, 64)])
 def test_residual_adding_product_of_few_tiles_with_its_k_in_runs(ops, m, n, k):
     """Between 129 and about 1,000 tokens the residual-adding products have fewer 128 x 256 tiles than the GPU has SMs, and
     every tile's K is cut into runs that different CTAs add into the output: widths and depths that fill no tile, a
-    last run that is shorter than the others, an output that already holds values."""
+    last run that is shorter than the others, an output that already holds values; outputs narrower than a tile, whose
+    sums leave in fewer staging chunks than a tile has (a chunk past the output's end must not touch a staging buffer
+    that a reduction still reads)."""
     g = torch.Generator().manual_seed(m + n + k)
     a = (torch.randn(m, k, generator=g)).to(torch.bfloat16)
     w = (torch.randn(n, k, generator=g) / math.sqrt(k)).to(torch.bfloat16)

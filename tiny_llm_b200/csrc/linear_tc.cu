@@ -879,7 +879,7 @@ linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         const int row0 = (item_tile(t) % tiles_m) * BM, col0 = (item_tile(t) / tiles_m) * BN;
         const bool issuer = warp == 2 && lane == 0;
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 32, ++out_chunks) {
+        for (int c = 0; c < BN && col0 + c < rows_b; c += 32, ++out_chunks) {   // (columns past the output's end: no chunk)
           float v[32];
           tmem_ld32(taddr + c, v);
           uint8_t* buf = stage_out + (out_chunks & 1) * L::OUT_CHUNK_BYTES;
@@ -890,7 +890,7 @@ linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             *reinterpret_cast<float4*>(buf + row * 128 + ((j ^ (row & 7)) << 4)) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           epilogue_barrier();
-          if (issuer && col0 + c < rows_b) {
+          if (issuer) {
             tma_reduce_add_2d(&map_out, buf, col0 + c, row0);   // rows and columns past the output's end are clipped
             bulk_commit();
           }
