@@ -83,11 +83,13 @@ def test_linear(ops, dtype, m, n, k):
 
 
 @pytest.mark.parametrize("m,n,k", [(1, 2048, 2048), (2, 37, 132), (3, 640, 5632), (4, 16, 4), (5, 331, 80), (8, 2560, 2048),
-                                   (9, 250, 1000), (16, 24, 388), (13, 7, 128)])
+                                   (9, 250, 1000), (16, 24, 388), (13, 7, 128),
+                                   (300, 520, 328), (2048, 256, 2048), (129, 130, 72), (128, 128, 4)])
 def test_float32_linear_of_few_rows_gives_the_bits_of_the_tile_kernel(ops, m, n, k, monkeypatch):
-    """Up to 16 float32 rows run on a kernel of their own; every output element is the same chain of fmaf over
-    ascending k as in the 64 x 64 tiles, so the two agree to the bit, for every row count, for widths and depths
-    that fill no tile or chunk, for a strided input and when adding into the output."""
+    """Up to 16 float32 rows run on a kernel of their own, products of at least 128 x 128 on 128 x 128 tiles; every
+    output element is the same chain of fmaf over ascending k as in the 64 x 64 tiles, so all agree to the bit, for
+    every row count, for widths and depths that fill no tile or chunk, for a strided input and when adding into the
+    output."""
     torch.manual_seed(m * 1000 + n)
     a = torch.randn(m, k + 8, device=DEV)[:, :k]
     w = torch.randn(n, k, device=DEV)
@@ -286,13 +288,16 @@ def test_paged_attention(ops, dtype, nq, nkv, hd, page, window):
 
 @pytest.mark.parametrize("dtype", DT)
 @pytest.mark.parametrize("window", [None, 300])
-def test_attention_of_the_32_bit_path_gives_the_same_bits_with_one_warp_or_eight_per_head(ops, dtype, window, monkeypatch):
+@pytest.mark.parametrize("nq,nkv,hd", [(6, 2, 48), (8, 1, 64), (4, 4, 128), (10, 2, 256)])
+def test_attention_of_the_32_bit_path_gives_the_same_bits_with_one_warp_or_eight_per_head(ops, dtype, window, nq, nkv, hd,
+                                                                                           monkeypatch):
     """The kernel of the 32-bit path walks the keys as eight interleaved running softmaxes that are merged in a fixed
-    order; with few (token, head) pairs eight warps carry one each, with many one warp carries all eight.  Both must
+    order; with few (token, head) pairs eight warps carry one each, with many one warp walks them one after the other
+    for up to four heads of a group at once (or, the plainest form, carries all eight for one head).  All must
     agree with the plain implementation and with each other to the bit, at contexts of a few tiles and of dozens, with
     a window and without: else a token's logits would depend on how many others shared its step."""
     from tiny_llm_b200.engine import Workspace
-    nq, nkv, hd, page = 6, 2, 48, 8
+    page = 8
     lens, q_lens = [2100, 700, 33, 9], [1, 3, 2, 9]
     table, k_cache, v_cache, ks, vs = paged_setup(dtype, 4, lens, nkv, hd, page, seed=5)
     g = torch.Generator().manual_seed(3)
@@ -306,13 +311,13 @@ def test_attention_of_the_32_bit_path_gives_the_same_bits_with_one_warp_or_eight
                                   q_start=starts.to(DEV), num_requests=4, max_q_len=max(q_lens), max_kv_len=max(lens))
     monkeypatch.setattr(ops, "force_generic", True)
     outs = []
-    for split in (False, True):
+    for split in (False, True, 2):    # a warp per (token, kv head, four heads); eight warps per pair; one warp per pair
         monkeypatch.setattr(ops, "generic_attention_split", split)
         out = torch.empty(t, nq * hd, dtype=DT[dtype], device=DEV)
         ops.paged_attention(qkv.to(DEV), nq, nkv, hd, k_cache.to(DEV), v_cache.to(DEV), table.to(DEV), batch, out,
                             1.0 / math.sqrt(hd), window, Workspace(DEV))
         outs.append(out.cpu())
-    assert torch.equal(outs[0], outs[1])
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
     cur = 0
     for r, (l, n) in enumerate(zip(lens, q_lens)):
         q = qkv[cur: cur + n, : nq * hd].float().view(n, nq, hd)

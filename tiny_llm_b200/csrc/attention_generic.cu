@@ -119,6 +119,156 @@ __device__ __forceinline__ void merge_ways(FM way_m, FL way_l, FO way_o, float* 
   }
 }
 
+// The same tile for up to GH query heads that share the key/value head: every key row and value row is fetched once
+// for all of them.  Head by head the operations are those of attend_tile, in the same order.
+constexpr int GH = 4;
+
+template <typename T, int OD>
+__device__ __forceinline__ void attend_tile_grouped(Softmax<OD> (&st)[GH], int nh, int j0, int lo, int p,
+                                                    const float (*q_rows)[OD * 32], const T* kcache, const T* vcache,
+                                                    const int* table, int max_blocks, int kvh, int hd, int page_size,
+                                                    long long page_stride, long long head_stride, int lane) {
+  const int j = j0 + lane;
+  bool valid = j >= lo && j <= p && j / page_size < max_blocks;
+  const int page = valid ? table[j / page_size] : -1;
+  valid = valid && page >= 0;
+  long long row_off = 0;
+  float s[GH];
+#pragma unroll
+  for (int i = 0; i < GH; ++i) s[i] = -CUDART_INF_F;
+  if (valid) {
+    row_off = (long long)page * page_stride + (long long)kvh * head_stride + (long long)(j % page_size) * hd;
+    const T* krow = kcache + row_off;
+    float acc[GH];
+#pragma unroll
+    for (int i = 0; i < GH; ++i) acc[i] = 0.f;
+#pragma unroll 2
+    for (int d = 0; d < hd; d += Vec<T>::N) {
+      float kv[Vec<T>::N];
+      load16(krow + d, kv);
+#pragma unroll
+      for (int i = 0; i < GH; ++i)
+#pragma unroll
+        for (int e = 0; e < Vec<T>::N; ++e) acc[i] = fmaf(q_rows[i][d + e], kv[e], acc[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < GH; ++i) s[i] = acc[i];
+  }
+  float pr[GH];
+#pragma unroll
+  for (int i = 0; i < GH; ++i) {
+    pr[i] = 0.f;
+    if (i < nh) {
+      const float m_new = fmaxf(st[i].m, warp_max(s[i]));
+      const float m_ref = m_new == -CUDART_INF_F ? 0.f : m_new;
+      pr[i] = valid ? expf(s[i] - m_ref) : 0.f;
+      const float corr = expf(st[i].m - m_ref);
+      st[i].l = fmaf(st[i].l, corr, warp_sum(pr[i]));
+      st[i].m = m_new;
+#pragma unroll
+      for (int x = 0; x < OD; ++x) st[i].o[x] = __fmul_rn(st[i].o[x], corr);
+    }
+  }
+  const int last = min(31, p - j0);
+  const int first = max(0, lo - j0);
+  for (int kk = first; kk <= last; ++kk) {
+    float pk[GH];
+    bool any = false;
+#pragma unroll
+    for (int i = 0; i < GH; ++i) {
+      pk[i] = __shfl_sync(0xffffffffu, pr[i], kk);
+      any = any || pk[i] != 0.f;
+    }
+    if (!any) continue;   // uniform across the warp: nothing to add, and the row may name no page
+    const long long off = __shfl_sync(0xffffffffu, row_off, kk);
+    const T* vrow = vcache + off;
+#pragma unroll
+    for (int x = 0; x < OD; ++x) {
+      const int d = lane + 32 * x;
+      if (d < hd) {
+        const float v = to_f32(vrow[d]);
+#pragma unroll
+        for (int i = 0; i < GH; ++i)
+          if (pk[i] != 0.f) st[i].o[x] = fmaf(pk[i], v, st[i].o[x]);
+      }
+    }
+  }
+}
+
+// Many (token, head) pairs (prompts): one warp per (token, key/value head, up to GH of its query heads).  The eight
+// softmaxes are walked one after the other (way w over its own tiles in ascending order, as everywhere), their results
+// parked in shared memory and merged per head in the order 0..7: the arithmetic of every head is that of the other two
+// launches, and the keys and values of a tile are fetched once for the heads of the group instead of once per head
+// (with one warp per pair the kernel was bound by those fetches: 34 GB through L2 per layer of a 2,048-token prompt).
+template <int OD> struct GroupedWarps { static constexpr int N = OD <= 2 ? 4 : (OD <= 4 ? 2 : 1); };
+
+template <typename T, int OD>
+__global__ void __launch_bounds__(GroupedWarps<OD>::N * 32)
+paged_attention_grouped_kernel(const T* __restrict__ q, int q_row_stride, const T* __restrict__ kcache,
+                               const T* __restrict__ vcache, const int* __restrict__ block_table,
+                               int max_blocks, const int* __restrict__ token_request,
+                               const int* __restrict__ positions, T* __restrict__ out, int n_tokens,
+                               int nq, int nkv, int hd, int page_size, long long page_stride,
+                               long long head_stride, float scale, int window) {
+  constexpr int GW = GroupedWarps<OD>::N;
+  __shared__ __align__(16) float q_s[GW][GH][OD * 32];
+  __shared__ float way_s[GW][WAYS][GH][OD * 32 + 2];
+  pdl_trigger();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int group = nq / nkv, chunks = (group + GH - 1) / GH;
+  const long long task = (long long)blockIdx.x * GW + warp;
+  if (task >= (long long)n_tokens * nkv * chunks) return;
+  const int t = (int)(task / (nkv * chunks)), rem = (int)(task % (nkv * chunks));
+  const int kvh = rem / chunks, h0 = (rem % chunks) * GH, nh = min(GH, group - h0);
+  const int head0 = kvh * group + h0;
+  const int req = token_request[t];
+  const int p = positions[t];
+  const int lo = window > 0 ? max(0, p - window + 1) : 0;
+  const int* table = block_table + (size_t)req * max_blocks;
+  for (int i = 0; i < nh; ++i) {
+    const T* qrow = q + (size_t)t * q_row_stride + (size_t)(head0 + i) * hd;
+    for (int d = lane; d < hd; d += 32) q_s[warp][i][d] = to_f32(qrow[d]) * scale;
+  }
+  for (int i = nh; i < GH; ++i)
+    for (int d = lane; d < hd; d += 32) q_s[warp][i][d] = 0.f;
+  __syncwarp();
+
+  const int first_group = (lo / (32 * WAYS)) * (32 * WAYS);
+  for (int w = 0; w < WAYS; ++w) {
+    Softmax<OD> st[GH];
+#pragma unroll
+    for (int i = 0; i < GH; ++i) {
+      st[i].m = -CUDART_INF_F; st[i].l = 0.f;
+#pragma unroll
+      for (int x = 0; x < OD; ++x) st[i].o[x] = 0.f;
+    }
+    for (int j0 = first_group + w * 32; j0 <= p; j0 += 32 * WAYS)
+      if (j0 + 31 >= lo)
+        attend_tile_grouped<T, OD>(st, nh, j0, lo, p, q_s[warp], kcache, vcache, table, max_blocks, kvh, hd, page_size,
+                                   page_stride, head_stride, lane);
+#pragma unroll
+    for (int i = 0; i < GH; ++i) {
+      if (lane == 0) { way_s[warp][w][i][OD * 32] = st[i].m; way_s[warp][w][i][OD * 32 + 1] = st[i].l; }
+#pragma unroll
+      for (int x = 0; x < OD; ++x) way_s[warp][w][i][lane + 32 * x] = st[i].o[x];
+    }
+  }
+  __syncwarp();
+  for (int i = 0; i < nh; ++i) {
+    float o[OD], l;
+    merge_ways<OD>([&](int w) { return way_s[warp][w][i][OD * 32]; }, [&](int w) { return way_s[warp][w][i][OD * 32 + 1]; },
+                   [&](int w, int x) { return way_s[warp][w][i][lane + 32 * x]; }, o, l);
+    T* orow = out + (size_t)t * nq * hd + (size_t)(head0 + i) * hd;
+    const float inv = 1.f / l;
+#pragma unroll
+    for (int x = 0; x < OD; ++x) {
+      const int d = lane + 32 * x;
+      if (d < hd) orow[d] = from_f32<T>(o[x] * inv);
+    }
+  }
+}
+
 // SPLIT = false: WARPS (token, head) pairs per CTA, one warp each, eight softmaxes in its registers.
 // SPLIT = true: one pair per CTA of eight warps, warp w carries softmax w.
 template <typename T, bool SPLIT, int OD>
@@ -220,8 +370,14 @@ extern "C" int tllm_paged_attention_generic(const void* q, int q_row_stride, con
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
     TLLM_FAIL(TLLM_ERR_CUDA, "attention: cannot read the number of SMs");
-  const bool split = split_override >= 0 ? split_override != 0 : tasks <= 8LL * sms;
-  const long long blocks = split ? tasks : (tasks + WARPS - 1) / WARPS;
+  // split_override: -1 by the number of pairs; 1 eight warps per pair; 0 one warp per (token, key/value head, four heads);
+  // 2 one warp per pair (the plainest form, kept for comparison: all give the same bits)
+  const bool split = split_override >= 0 ? split_override == 1 : tasks <= 8LL * sms;
+  const bool grouped = !split && split_override != 2;
+  const int od = hd <= 64 ? 2 : (hd <= 128 ? 4 : 8);
+  const int gw = od <= 2 ? 4 : (od <= 4 ? 2 : 1);
+  const long long gtasks = (long long)n_tokens * nkv * ((nq / nkv + GH - 1) / GH);
+  const long long blocks = split ? tasks : (grouped ? (gtasks + gw - 1) / gw : (tasks + WARPS - 1) / WARPS);
   TLLM_REQUIRE(blocks <= 2147483647LL, "attention: %lld (token, head) pairs exceed the grid", tasks);
   cudaStream_t s = (cudaStream_t)stream;
 #define TLLM_ATT_GENERIC(T_, SPLIT_, OD_)                                                                             \
@@ -235,14 +391,29 @@ extern "C" int tllm_paged_attention_generic(const void* q, int q_row_stride, con
     else if (hd <= 128) TLLM_ATT_GENERIC(T_, SPLIT_, 4);             \
     else TLLM_ATT_GENERIC(T_, SPLIT_, 8);                            \
   } while (0)
+#define TLLM_ATT_GROUPED(T_, OD_)                                                                                     \
+  TLLM_LAUNCH("paged_attention_grouped", (paged_attention_grouped_kernel<T_, OD_>), (unsigned)blocks,                  \
+              GroupedWarps<OD_>::N * 32, 0, s, (const T_*)q, q_row_stride, (const T_*)kcache, (const T_*)vcache,      \
+              block_table, max_blocks, token_request, positions, (T_*)out, n_tokens, nq, nkv, hd, page_size,           \
+              page_stride, head_stride, scale, window)
+#define TLLM_ATT_GROUPED_HD(T_)                          \
+  do {                                                  \
+    if (od == 2) TLLM_ATT_GROUPED(T_, 2);                \
+    else if (od == 4) TLLM_ATT_GROUPED(T_, 4);           \
+    else TLLM_ATT_GROUPED(T_, 8);                        \
+  } while (0)
   if (dtype == TLLM_F32) {
-    if (split) TLLM_ATT_GENERIC_HD(float, true); else TLLM_ATT_GENERIC_HD(float, false);
+    if (split) TLLM_ATT_GENERIC_HD(float, true); else if (grouped) TLLM_ATT_GROUPED_HD(float); else TLLM_ATT_GENERIC_HD(float, false);
   } else if (dtype == TLLM_BF16) {
-    if (split) TLLM_ATT_GENERIC_HD(__nv_bfloat16, true); else TLLM_ATT_GENERIC_HD(__nv_bfloat16, false);
+    if (split) TLLM_ATT_GENERIC_HD(__nv_bfloat16, true);
+    else if (grouped) TLLM_ATT_GROUPED_HD(__nv_bfloat16);
+    else TLLM_ATT_GENERIC_HD(__nv_bfloat16, false);
   } else {
     TLLM_FAIL(TLLM_ERR_ARG, "attention: unknown dtype code %d", dtype);
   }
 #undef TLLM_ATT_GENERIC_HD
+#undef TLLM_ATT_GROUPED_HD
+#undef TLLM_ATT_GROUPED
 #undef TLLM_ATT_GENERIC
   return TLLM_OK;
 }

@@ -3,7 +3,8 @@
 // tensor-core kernels refuse.  Any M, N, K.  Every output element is ONE chain of fmaf over k in
 // ascending order starting from zero, whatever M is and whichever of the two kernels below computes it,
 // so a row's result does not depend on its batch, to the bit.
-//   linear_generic_kernel: 64 x 64 tiles, 4 x 4 outputs per thread (many rows);
+//   linear_generic_kernel: 64 x 64 tiles, 4 x 4 outputs per thread (any sizes and both dtypes);
+//   linear_large_kernel: float32, 128 x 128 tiles, 8 x 8 outputs per thread (products of at least 128 x 128);
 //   linear_skinny_kernel: float32, at most 16 rows (decoded tokens): a CTA takes 8 or 16 weight rows and
 //     streams them through shared memory in chunks of 128 k (cp.async, three stages), one thread per
 //     output element.  With so few rows the 64-row tile left 32 CTAs to stream a matrix that 148 SMs could
@@ -79,6 +80,98 @@ linear_generic_kernel(const T* __restrict__ a, const T* __restrict__ w, void* __
       else reinterpret_cast<float*>(out)[o] += acc[i][j];
     }
   }
+}
+
+// ---------------------------------------------------------------- many rows: 128 x 128 tiles, 8 x 8 outputs per thread
+// The same chains of fmaf (k ascending from zero for every output element), with an eighth of the shared-memory reads
+// per fmaf of the 64 x 64 kernel: 16-byte global loads of the next 16-wide slice of k into registers while the current
+// one is multiplied, shared memory transposed to [k][row] so that a thread's eight rows (and eight columns) are two
+// 16-byte reads.  Taken for products of at least 128 x 128 whose rows start on 16 bytes; float32 only.
+constexpr int LBM = 128, LBN = 128, LBK = 16, LTHREADS = 256;
+
+template <int MODE>
+__global__ void __launch_bounds__(LTHREADS)
+linear_large_kernel(const float* __restrict__ a, const float* __restrict__ w, float* __restrict__ out,
+                    int m, int n, int k, int lda, int ldo) {
+  __shared__ __align__(16) float as[2][LBK][LBM + 4];
+  __shared__ __align__(16) float ws[2][LBK][LBN + 4];
+  pdl_trigger();
+  pdl_wait();
+  const int tid = threadIdx.x;
+  const int tx = tid % 16, ty = tid / 16;          // this thread's columns tx * 4 + {0..3} and 64 + tx * 4 + {0..3}; rows likewise
+  const int m0 = blockIdx.y * LBM, n0 = blockIdx.x * LBN;
+  // loader: thread -> (row lr of the tile, k quad lq); two rows per operand (lr and lr + 64)
+  const int lr = tid / 4, lq = (tid % 4) * 4;
+  float acc[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+  float4 ra[2], rw[2];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int gm = m0 + lr + 64 * h, gn = n0 + lr + 64 * h, kk = k0 + lq;
+      ra[h] = (gm < m && kk < k) ? *reinterpret_cast<const float4*>(a + (size_t)gm * lda + kk) : make_float4(0.f, 0.f, 0.f, 0.f);
+      rw[h] = (gn < n && kk < k) ? *reinterpret_cast<const float4*>(w + (size_t)gn * k + kk) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  };
+  auto stash = [&](int buf) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = lr + 64 * h;
+      as[buf][lq + 0][r] = ra[h].x; as[buf][lq + 1][r] = ra[h].y; as[buf][lq + 2][r] = ra[h].z; as[buf][lq + 3][r] = ra[h].w;
+      ws[buf][lq + 0][r] = rw[h].x; ws[buf][lq + 1][r] = rw[h].y; ws[buf][lq + 2][r] = rw[h].z; ws[buf][lq + 3][r] = rw[h].w;
+    }
+  };
+  fetch(0);
+  stash(0);
+  __syncthreads();
+  int buf = 0;
+  for (int k0 = 0; k0 < k; k0 += LBK) {
+    const bool more = k0 + LBK < k;
+    if (more) fetch(k0 + LBK);
+#pragma unroll
+    for (int p = 0; p < LBK; ++p) {
+      const float4 a0 = *reinterpret_cast<const float4*>(&as[buf][p][ty * 4]);
+      const float4 a1 = *reinterpret_cast<const float4*>(&as[buf][p][64 + ty * 4]);
+      const float4 w0 = *reinterpret_cast<const float4*>(&ws[buf][p][tx * 4]);
+      const float4 w1 = *reinterpret_cast<const float4*>(&ws[buf][p][64 + tx * 4]);
+      const float ar[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const float wr[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(ar[i], wr[j], acc[i][j]);
+    }
+    if (more) {
+      stash(buf ^ 1);
+      __syncthreads();
+      buf ^= 1;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int gm = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
+    if (gm >= m) continue;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int gn = n0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + (j - 4));
+      if (gn >= n) continue;
+      const size_t o = (size_t)gm * ldo + gn;
+      if (MODE == OUT_ACC) out[o] += acc[i][j];
+      else out[o] = acc[i][j];
+    }
+  }
+}
+
+static int launch_large(const float* a, const float* w, float* out, int m, int n, int k, int lda, int ldo, int mode, cudaStream_t s) {
+  dim3 grid((n + LBN - 1) / LBN, (m + LBM - 1) / LBM);
+  if (mode == OUT_ACC)
+    TLLM_LAUNCH("linear_large", linear_large_kernel<OUT_ACC>, grid, LTHREADS, 0, s, a, w, out, m, n, k, lda, ldo);
+  else
+    TLLM_LAUNCH("linear_large", linear_large_kernel<OUT_F32>, grid, LTHREADS, 0, s, a, w, out, m, n, k, lda, ldo);
+  return TLLM_OK;
 }
 
 // ---------------------------------------------------------------- at most 16 rows, float32
@@ -191,7 +284,7 @@ int launch(const void* a, const void* w, void* out, int m, int n, int k, int lda
 
 }  // namespace tllm
 
-// skinny: 0 keeps the tile kernel even for few float32 rows (tests compare the two, which must agree to the bit)
+// skinny: 0 keeps the 64 x 64 tile kernel for every size (tests compare it with the two others, which must agree with it to the bit)
 extern "C" int tllm_linear_generic(const void* a, const void* w, void* out, int m, int n, int k, int lda, int ldo,
                                    int dtype, int mode, int skinny, void* stream) {
   TLLM_REQUIRE(m > 0 && n > 0 && k > 0, "linear: empty product %d x %d x %d", m, n, k);
@@ -209,6 +302,9 @@ extern "C" int tllm_linear_generic(const void* a, const void* w, void* out, int 
     if (m <= 8) return tllm::launch_skinny<8>(af, wf, of, m, n, k, lda, ldo, mode, s);
     return tllm::launch_skinny<16>(af, wf, of, m, n, k, lda, ldo, mode, s);
   }
+  if (dtype == TLLM_F32 && skinny != 0 && m >= 128 && n >= 128 && k % 4 == 0 && lda % 4 == 0 && ((uintptr_t)a % 16) == 0 &&
+      ((uintptr_t)w % 16) == 0 && (m + tllm::LBM - 1) / tllm::LBM <= 65535)
+    return tllm::launch_large((const float*)a, (const float*)w, (float*)out, m, n, k, lda, ldo, mode, (cudaStream_t)stream);
   if (dtype == TLLM_F32) return tllm::launch<float>(a, w, out, m, n, k, lda, ldo, mode, (cudaStream_t)stream);
   if (dtype == TLLM_BF16) return tllm::launch<__nv_bfloat16>(a, w, out, m, n, k, lda, ldo, mode, (cudaStream_t)stream);
   TLLM_FAIL(TLLM_ERR_ARG, "linear: unknown dtype code %d", dtype);

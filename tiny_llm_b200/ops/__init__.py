@@ -489,9 +489,10 @@ def _wide_splits(num_requests: int, num_kv_heads: int, max_kv_len: int) -> int:
     return splits if ctas < lo and hi > 0 and _cluster_merge(num_requests, num_kv_heads, splits) else 0
 
 
-# The attention of the 32-bit path runs one warp or eight warps per (token, head), by the number of pairs; both give
-# the same bits.  True / False force one of them (tests compare the two).
-generic_attention_split: Optional[bool] = None
+# The attention of the 32-bit path runs eight warps per (token, head) or one warp per (token, key/value head, four query
+# heads), by the number of pairs; both give the same bits.  True / False force one of them, 2 the plainest form (one
+# warp per pair); tests compare the three.
+generic_attention_split = None
 
 
 split_mixed_attention = os.environ.get("TLLM_SPLIT_MIXED_ATTENTION", "1") != "0"   # (a switch for measurements)
