@@ -154,7 +154,9 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, float* __restrict__ sr
     const int e = h * hd + i;
     float va, vb;
     if (srow) {
-      va = srow[e]; vb = srow[e + half_hd];
+      // the projection's output is a tensor of the model's dtype: its sums are rounded to it before the rotation,
+      // as where the projection itself stores them
+      va = to_f32(from_f32<T>(srow[e])); vb = to_f32(from_f32<T>(srow[e + half_hd]));
       srow[e] = 0.f; srow[e + half_hd] = 0.f;
     } else {
       va = to_f32(row[e]); vb = to_f32(row[e + half_hd]);
@@ -239,6 +241,8 @@ __global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, float* __restrict_
     if (srow) {
       load8(srow + e, va); load8(srow + e + half_hd, vb);
       store8(srow + e, zeros); store8(srow + e + half_hd, zeros);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { va[j] = to_f32(from_f32<T>(va[j])); vb[j] = to_f32(from_f32<T>(vb[j])); }   // (as above)
     } else {
       load8(row + e, va); load8(row + e + half_hd, vb);
     }
