@@ -296,6 +296,10 @@ extern "C" long long tllm_attention_mma_scratch_bytes(int n_tokens, int nq, int 
   return splits <= 1 ? 0 : (long long)n_tokens * nq * splits * (HD + 2) * 4;
 }
 
+// Attention of the step's tokens over the paged cache (bfloat16).  `splits` > 1: the keys of decoded tokens in that many
+// slices, merged from `scratch` by a kernel behind, unless `wide` has bit 1.  `wide` (decoded tokens only): bit 0 = one warp
+// per 64-key tile (slices of at most four tiles, `max_kv_len` the longest context of the step), bit 1 = the 2 to 8 slices
+// of a (request, key/value head) form a cluster that merges them itself (no scratch, no merging kernel).
 extern "C" int tllm_attention_mma(const void* q, int q_row_stride, const void* kcache, const void* vcache,
                                   const int* block_table, int max_blocks, const int* cu_q, const int* q_start,
                                   void* out, int n_tokens, int n_requests, int max_q_len, int nq, int nkv, int hd,
@@ -325,7 +329,7 @@ extern "C" int tllm_attention_mma(const void* q, int q_row_stride, const void* k
   const long long gx = (long long)n_requests * p.tiles_per_req;
   TLLM_REQUIRE(gx <= 2147483647LL, "attention_mma: grid too large");
   cudaStream_t s = (cudaStream_t)stream;
-  // wide != 0 (decoded tokens only): every slice has at most four tiles for the longest context of the step, and one
+  // wide, bit 0 (decoded tokens only): every slice has at most four tiles for the longest context of the step, and one
   // warp takes each (tllm_attention_mma_wide_fits says whether this head size leaves room for two such CTAs on an SM)
   const bool cluster = (wide & 2) != 0;   // bit 1: the slices of a (request, key/value head) merge inside a cluster
   if (cluster) TLLM_REQUIRE((wide & 1) && splits >= 2 && splits <= 8,
