@@ -192,11 +192,16 @@ def timed_prefill(runner, tokens, repeats=5):
     for i in range(repeats + 2):
         runner.cache.add_request("p")
         torch.cuda.synchronize()
+        if TRACE and i == repeats + 1:   # the last step alone, between two reads of the timeline notes
+            from tiny_llm_b200 import ops
+            ops.trace_dump()
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0.record()
         runner.step([StepEntry("p", toks, [tokens - 1])])
         t1.record()
         torch.cuda.synchronize()
+        if TRACE and i == repeats + 1:
+            timed_prefill.timeline = ops.trace_dump()
         runner.cache.free_request("p")
         if i >= 2:
             times.append(t0.elapsed_time(t1))
@@ -399,6 +404,7 @@ def main():
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="measure one part only (for profiler captures of a small case)")
     ap.add_argument("--batch", type=int, default=BATCH, help="requests of the decode step (default 8)")
+    ap.add_argument("--tokens", type=int, default=2048, help="tokens of the prompt step of --only prefill (default 2,048)")
     ap.add_argument("--page-size", type=int, default=PAGE, help="tokens per page of the cache")
     ap.add_argument("--shape", default="tinyllama", choices=["tinyllama"] + list(OTHER_SHAPES),
                     help="layer sizes for --only runs (profiler captures of the other models' kernels)")
@@ -445,12 +451,14 @@ def main():
             print(json.dumps(rec))
         else:
             ops.attention_tc_timing(cfg.head_dim)   # (a build with cycle counters: start from zero)
-            rec = {"only": "prefill", "shape": args.shape, "layers": cfg.num_hidden_layers, "tokens": 2048,
-                   "ms": round(timed_prefill(runner, 2048, repeats=2), 3)}
+            rec = {"only": "prefill", "shape": args.shape, "layers": cfg.num_hidden_layers, "tokens": args.tokens,
+                   "ms": round(timed_prefill(runner, args.tokens, repeats=2), 3)}
+            if TRACE:
+                rec["timeline"] = timeline_summary(timed_prefill.timeline)
             cycles = ops.attention_tc_timing(cfg.head_dim)
             if cycles is not None:
                 # cycles per key tile in the roles of the attention kernel's first CTA, which walks 2048 / 64 tiles
-                tiles = (2048 // 64) * args.layers * 4
+                tiles = (args.tokens // 64) * args.layers * 4
                 rec["attention_cycles_per_tile"] = {n: round(v / tiles, 1) for n, v in cycles.items()}
             print(json.dumps(rec))
         return 0
