@@ -405,6 +405,8 @@ def main():
                     help="measure one part only (for profiler captures of a small case)")
     ap.add_argument("--batch", type=int, default=BATCH, help="requests of the decode step (default 8)")
     ap.add_argument("--tokens", type=int, default=2048, help="tokens of the prompt step of --only prefill (default 2,048)")
+    ap.add_argument("--context", type=int, default=CONTEXT,
+                    help="context the last timed step of --only decode reaches (default 2,048; at most the model's positions)")
     ap.add_argument("--page-size", type=int, default=PAGE, help="tokens per page of the cache")
     ap.add_argument("--shape", default="tinyllama", choices=["tinyllama"] + list(OTHER_SHAPES),
                     help="layer sizes for --only runs (profiler captures of the other models' kernels)")
@@ -436,16 +438,23 @@ def main():
     if start_len < 64:
         print(f"--steps {steps} x {REPEATS} repeats + --warmup {warmup} do not fit a context of {CONTEXT}")
         return 2
-    runner = make_runner(model, dtype, device, max_tokens=64 * CONTEXT, page_size=PAGE, max_requests=64,
+    if args.only == "decode" and not 64 + steps + warmup <= args.context <= cfg.max_position_embeddings:
+        print(f"--context {args.context}: the model has {cfg.max_position_embeddings} positions, and {steps} + {warmup} steps must fit")
+        return 2
+    pool_tokens = 64 * CONTEXT if args.only != "decode" else max(args.batch, 1) * (args.context + PAGE)
+    runner = make_runner(model, dtype, device, max_tokens=pool_tokens, page_size=PAGE, max_requests=64,
                          max_tokens_per_step=2048)
     out = torch.zeros(64, dtype=torch.int32, device=device)
 
     if args.only != "all":
-        # a small, single-purpose run for a profiler capture: one plain line, no record
+        # a small, single-purpose run for a profiler capture or a sweep: one plain line, no record
         if args.only == "decode":
-            ms, launched, _ = timed_decode(runner, args.batch, CONTEXT - (steps + warmup), steps, warmup, out)
-            rec = {"only": "decode", "shape": args.shape, "batch": args.batch, "layers": cfg.num_hidden_layers,
-                   "ms_per_step": round(ms, 4), "gpu_launches": launched}
+            ms, launched, ctx = timed_decode(runner, args.batch, args.context - (steps + warmup), steps, warmup, out)
+            moved = decode_bytes(model, runner, args.batch, ctx, itemsize)
+            rec = {"only": "decode", "shape": args.shape, "batch": args.batch, "context": args.context,
+                   "layers": cfg.num_hidden_layers, "ms_per_step": round(ms, 4),
+                   "tokens_per_s": round(args.batch * 1e3 / ms, 1),
+                   "hbm_frac": round(moved / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4), "gpu_launches": launched}
             if TRACE:
                 rec["timeline"] = timeline_summary(timed_decode.timeline)
             print(json.dumps(rec))
